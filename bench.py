@@ -1,0 +1,310 @@
+"""Benchmark of the flash_dism hard path (labels -> forward -> backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the whole path over one batch of the training shape (B8 H16 N8192 D64 R32
+DV64, 512 symbols per head): the discretiser for q and k, the fused hard forward, and the hard
+backward.  Metric: query positions per second, whole job.  With N > 1 (torchrun, one rank per GPU)
+every rank runs the same shape on its own 16 heads (heads are independent: no collective on the
+data path, weak scaling) and the time is the maximum over ranks.
+
+`value` is timed with the inputs resident in HBM; `e2e` times the same step through the drop-in
+Python API with pinned host inputs copied in and results copied out inside the timed region.
+`--impl reference` times the CPU restatement of the reference's dense algorithm (plus the
+reference's own native CPU forward when it was built) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPE = dict(batch=8, heads=16, n=8192, d=64, r=32, dv=64, vocab=512)
+FWD_BYTES = 396   # per position: labels 8, sq+sk 128, v 128, out 128, lse2 4
+BWD_BYTES = 716   # per position: sq,sk 128 + v,dO 256 + labels 8 + lse2 4 read; dsq 128, dsk 64, dv 128 written
+LABEL_BYTES = 264  # per position: q,k rows 256 read, two labels 8 written
+
+
+def measured_peak():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)['hbm_gbs']), 'measured'
+    return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self.stop = threading.Event()
+        self.thread = threading.Thread(target=self.run, daemon=True)
+
+    def run(self):
+        query = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+                 'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+        names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
+        while not self.stop.is_set():
+            try:
+                line = subprocess.run(['nvidia-smi', f'--id={self.index}', f'--query-gpu={query}',
+                                       '--format=csv,noheader,nounits'], capture_output=True, text=True,
+                                      timeout=5).stdout.strip().split(',')
+                self.samples.append(float(line[0]))
+                self.max_mhz = float(line[1])
+                for name, value in zip(names, line[2:]):
+                    if value.strip().lower().startswith('active'):
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self.stop.wait(.1)
+
+    def __enter__(self):
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop.set()
+        self.thread.join()
+
+    def summary(self):
+        return dict(sm_mhz=float(np.median(self.samples)) if self.samples else None, sm_max_mhz=self.max_mhz,
+                    reasons=sorted(self.reasons))
+
+
+def make_inputs(seed, device):
+    s = SHAPE
+    g = torch.Generator().manual_seed(seed)
+    shape = (s['batch'], s['n'], s['heads'])
+    host = {}
+    host['q'], host['k'] = [torch.randn(*shape, s['d'], generator=g).bfloat16() for _ in range(2)]
+    host['v'] = torch.randn(*shape, s['dv'], generator=g).bfloat16()
+    host['sq'], host['sk'] = [(torch.nn.functional.silu(torch.randn(*shape, s['r'], generator=g)) * .4).bfloat16()
+                              for _ in range(2)]
+    params = {name: torch.nn.functional.silu(torch.randn(s['heads'], s['vocab'], s['d'], generator=g)).bfloat16()
+              for name in ('eq', 'ek')}
+    host['dout'] = torch.randn(*shape, s['dv'], generator=g).bfloat16()
+    params['tau'] = torch.full((s['heads'],), .5)
+    params['hard'] = torch.ones(s['batch'], s['heads'], dtype=torch.bool)
+    host = {k: v.pin_memory() for k, v in host.items()}
+    return host, {k: v.to(device) for k, v in params.items()}
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    import dism_b200
+    dism_b200.install_dropin()
+    import cu_flash_dism as cu
+    from flash_dism.hard_forward import forward_hard, hard_log_weights
+    from flash_dism.hard_backward import backward_hard
+
+    rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
+    local = int(os.environ.get('LOCAL_RANK', 0))
+    torch.cuda.set_device(local)
+    device = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    s = SHAPE
+    positions = s['batch'] * s['heads'] * s['n']
+    host, params = make_inputs(rank, device)
+    resident = {k: v.to(device) for k, v in host.items()}
+    launches = [0]
+
+    def step(x, stage_events=None):
+        mark = (lambda: None) if stage_events is None else (lambda: stage_events.append(_event()))
+        mark()
+        iq, ik = cu.labels(x['q'], params['eq']), cu.labels(x['k'], params['ek'])
+        mark()
+        out, norm = forward_hard(x['sq'], x['sk'], x['v'], iq, ik, params['hard'], params['tau'])
+        mark()
+        lut = hard_log_weights(params['tau'], s['n'])
+        grads = backward_hard(x['sq'], x['sk'], x['v'], x['dout'], iq, ik, params['hard'], norm,
+                              dict(boundary=None, log_weights=lut))
+        mark()
+        launches[0] += 2 + 2 + 1 + 4  # labels x2, (lut, forward), lut, (dlut, query, key, tau)
+        return out, norm, grads
+
+    def _event():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(resident)
+    barrier()
+    launches[0] = 0
+    stages = []
+    with ClockSampler(local) as clocks:
+        start = _event()
+        for _ in range(args.steps):
+            events = []
+            step(resident, events)
+            stages.append(events)
+        stop = _event()
+        barrier()
+        elapsed_ms = start.elapsed_time(stop)
+        kernel_launches = launches[0]
+        stage_ms = np.array([[a.elapsed_time(b) for a, b in zip(e, e[1:])] for e in stages]).mean(0)
+
+        # end to end: pinned host inputs in, results out, every step
+        copy_names = ('q', 'k', 'sq', 'sk', 'v', 'dout')
+        h2d = sum(host[k].numel() * host[k].element_size() for k in copy_names)
+        result_host = None
+
+        def e2e_step():
+            nonlocal result_host
+            x = {k: host[k].to(device, non_blocking=True) for k in copy_names}
+            out, norm, grads = step(x)
+            outputs = [out, norm, *grads]
+            if result_host is None:
+                result_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outputs]
+            for dst, src in zip(result_host, outputs):
+                dst.copy_(src, non_blocking=True)
+            return outputs
+
+        for _ in range(min(args.warmup, 3)):
+            e2e_step()
+        barrier()
+        e2e_steps = max(2, min(args.steps, 5))
+        e2e_start = _event()
+        for _ in range(e2e_steps):
+            outputs = e2e_step()
+        e2e_stop = _event()
+        barrier()
+        e2e_ms = e2e_start.elapsed_time(e2e_stop)
+        d2h = sum(o.numel() * o.element_size() for o in outputs)
+
+    times = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = times.tolist()
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        ms_per_step = elapsed_ms / args.steps
+        forward_ms = float(stage_ms[1])
+        achieved = FWD_BYTES * positions / (forward_ms * 1e-3) / 1e9
+        line = {
+            'metric': 'DISM fwd+bwd query-positions/s (labels + hard forward + hard backward)',
+            'value': positions * world / (ms_per_step * 1e-3), 'unit': 'positions/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16 vectors, int32 labels, f32 accumulate',
+            'data': 'synthetic (seeded N(0,1) q,k,v,dO; silu(N(0,1)) codebooks and readout features)',
+            'config': {'workload': 'training shape B8 H16 N8192 D64 R32 DV64 V512 per GPU, all rows hard, tau 0.5',
+                       'parallelism': f'heads sharded, 16 heads per GPU x {world}, no collective',
+                       'l2': 'inputs per step (671 MB) exceed L2'},
+            'stage_ms': {'labels': float(stage_ms[0]), 'forward': forward_ms, 'backward': float(stage_ms[2])},
+            'per_gpu_value': positions / (ms_per_step * 1e-3),
+            'e2e': {'value': positions * world / (e2e_ms / e2e_steps * 1e-3), 'unit': 'positions/s',
+                    'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'steps': e2e_steps},
+            'gpu_launches': kernel_launches,
+            'clocks': clocks.summary(),
+            'roofline': {'bound': 'hbm', 'kernel': 'hard_forward_kernel<32,64>', 'achieved': achieved, 'peak': peak,
+                         'unit': 'GB/s', 'frac': achieved / peak, 'peak_kind': peak_kind, 'traffic': None,
+                         'algorithmic_bytes_per_launch': FWD_BYTES * positions},
+            'cpu_baseline': cpu_baseline() if world == 1 else None,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_sample(heads, threads, seed=0):
+    """Time the CPU port on `heads` (batch, head) slices of the benchmark shape; returns seconds."""
+    from oracle import dism_oracle as o
+    s = SHAPE
+    rng = np.random.default_rng(seed)
+    b, n = 1, s['n']
+    f = lambda *shape: o.bf16_round(rng.standard_normal(shape).astype(np.float32))
+    q, k = f(b, n, heads, s['d']), f(b, n, heads, s['d'])
+    eq, ek = f(heads, s['vocab'], s['d']), f(heads, s['vocab'], s['d'])
+    sq, sk = f(b, n, heads, s['r']) * np.float32(.25), f(b, n, heads, s['r']) * np.float32(.25)
+    v, dout = f(b, n, heads, s['dv']), f(b, n, heads, s['dv'])
+    tau, hard = np.full(heads, .5, np.float32), np.ones((b, heads), bool)
+    # the discretiser on the CPU side is a plain fp32 GEMM + argmax (what the reference's torch path does)
+    t0 = time.perf_counter()
+    torch.set_num_threads(threads)
+    iq = torch.argmax(torch.einsum('bnhd,hvd->bnhv', torch.from_numpy(q), torch.from_numpy(eq)), -1)
+    ik = torch.argmax(torch.einsum('bnhd,hvd->bnhv', torch.from_numpy(k), torch.from_numpy(ek)), -1)
+    iq, ik = [t.transpose(1, 2).contiguous().int().numpy() for t in (iq, ik)]
+    t1 = time.perf_counter()
+    o.forward(sq, sk, v, iq, ik, hard, tau, threads=threads)
+    t2 = time.perf_counter()
+    o.backward(sq, sk, v, dout, iq, ik, hard, tau, threads=threads)
+    t3 = time.perf_counter()
+    native = None
+    if o.reference_lib() is not None:
+        t = time.perf_counter()
+        o.reference_forward(sq[0, :, 0], sk[0, :, 0], v[0, :, 0], iq[0, 0], ik[0, 0], .5)
+        native = time.perf_counter() - t
+    return dict(labels=t1 - t0, forward=t2 - t1, backward=t3 - t2, native_forward_one_head=native)
+
+
+def cpu_baseline(heads=None):
+    cores = os.cpu_count() or 1
+    heads = heads or max(cores, 8)
+    cpu_sample(min(heads, 2), cores)  # warm caches and the thread pool
+    t = cpu_sample(heads, cores)
+    total = t['labels'] + t['forward'] + t['backward']
+    return {'value': heads * SHAPE['n'] / total, 'unit': 'positions/s', 'cores': cores, 'kind': 'port',
+            'sample': f'{heads} of the 128 (batch, head) slices at N=8192, all {cores} host threads, '
+                      f'oracle C port (sparse-aware dense recurrence) + torch fp32 argmax for labels',
+            'seconds': {k: v for k, v in t.items() if v is not None}}
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', 0))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    heads = max(cores, 8)
+    for _ in range(args.warmup):
+        cpu_sample(2, cores)
+    start = time.perf_counter()
+    native = []
+    for step in range(args.steps):
+        native.append(cpu_sample(heads, cores, seed=step)['native_forward_one_head'])
+    elapsed = time.perf_counter() - start
+    value = heads * SHAPE['n'] * args.steps / elapsed
+    base = {'value': value, 'unit': 'positions/s', 'cores': cores, 'kind': 'port',
+            'sample': f'each step = {heads} of the 128 (batch, head) slices at N=8192 on all {cores} host threads; '
+                      'C port of the reference dense recurrence (fwd+bwd) + torch fp32 argmax labels',
+            'reference_native_forward_one_head_s': float(np.median([x for x in native if x])) if any(native) else None}
+    print(json.dumps({
+        'impl': 'reference', 'metric': 'DISM fwd+bwd query-positions/s (labels + hard forward + hard backward)',
+        'value': value, 'unit': 'positions/s', 'n_gpus': int(os.environ.get('WORLD_SIZE', 1)), 'steps': args.steps,
+        'warmup': args.warmup, 'ms_per_step': elapsed / args.steps * 1e3, 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'f64 accumulate over bf16-rounded f32 inputs', 'data': 'synthetic',
+        'config': {'workload': 'training shape B8 H16 N8192 D64 R32 DV64 V512, bounded sample of (batch, head) slices'},
+        'cpu_baseline': base,
+        'e2e': {'value': value, 'unit': 'positions/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument('--gpus', type=int, default=1)
+    parser.add_argument('--steps', type=int, default=10)
+    parser.add_argument('--warmup', type=int, default=3)
+    parser.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    args = parser.parse_args()
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,137 @@
+// C ABI of the library: argument validation, error reporting and dispatch to the launchers.
+// The messages keep the key words the reference's checks use ("256-aligned", "CTA", "too short"),
+// so callers that match on them keep working.
+#include "../../include/dism_b200.h"
+#include "dism_common.cuh"
+
+#include <climits>
+#include <cstdarg>
+#include <cstdio>
+
+namespace {
+thread_local char last_error[512] = "";
+
+int fail(int code, const char* format, ...) {
+    va_list args;
+    va_start(args, format);
+    vsnprintf(last_error, sizeof(last_error), format, args);
+    va_end(args);
+    return code;
+}
+int cuda_status(cudaError_t status, const char* what) {
+    if (status == cudaSuccess) return DISM_OK;
+    return fail(DISM_ECUDA, "%s: %s", what, cudaGetErrorString(status));
+}
+bool aligned(const void* p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) & (bytes - 1)) == 0; }
+
+int check_shape(int batch, int heads, int n) {
+    if (batch <= 0 || heads <= 0 || int64_t(batch) * heads > INT_MAX || n <= 0 || n > INT_MAX - 256 || n % 256)
+        return fail(DISM_EINVAL, "positive dimensions and 256-aligned sequence length required");
+    return DISM_OK;
+}
+int check_dims(int r, int dv) {
+    if ((r != 16 && r != 32) || (dv != 32 && dv != 64 && dv != 128))
+        return fail(DISM_EUNSUPPORTED, "unsupported readout shape R=%d DV=%d (R in {16,32}, DV in {32,64,128})", r, dv);
+    return DISM_OK;
+}
+}  // namespace
+
+extern "C" {
+
+const char* dism_last_error(void) { return last_error; }
+int dism_abi_version(void) { return 1; }
+
+int dism_labels(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab,
+                int32_t* labels, void* stream) {
+    if (!x || !codebook || !labels) return fail(DISM_EINVAL, "null pointer");
+    if (batch <= 0 || n <= 0 || heads <= 0 || vocab <= 0 || int64_t(batch) * heads > 65535)
+        return fail(DISM_EINVAL, "positive dimensions required (batch*heads <= 65535)");
+    if (d != 32 && d != 64 && d != 128) return fail(DISM_EUNSUPPORTED, "unsupported label width D=%d", d);
+    if (!aligned(x, 16)) return fail(DISM_EINVAL, "x must be 16-byte aligned");
+    return cuda_status(dism::launch_labels(static_cast<const __nv_bfloat16*>(x),
+                                           static_cast<const __nv_bfloat16*>(codebook), batch, n, heads, d, vocab,
+                                           labels, static_cast<cudaStream_t>(stream)), "labels");
+}
+
+int dism_hard_summary(const int32_t* iq, const int32_t* ik, const uint8_t* hard, int batch, int heads, int n,
+                      int ctas, int32_t* summary, void* stream) {
+    if (int status = check_shape(batch, heads, n)) return status;
+    if (!iq || !ik || !hard || (!summary && n > 32)) return fail(DISM_EINVAL, "null pointer");
+    if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
+    return cuda_status(dism::launch_hard_summary(iq, ik, hard, batch, heads, n, ctas, summary,
+                                                 static_cast<cudaStream_t>(stream)), "hard_summary");
+}
+
+int dism_hard_chunk(const int32_t* summary, int32_t* boundary, int batch_heads, int n, void* stream) {
+    if (int status = check_shape(1, batch_heads, n)) return status;
+    if (!summary || !boundary) return fail(DISM_EINVAL, "null pointer");
+    if (int64_t(n) + int64_t((n - 1) / 32) * 32 > INT_MAX) return fail(DISM_EINVAL, "invalid hard checkpoint shape");
+    return cuda_status(dism::launch_hard_chunk(summary, boundary, batch_heads, n, static_cast<cudaStream_t>(stream)),
+                       "hard_chunk");
+}
+
+int dism_hard_log_weights(const float* tau, int heads, int n, float* lut, void* stream) {
+    if (!tau || !lut) return fail(DISM_EINVAL, "null pointer");
+    if (heads <= 0 || heads > 65535) return fail(DISM_EINVAL, "tau must hold 1..65535 heads");
+    if (n <= 0 || n > INT_MAX - 256 || n % 256)
+        return fail(DISM_EINVAL, "LUT maximum length must be positive and 256-aligned");
+    return cuda_status(dism::launch_log_weights(tau, heads, n, lut, static_cast<cudaStream_t>(stream)),
+                       "hard_log_weights");
+}
+
+int dism_hard_readout(const void* sq, const void* sk, const void* v, const int32_t* iq, const int32_t* ik,
+                      const uint8_t* hard, const int32_t* boundary, const float* lut, int lut_stride, int batch,
+                      int n, int heads, int r, int dv, int ctas, void* out, float* lse2, void* stream) {
+    if (int status = check_shape(batch, heads, n)) return status;
+    if (int status = check_dims(r, dv)) return status;
+    if (!sq || !sk || !v || !iq || !ik || !hard || !lut || !out || !lse2) return fail(DISM_EINVAL, "null pointer");
+    if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
+    if (lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
+    if (!aligned(v, 8) || !aligned(out, 8)) return fail(DISM_EINVAL, "value and output tensors must be 8-byte aligned");
+    dism::HardShape shape{batch, heads, n, r, dv};
+    using bf = __nv_bfloat16;
+    return cuda_status(dism::launch_hard_forward(shape, static_cast<const bf*>(sq), static_cast<const bf*>(sk),
+                                                 static_cast<const bf*>(v), iq, ik, hard, boundary, lut, lut_stride,
+                                                 ctas, static_cast<bf*>(out), lse2, static_cast<cudaStream_t>(stream)),
+                       "hard_readout");
+}
+
+size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride) {
+    if (batch <= 0 || heads <= 0 || n <= 0 || lut_stride <= 0) return 0;
+    return dism::hard_backward_workspace_bytes(batch, heads, n, lut_stride);
+}
+
+int dism_hard_backward(const void* sq, const void* sk, const void* v, const void* dout, const int32_t* iq,
+                       const int32_t* ik, const uint8_t* hard, const int32_t* boundary, const float* lut,
+                       int lut_stride, const float* lse2, int batch, int n, int heads, int r, int dv, int ctas,
+                       float* dsq, void* dsk, void* dv_out, float* dtau, void* workspace, size_t workspace_bytes,
+                       void* stream) {
+    if (int status = check_shape(batch, heads, n)) return status;
+    if (int status = check_dims(r, dv)) return status;
+    if (!sq || !sk || !v || !dout || !iq || !ik || !hard || !lut || !lse2 || !dsq || !dsk || !dv_out || !dtau ||
+        !workspace)
+        return fail(DISM_EINVAL, "null pointer");
+    if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
+    if (lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
+    if (workspace_bytes < dism::hard_backward_workspace_bytes(batch, heads, n, lut_stride) || !aligned(workspace, 4))
+        return fail(DISM_EINVAL, "workspace too small or misaligned (see dism_hard_backward_workspace)");
+    if (!aligned(v, 8) || !aligned(dout, 8) || !aligned(dv_out, 8))
+        return fail(DISM_EINVAL, "value-shaped tensors must be 8-byte aligned");
+    dism::HardShape shape{batch, heads, n, r, dv};
+    using bf = __nv_bfloat16;
+    return cuda_status(dism::launch_hard_backward(shape, static_cast<const bf*>(sq), static_cast<const bf*>(sk),
+                                                  static_cast<const bf*>(v), static_cast<const bf*>(dout), iq, ik,
+                                                  hard, boundary, lut, lut_stride, lse2, ctas, dsq,
+                                                  static_cast<bf*>(dsk), static_cast<bf*>(dv_out), dtau, workspace,
+                                                  static_cast<cudaStream_t>(stream)), "hard_backward");
+}
+
+int dism_longest_match(const int32_t* streams, int batch, int n, int32_t* end, int32_t* length, int32_t* next,
+                       void* stream) {
+    if (!streams || !end || !length || !next) return fail(DISM_EINVAL, "null pointer");
+    if (batch <= 0 || n <= 0 || n % 8) return fail(DISM_EINVAL, "positive batch and a stream length divisible by 8 required");
+    return cuda_status(dism::launch_longest_match(streams, batch, n, end, length, next,
+                                                  static_cast<cudaStream_t>(stream)), "longest_match");
+}
+
+}  // extern "C"

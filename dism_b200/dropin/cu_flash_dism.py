@@ -1,0 +1,247 @@
+"""Stand-in for the reference's native module `cu_flash_dism`, hard path only.
+
+The reference binds its kernels with pybind11 (dism_v3/src/module.cpp:11-37,
+dism_v3/src/frontend.cpp:282-403).  This module keeps those function names, argument orders,
+return shapes and error words, allocates outputs as torch tensors on the inputs' device, and
+forwards plain pointers to the C ABI of libdism_b200.so on the current CUDA stream.  It holds no
+compute of its own and has no fallback: without the library, importing it fails.
+
+Differences a caller can see: `hard_readout` and `hard_backward` accept `boundary=None` (run
+lengths are then derived from the labels inside the kernel, nothing quadratic is stored); the
+packed (`table`) layout and the soft path (`core_forward`, `core_backward`) are not built and
+raise NotImplementedError; the `choice` device word of the reference's CUDA-graph router is
+accepted only as None.
+"""
+import torch
+
+from dism_b200 import _lib
+
+_abi = _lib.load()
+
+# (R, D, DV) combinations the hard kernels are instantiated for; D is irrelevant to them.
+configs = {(r, d, dv): None for r in (16, 32) for d in (32, 64, 128) for dv in (32, 64, 128)}
+
+
+def fp32_enabled():
+    return False
+
+
+def get_config(r, d, dv):
+    if (r, d, dv) not in configs:
+        raise RuntimeError(f'unsupported configuration R={r} D={d} DV={dv}')
+    return None
+
+
+def _fail(message):
+    raise RuntimeError(message)
+
+
+def _stream(tensor):
+    return torch.cuda.current_stream(tensor.device).cuda_stream
+
+
+def _no_table(table, choice):
+    if table is not None:
+        raise NotImplementedError('packed (varlen) layouts are not built yet')
+    if choice is not None:
+        raise NotImplementedError('the CUDA-graph route word is not supported')
+
+
+def _check(tensor, dtype, shape, name):
+    if not (torch.is_tensor(tensor) and tensor.is_cuda and tensor.dtype == dtype and tensor.is_contiguous()
+            and (shape is None or tuple(tensor.shape) == tuple(shape))):
+        _fail(f'{name}: invalid device, dtype, shape or stride')
+
+
+def _check_hard(hard, device, batch, heads, what='hard'):
+    if not (torch.is_tensor(hard) and hard.device == device and hard.dtype == torch.bool and hard.dim() == 2
+            and hard.size(0) > 0 and hard.size(1) == heads and hard.is_contiguous()):
+        _fail(f'{what} must be contiguous bool [training_rows,H]; token-level masks are unsupported '
+              '(sequence hard flags only)')
+    if hard.size(0) != batch:
+        _fail('fixed hard must be [B,H]')
+
+
+def hard_summary(query, key, hard, table=None, ctas=0, choice=None):
+    """int32 labels [B,H,N] -> strip summaries int32 [B,H,(N-1)//32,N]."""
+    _no_table(table, choice)
+    if not (torch.is_tensor(query) and query.is_cuda and query.dtype == torch.int32 and query.dim() == 3
+            and query.is_contiguous()):
+        _fail('query labels must be contiguous CUDA int32 [B,H,N]')
+    b, h, n = query.shape
+    if not (torch.is_tensor(key) and key.device == query.device and key.dtype == torch.int32
+            and key.shape == query.shape and key.is_contiguous()):
+        _fail('invalid key labels')
+    if n <= 0 or n % 256:
+        _fail('positive dimensions and 256-aligned sequence length required')
+    _check_hard(hard, query.device, b, h)
+    if ctas < 0:
+        _fail('invalid CTA count')
+    with torch.cuda.device(query.device):
+        out = torch.empty((b, h, (n - 1) // 32, n), dtype=torch.int32, device=query.device)
+        _lib.check(_abi.dism_hard_summary(query.data_ptr(), key.data_ptr(), hard.data_ptr(), b, h, n, int(ctas),
+                                          out.data_ptr(), _stream(query)))
+    return out
+
+
+def hard_chunk(summary, table=None, heads=0, choice=None, inplace=False):
+    """Compose strip summaries into inclusive boundaries (same shape; aliases the input if inplace)."""
+    if not (torch.is_tensor(summary) and summary.is_cuda and summary.dtype == torch.int32 and summary.is_contiguous()):
+        _fail('hard summary must be contiguous CUDA int32')
+    if table is not None and summary.dim() != 1:
+        _fail('invalid packed hard summary/heads')
+    _no_table(table, choice)
+    if summary.dim() != 4:
+        _fail('fixed hard summary must be [B,H,C,N]')
+    b, h, c, n = summary.shape
+    if b * h <= 0 or not (heads == 0 or heads == h):
+        _fail('invalid fixed batch/head count')
+    if n <= 0 or n % 256 or c != (n - 1) // 32:
+        _fail('invalid hard checkpoint shape/alignment')
+    with torch.cuda.device(summary.device):
+        out = summary if inplace else torch.empty_like(summary)
+        _lib.check(_abi.dism_hard_chunk(summary.data_ptr(), out.data_ptr(), b * h, n, _stream(summary)))
+    return out
+
+
+def hard_log_weights(tau, n, choice=None):
+    """FP32 log2 geometric-sum table [H,n+1] for per-head tau."""
+    _no_table(None, choice)
+    if not (torch.is_tensor(tau) and tau.is_cuda and tau.dtype == torch.float32 and tau.dim() == 1
+            and tau.is_contiguous() and 0 < tau.numel() <= 65535):
+        _fail('tau must be contiguous CUDA FP32 [H]')
+    if n <= 0 or n % 256:
+        _fail('LUT maximum length must be positive and 256-aligned')
+    with torch.cuda.device(tau.device):
+        out = torch.empty((tau.numel(), n + 1), dtype=torch.float32, device=tau.device)
+        _lib.check(_abi.dism_hard_log_weights(tau.data_ptr(), tau.numel(), int(n), out.data_ptr(), _stream(tau)))
+    return out
+
+
+def _vectors(x, count, names):
+    if len(x) != count:
+        _fail('expected ' + ','.join(names))
+    sq = x[0]
+    if not (torch.is_tensor(sq) and sq.is_cuda and sq.dim() == 4):
+        _fail('SQ must be CUDA [B,N,H,R]')
+    b, n, h, r = sq.shape
+    if b <= 0 or h <= 0 or n <= 0 or n % 256:
+        _fail('positive dimensions and 256-aligned length required')
+    return b, n, h, r
+
+
+def _check_boundary(boundary, b, h, n, device):
+    if boundary is None:
+        return 0
+    if not (torch.is_tensor(boundary) and boundary.device == device and boundary.dtype == torch.int32
+            and boundary.is_contiguous() and tuple(boundary.shape) == (b, h, (n - 1) // 32, n)):
+        _fail('hard boundary: invalid device, dtype, shape or stride')
+    return boundary.data_ptr()
+
+
+def _check_lut(lut, h, n, device):
+    if not (torch.is_tensor(lut) and lut.device == device and lut.dtype == torch.float32 and lut.dim() == 2
+            and lut.size(0) == h and lut.is_contiguous()):
+        _fail('invalid hard log-weight table')
+    if lut.size(1) <= n:
+        _fail('hard log-weight table is too short')
+
+
+def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
+    """x = (sq, sk, v, query labels, key labels, hard) -> (bf16 [B,N,H,DV], FP32 log2 normaliser [B,H,N])."""
+    _no_table(table, choice)
+    b, n, h, r = _vectors(x, 6, ('SQ', 'SK', 'V', 'query labels', 'key labels', 'hard flags'))
+    sq, sk, v, iq, ik, hard = x
+    _check(sq, torch.bfloat16, (b, n, h, r), 'SQ')
+    _check(sk, torch.bfloat16, (b, n, h, r), 'SK')
+    _check(v, torch.bfloat16, None, 'V')
+    if v.dim() != 4 or tuple(v.shape[:3]) != (b, n, h):
+        _fail('V: invalid device, dtype, shape or stride')
+    dv = v.size(3)
+    _check(iq, torch.int32, (b, h, n), 'query labels')
+    _check(ik, torch.int32, (b, h, n), 'key labels')
+    _check_hard(hard, sq.device, b, h)
+    _check_lut(lut, h, n, sq.device)
+    if ctas < 0:
+        _fail('invalid CTA count')
+    boundary_ptr = _check_boundary(boundary, b, h, n, sq.device)
+    with torch.cuda.device(sq.device):
+        out = torch.empty((b, n, h, dv), dtype=torch.bfloat16, device=sq.device)
+        norm = torch.empty((b, h, n), dtype=torch.float32, device=sq.device)
+        _lib.check(_abi.dism_hard_readout(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), iq.data_ptr(), ik.data_ptr(),
+                                          hard.data_ptr(), boundary_ptr, lut.data_ptr(), lut.size(1), b, n, h, r, dv,
+                                          int(ctas), out.data_ptr(), norm.data_ptr(), _stream(sq)))
+    return out, norm
+
+
+def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None):
+    """x = (sq, sk, v, dO, query labels, key labels, hard) -> [dSQ f32, dSK bf16, dV bf16, dtau f32[H]]."""
+    _no_table(table, choice)
+    b, n, h, r = _vectors(x, 7, ('SQ', 'SK', 'V', 'dO', 'query labels', 'key labels', 'hard'))
+    sq, sk, v, dout, iq, ik, hard = x
+    _check(sq, torch.bfloat16, (b, n, h, r), 'SQ')
+    _check(sk, torch.bfloat16, (b, n, h, r), 'SK')
+    if not (torch.is_tensor(v) and v.dim() == 4):
+        _fail('V: invalid device, dtype, shape or stride')
+    dv = v.size(3)
+    _check(v, torch.bfloat16, (b, n, h, dv), 'V')
+    _check(dout, torch.bfloat16, (b, n, h, dv), 'dO')
+    _check(iq, torch.int32, (b, h, n), 'query labels')
+    _check(ik, torch.int32, (b, h, n), 'key labels')
+    _check(normalizer, torch.float32, (b, h, n), 'log2 normalizer')
+    if not (torch.is_tensor(hard) and hard.dtype == torch.bool and tuple(hard.shape) == (b, h)
+            and hard.is_contiguous() and hard.device == sq.device):
+        _fail('sequence hard flags: invalid device, dtype, shape or stride')
+    _check_lut(lut, h, n, sq.device)
+    if ctas < 0:
+        _fail('invalid CTA count')
+    boundary_ptr = _check_boundary(boundary, b, h, n, sq.device)
+    with torch.cuda.device(sq.device):
+        dsq = torch.empty((b, n, h, r), dtype=torch.float32, device=sq.device)
+        dsk, dv_out = torch.empty_like(sk), torch.empty_like(v)
+        dtau = torch.empty((h,), dtype=torch.float32, device=sq.device)
+        size = _abi.dism_hard_backward_workspace(b, h, n, lut.size(1))
+        workspace = torch.empty((size,), dtype=torch.uint8, device=sq.device)
+        _lib.check(_abi.dism_hard_backward(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), dout.data_ptr(),
+                                           iq.data_ptr(), ik.data_ptr(), hard.data_ptr(), boundary_ptr,
+                                           lut.data_ptr(), lut.size(1), normalizer.data_ptr(), b, n, h, r, dv,
+                                           int(ctas), dsq.data_ptr(), dsk.data_ptr(), dv_out.data_ptr(),
+                                           dtau.data_ptr(), workspace.data_ptr(), size, _stream(sq)))
+    return [dsq, dsk, dv_out, dtau]
+
+
+def labels(x, codebook):
+    """bf16 rows [B,N,H,D] against bf16 codebooks [H,V,D] -> int32 labels [B,H,N] (lowest index on ties)."""
+    _check(x, torch.bfloat16, None, 'x')
+    if x.dim() != 4:
+        _fail('x must be [B,N,H,D]')
+    b, n, h, d = x.shape
+    _check(codebook, torch.bfloat16, None, 'codebook')
+    if codebook.dim() != 3 or codebook.size(0) != h or codebook.size(2) != d or codebook.device != x.device:
+        _fail('codebook must be [H,V,D] on the device of x')
+    with torch.cuda.device(x.device):
+        out = torch.empty((b, h, n), dtype=torch.int32, device=x.device)
+        _lib.check(_abi.dism_labels(x.data_ptr(), codebook.data_ptr(), b, n, h, d, codebook.size(1), out.data_ptr(),
+                                    _stream(x)))
+    return out
+
+
+def longest_match(streams):
+    """int32 symbol streams [B,N] -> (end index, run length, next symbol), each int32 [B,N]."""
+    _check(streams, torch.int32, None, 'streams')
+    if streams.dim() != 2:
+        _fail('streams must be [B,N]')
+    b, n = streams.shape
+    with torch.cuda.device(streams.device):
+        end, length, nxt = (torch.empty_like(streams) for _ in range(3))
+        _lib.check(_abi.dism_longest_match(streams.data_ptr(), b, n, end.data_ptr(), length.data_ptr(),
+                                           nxt.data_ptr(), _stream(streams)))
+    return end, length, nxt
+
+
+def core_forward(*args, **kwargs):
+    raise NotImplementedError('the soft path is not built in this library')
+
+
+def core_backward(*args, **kwargs):
+    raise NotImplementedError('the soft path is not built in this library')

@@ -1,0 +1,83 @@
+/*
+ * dism_b200 — C ABI of the B200 (sm_100a) implementation of the flash_dism hard path.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its kernels on `stream`
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream), never synchronises the
+ * host, and returns 0 on success or a DISM_E* code; dism_last_error() then holds a message for
+ * the calling thread.  Layouts follow the reference: vectors are contiguous bf16 [B,N,H,C],
+ * labels are contiguous int32 [B,H,N], hard flags are bytes [B,H] (non-zero = hard), N is a
+ * positive multiple of 256.  `ctas` caps the grid (0 = fill the device); results never depend
+ * on it.  Each declaration names the reference interface it stands in for.
+ */
+#ifndef DISM_B200_H
+#define DISM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { DISM_OK = 0, DISM_EINVAL = 1, DISM_EUNSUPPORTED = 2, DISM_ECUDA = 3 };
+
+/* Message of the last failing call on this thread ("" if none). */
+const char *dism_last_error(void);
+/* ABI revision; bumped on any signature change. */
+int dism_abi_version(void);
+
+/* Discretiser: labels[b,h,n] = argmax_v <x[b,n,h,:], codebook[h,v,:]>, lowest index on ties,
+ * FP32 accumulation in ascending d.  x bf16 [B,N,H,D], codebook bf16 [H,V,D], D in {32,64,128}.
+ * Stands in for the label output of emb_fwd (dism_v3/python/flash_dism/emb_kernel.py:88-108,
+ * 155-189) and of kernels/interp_true.py:8-65. */
+int dism_labels(const void *x, const void *codebook, int batch, int n, int heads, int d, int vocab,
+                int32_t *labels, void *stream);
+
+/* Strip summaries: summary int32 [B,H,(N-1)/32,N]; non-causal and soft entries are -1.
+ * Stands in for cu_flash_dism.hard_summary (dism_v3/src/frontend.cpp:309-312,
+ * dism_v3/src/host/hard_summary.cpp:11-73), fixed-length layout. */
+int dism_hard_summary(const int32_t *iq, const int32_t *ik, const uint8_t *hard, int batch, int heads,
+                      int n, int ctas, int32_t *summary, void *stream);
+
+/* Boundary composition over [BH,(N-1)/32,N]; `boundary` may alias `summary` (in place).
+ * Stands in for cu_flash_dism.hard_chunk (dism_v3/src/host/hard_chunk.cpp:10-68). */
+int dism_hard_chunk(const int32_t *summary, int32_t *boundary, int batch_heads, int n, void *stream);
+
+/* lut float [H, n+1]: log2 of sum_{s=1..l} exp(s*tau[h]); entry 0 is -1e6.
+ * Stands in for cu_flash_dism.hard_log_weights (dism_v3/src/host/hard_forward.cpp:11-23). */
+int dism_hard_log_weights(const float *tau, int heads, int n, float *lut, void *stream);
+
+/* Fused hard readout.  `boundary` is the rectangle of dism_hard_chunk or NULL (the kernel then
+ * derives run lengths from the labels alone); lut has row stride lut_stride > N.
+ * out bf16 [B,N,H,DV], lse2 float [B,H,N]; soft (batch, head) rows are written as zeros.
+ * R in {16,32}, DV in {32,64,128}.
+ * Stands in for cu_flash_dism.hard_readout (dism_v3/src/host/hard_forward.cpp:25-113). */
+int dism_hard_readout(const void *sq, const void *sk, const void *v, const int32_t *iq, const int32_t *ik,
+                      const uint8_t *hard, const int32_t *boundary, const float *lut, int lut_stride,
+                      int batch, int n, int heads, int r, int dv, int ctas, void *out, float *lse2,
+                      void *stream);
+
+/* Bytes of scratch dism_hard_backward needs for this shape. */
+size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride);
+
+/* Hard backward: dsq float [B,N,H,R], dsk bf16 [B,N,H,R], dv bf16 [B,N,H,DV], dtau float [H]
+ * (gradient of the natural-log coefficient).  lse2 is the normaliser the forward returned;
+ * `boundary` may be NULL; `workspace` is caller-owned scratch of dism_hard_backward_workspace bytes.
+ * Stands in for cu_flash_dism.hard_backward (dism_v3/src/host/hard_backward.cpp:13-141). */
+int dism_hard_backward(const void *sq, const void *sk, const void *v, const void *dout, const int32_t *iq,
+                       const int32_t *ik, const uint8_t *hard, const int32_t *boundary, const float *lut,
+                       int lut_stride, const float *lse2, int batch, int n, int heads, int r, int dv,
+                       int ctas, float *dsq, void *dsk, void *dv_out, float *dtau, void *workspace,
+                       size_t workspace_bytes, void *stream);
+
+/* Single longest earlier match of symbol streams int32 [B,N] (labels of queries and keys are
+ * the same stream): for every i the most recent j < i with the longest run L(i,j), its length,
+ * and the symbol after it (-1 when nothing matches).  The reference defines L(i,j)
+ * (dism_v3/python/flash_dism/summary.py:8-16) but no single winner: this reduction is ours. */
+int dism_longest_match(const int32_t *streams, int batch, int n, int32_t *end, int32_t *length,
+                       int32_t *next, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

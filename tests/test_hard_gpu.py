@@ -1,0 +1,313 @@
+"""Parity of the CUDA hard path with the CPU oracle and the reference's golden vectors.
+
+Every call goes through the drop-in modules, which forward to the C ABI of libdism_b200.so.
+Tolerances are the ones the reference's own tests use (dism_v3/tests/test_hard_forward.py:54-57,80;
+dism_v3/tests/test_hard_backward.py:32-38); integer stages and labels are compared bit for bit.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden, reference_labels
+
+pytestmark = pytest.mark.gpu
+
+PATTERNS = ['random', 'equal', 'disjoint', 'periodic', 'boundary']
+
+
+@pytest.fixture(scope='module')
+def api():
+    import dism_b200
+    dism_b200.install_dropin()
+    import cu_flash_dism as cu
+    from flash_dism import summary, hard_forward, hard_backward
+    return dict(cu=cu, summary=summary, fwd=hard_forward, bwd=hard_backward)
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def vectors(seed, b, n, h, r, dv):
+    g = torch.Generator().manual_seed(seed)
+    sq, sk = [(torch.nn.functional.silu(torch.randn(b, n, h, r, generator=g)) * .4).bfloat16() for _ in range(2)]
+    v, dout = [torch.randn(b, n, h, dv, generator=g).bfloat16() for _ in range(2)]
+    return sq, sk, v, dout
+
+
+def assert_vectors(actual, expected, atol=.008, rtol=.025, l2=.01):
+    actual, expected = actual.double().cpu(), torch.as_tensor(expected).double()
+    torch.testing.assert_close(actual, expected, atol=atol, rtol=rtol)
+    assert (actual - expected).norm() / expected.norm().clamp_min(1e-8) < l2
+
+
+# ---- integer stages: bit-exact -----------------------------------------------------------------
+@pytest.mark.parametrize('pattern', PATTERNS)
+@pytest.mark.parametrize('n', [256, 512])
+def test_summary_and_boundary_match_golden(api, pattern, n):
+    g = golden(f'pattern_{pattern}.npz')
+    iq, ik, hard = dev(g[f'iq{n}']), dev(g[f'ik{n}']), dev(g['hard'])
+    for ctas in (1, 2, 0):
+        summary = api['summary'].summarize_hard(iq, ik, hard, ctas=ctas)
+        assert np.array_equal(summary.cpu().numpy(), g[f'summary{n}'])
+    boundary = api['summary'].hard_chunk_scan(summary)
+    assert np.array_equal(boundary.cpu().numpy(), g[f'boundary{n}'])
+    assert np.array_equal(summary.cpu().numpy(), g[f'summary{n}'])  # input preserved
+    inplace = api['summary'].hard_chunk_scan(summary, inplace=True)
+    assert inplace.data_ptr() == summary.data_ptr()
+    assert np.array_equal(inplace.cpu().numpy(), g[f'boundary{n}'])
+
+
+@pytest.mark.parametrize('pattern', PATTERNS)
+@pytest.mark.parametrize('n', [1024, 2048])
+def test_summary_and_boundary_match_oracle(api, oracle, pattern, n):
+    q, k = reference_labels(n, pattern)
+    hard = np.array([[True, False, True], [False, True, True]])
+    summary = api['summary'].summarize_hard(dev(q), dev(k), dev(hard))
+    expected = oracle.summary(q, k, hard)
+    assert np.array_equal(summary.cpu().numpy(), expected)
+    assert np.array_equal(api['summary'].hard_chunk_scan(summary).cpu().numpy(), oracle.chunk(expected))
+
+
+@pytest.mark.parametrize('n', [256, 2048])
+def test_chunk_ignores_poisoned_noncausal_entries(api, oracle, n):
+    rng = np.random.default_rng(63)
+    source = rng.integers(-1, n, (2, 3, (n - 1) // 32, n), dtype=np.int32)
+    for c in range(source.shape[2]):
+        source[:, :, c, 32 * c + 32:] = np.iinfo(np.int32).max
+    expected = oracle.chunk(source)
+    for inplace in (False, True):
+        actual = api['summary'].hard_chunk_scan(dev(source), inplace=inplace)
+        assert np.array_equal(actual.cpu().numpy(), expected)
+
+
+# ---- forward ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize('pattern', PATTERNS)
+def test_forward_matches_golden(api, pattern):
+    g = golden(f'pattern_{pattern}.npz')
+    x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
+         dev(g['iq256']), dev(g['ik256']), dev(g['hard']), dev(g['tau'])]
+    out, norm = api['fwd'].forward_hard(*x, ctas=1)
+    assert out.dtype == torch.bfloat16 and norm.dtype == torch.float32
+    assert_vectors(out, g['out'])
+    torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(g['lse2']), atol=2e-5, rtol=2e-6)
+    # the saved-state route (summary + boundary rectangle) gives the same bits as the label-only route
+    out2, norm2, state = api['fwd'].forward_hard(*x, save_state=True)
+    assert torch.equal(out, out2) and torch.equal(norm, norm2)
+    assert np.array_equal(state['boundary'].cpu().numpy(), g['boundary256'])
+
+
+@pytest.mark.parametrize('pattern', PATTERNS)
+@pytest.mark.parametrize('n', [512, 1024])
+def test_forward_matches_oracle(api, oracle, pattern, n):
+    q, k = reference_labels(n, pattern)
+    hard = np.array([[True, False, True], [False, True, True]])
+    sq, sk, v, _ = vectors(417 + n, 2, n, 3, 32, 64)
+    tau = torch.linspace(-.5, .5, 3)
+    out, norm = api['fwd'].forward_hard(sq.cuda(), sk.cuda(), v.cuda(), dev(q), dev(k), dev(hard), tau.cuda())
+    expected, lse2 = oracle.forward(sq.float().numpy(), sk.float().numpy(), v.float().numpy(), q, k, hard, tau.numpy())
+    assert_vectors(out, expected)
+    torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
+
+
+def test_forward_long_chain_tau_sweep(api):
+    g = golden('chain_equal.npz')
+    x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
+         dev(g['iq']), dev(g['ik']), torch.ones(1, 1, dtype=torch.bool, device='cuda')]
+    for index, tau in enumerate(g['taus']):
+        out, norm = api['fwd'].forward_hard(*x, torch.tensor([tau], dtype=torch.float32, device='cuda'))
+        assert_vectors(out, g[f'out{index}'])
+        torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(g[f'lse2_{index}']), atol=2e-5, rtol=2e-6)
+
+
+@pytest.mark.parametrize('r,dv', [(16, 32), (16, 64), (32, 32), (32, 64), (32, 128), (16, 128)])
+def test_forward_backward_dimensions(api, oracle, r, dv):
+    n = 512
+    q, k = reference_labels(n, 'periodic')
+    hard = np.array([[True, False, True], [False, True, True]])
+    sq, sk, v, dout = vectors(5 + r + dv, 2, n, 3, r, dv)
+    tau = torch.linspace(-.5, .5, 3)
+    x = [sq.cuda(), sk.cuda(), v.cuda(), dev(q), dev(k), dev(hard)]
+    out, norm, state = api['fwd'].forward_hard(*x, tau.cuda(), ctas=2, save_state=True)
+    f = lambda t: t.float().numpy()
+    expected, lse2 = oracle.forward(f(sq), f(sk), f(v), q, k, hard, tau.numpy())
+    assert_vectors(out, expected)
+    torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
+    got = api['bwd'].backward_hard(*x[:3], dout.cuda(), *x[3:], norm, state)
+    want = oracle.backward(f(sq), f(sk), f(v), f(dout), q, k, hard, tau.numpy())
+    for a, e in zip(got[:3], want[:3]):
+        assert_vectors(a, e)
+    torch.testing.assert_close(got[3].double().cpu(), torch.from_numpy(want[3]), atol=.003, rtol=.01)
+
+
+def test_forward_exactness_properties(api):
+    g = golden('pattern_boundary.npz')
+    x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
+         dev(g['iq256']), dev(g['ik256']), dev(g['hard']), dev(g['tau'])]
+    out, norm = api['fwd'].forward_hard(*x, ctas=1)
+    for ctas in (2, 0, 7):  # grid size never changes a bit
+        o, m = api['fwd'].forward_hard(*x, ctas=ctas)
+        assert torch.equal(o, out) and torch.equal(m, norm)
+    x[0] = -x[0]  # flipping sq flips the output exactly and leaves the normaliser alone
+    flipped, flipped_norm = api['fwd'].forward_hard(*x, ctas=1)
+    assert torch.equal(flipped, -out) and torch.equal(flipped_norm, norm)
+    x[0] = torch.zeros_like(x[0])
+    zero, zero_norm = api['fwd'].forward_hard(*x)
+    assert not zero.count_nonzero() and torch.equal(zero_norm, norm)
+    x[3], x[4] = torch.full_like(x[3], 1), torch.full_like(x[4], 2)  # disjoint labels: nothing matches
+    zero, zero_norm = api['fwd'].forward_hard(*x)
+    assert not zero.count_nonzero() and not zero_norm.count_nonzero()
+    x[5] = torch.zeros_like(x[5])  # all soft: operands are never read
+    for item in x[:3]:
+        item.fill_(float('nan'))
+    zero, zero_norm = api['fwd'].forward_hard(*x)
+    assert not zero.count_nonzero() and not zero_norm.count_nonzero()
+
+
+def test_forward_is_causal(api):
+    n = 512
+    q, k = reference_labels(n, 'equal')
+    sq, sk, v, _ = vectors(3, 2, n, 3, 32, 64)
+    hard, tau = torch.ones(2, 3, dtype=torch.bool, device='cuda'), torch.linspace(-.5, .5, 3).cuda()
+    x = [sq.cuda(), sk.cuda(), v.cuda(), dev(q), dev(k), hard, tau]
+    original, _ = api['fwd'].forward_hard(*x)
+    x[2][:, 127:] = 20
+    changed, _ = api['fwd'].forward_hard(*x)
+    assert torch.equal(original[:, :127], changed[:, :127])
+
+
+# ---- backward --------------------------------------------------------------------------------------
+@pytest.mark.parametrize('pattern', PATTERNS)
+def test_backward_matches_golden(api, pattern):
+    g = golden(f'pattern_{pattern}.npz')
+    x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
+         dev(g['iq256']), dev(g['ik256']), dev(g['hard'])]
+    dout = dev(g['dout'], torch.bfloat16)
+    _, norm, state = api['fwd'].forward_hard(*x, dev(g['tau']), save_state=True, ctas=1)
+    got = api['bwd'].backward_hard(*x[:3], dout, *x[3:], norm, state, ctas=1)
+    assert got[0].dtype == torch.float32 and got[1].dtype == torch.bfloat16 and got[2].dtype == torch.bfloat16
+    for a, name in zip(got[:3], ('dsq', 'dsk', 'dv')):
+        assert torch.isfinite(a).all()
+        assert_vectors(a, g[name])
+        assert not a.masked_select(~x[5][:, None, :, None]).count_nonzero()  # soft rows: exact zeros
+    torch.testing.assert_close(got[3].double().cpu(), torch.from_numpy(g['dtau']), atol=.003, rtol=.01)
+    # label-only route (no rectangle) and any grid size give the same bits
+    for ctas in (0, 3):
+        again = api['bwd'].backward_hard(*x[:3], dout, *x[3:], norm, dict(boundary=None, log_weights=state['log_weights']),
+                                         ctas=ctas)
+        assert all(torch.equal(a, b) for a, b in zip(got, again))
+    recomputed = api['bwd'].backward_hard_recompute(*x[:3], dout, *x[3:], dev(g['tau']))
+    assert all(torch.equal(a, recomputed[key]) for a, key in zip(got, ('sq_vec', 'sk_vec', 'v', 'rtau')))
+
+
+def test_backward_tau_long_chain(api):
+    g = golden('chain_equal.npz')
+    x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
+         dev(g['iq']), dev(g['ik']), torch.ones(1, 1, dtype=torch.bool, device='cuda')]
+    dout = dev(g['dout'], torch.bfloat16)
+    for index, tau in enumerate(g['taus']):
+        t = torch.tensor([tau], dtype=torch.float32, device='cuda')
+        _, norm, state = api['fwd'].forward_hard(*x, t, save_state=True)
+        got = api['bwd'].backward_hard(*x[:3], dout, *x[3:], norm, state)
+        torch.testing.assert_close(got[3].double().cpu(), torch.from_numpy(g[f'dtau{index}']), atol=.003, rtol=.01)
+        assert_vectors(got[0], g[f'dsq{index}'])
+
+
+def test_backward_all_soft_is_zero(api):
+    g = golden('pattern_random.npz')
+    x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
+         dev(g['iq256']), dev(g['ik256']), torch.zeros(2, 3, dtype=torch.bool, device='cuda')]
+    _, norm, state = api['fwd'].forward_hard(*x, dev(g['tau']), save_state=True)
+    got = api['bwd'].backward_hard(*x[:3], dev(g['dout'], torch.bfloat16), *x[3:], norm, state)
+    assert all(not t.count_nonzero() for t in got)
+
+
+# ---- the CPU-runnable reference configuration --------------------------------------------------------
+def test_config1_reference_case(api, oracle):
+    g = golden('config1.npz')
+    bf = lambda a: dev(a, torch.bfloat16)
+    # labels: the kernel's pinned accumulation order against the CPU restatement, bit for bit, and
+    # against the reference's fp32 arg-max where the operands are bf16-exact
+    q, k, eq, ek = bf(g['q']), bf(g['k']), bf(g['eq']), bf(g['ek'])
+    f = lambda t: t.float().cpu().numpy()
+    iq, ik = api['cu'].labels(q, eq), api['cu'].labels(k, ek)
+    assert np.array_equal(iq.cpu().numpy(), oracle.labels(f(q), f(eq)))
+    assert np.array_equal(ik.cpu().numpy(), oracle.labels(f(k), f(ek)))
+    # hard path on the reference's own labels
+    hard = torch.ones(1, 2, dtype=torch.bool, device='cuda')
+    x = [bf(g['sq']), bf(g['sk']), bf(g['v']), dev(g['iq']), dev(g['ik']), hard]
+    out, norm, state = api['fwd'].forward_hard(*x, dev(g['tau']), save_state=True)
+    lengths = oracle.lengths(g['iq'][0, 0], g['ik'][0, 0])
+    c = 3
+    row = 32 * c + 31
+    assert np.array_equal(np.arange(row + 1) - state['boundary'][0, 0, c, :row + 1].cpu().numpy(), lengths[row, :row + 1])
+    # fp32 fixture inputs are rounded to bf16 for the kernel: compare with the oracle on the rounded values
+    expected, lse2 = oracle.forward(f(x[0]), f(x[1]), f(x[2]), g['iq'], g['ik'], np.ones((1, 2), bool), g['tau'])
+    assert_vectors(out, expected)
+    torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
+    torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(g['lse2']), atol=2e-5, rtol=2e-6)
+    assert_vectors(out, g['out'], atol=.02, rtol=.05, l2=.02)  # vs the fp32-input reference run
+
+
+def test_labels_bit_exact_and_ties(api, oracle):
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(2, 300, 3, 64, generator=g).bfloat16()
+    e = torch.nn.functional.silu(torch.randn(3, 512, 64, generator=g)).bfloat16()
+    got = api['cu'].labels(x.cuda(), e.cuda())
+    assert np.array_equal(got.cpu().numpy(), oracle.labels(x.float().numpy(), e.float().numpy()))
+    reference = torch.argmax(torch.einsum('bnhd,hvd->bnhv', x.float(), e.float()), -1).transpose(1, 2)
+    assert (got.cpu() != reference).float().mean() < 1e-3  # near-ties only
+    zero = api['cu'].labels(torch.zeros_like(x).cuda(), e.cuda())  # all ties: the lowest index wins
+    assert not zero.count_nonzero()
+
+
+# ---- symbol streams: single longest earlier match -----------------------------------------------------
+def symbol_streams(batch, n, vocab, seed):
+    rng = np.random.default_rng(seed)
+    out = np.empty((batch, n), np.int32)
+    for b in range(batch):
+        s = list(rng.integers(0, vocab, 512))
+        while len(s) < n:
+            length = int(rng.integers(16, 513))
+            if rng.random() < .5:
+                start = int(rng.integers(0, len(s)))
+                for t in range(length):  # may run into what it is writing, like a real self-copy
+                    s.append(s[start + t])
+            else:
+                s.extend(rng.integers(0, vocab, length))
+        out[b] = s[:n]
+    return out
+
+
+def test_longest_match_symbol_streams(api, oracle):
+    streams = symbol_streams(4, 4096, 256, 0)
+    end, length, nxt = api['cu'].longest_match(dev(streams))
+    for b in range(4):
+        e, l, x = oracle.longest(streams[b])
+        assert np.array_equal(end[b].cpu().numpy(), e)
+        assert np.array_equal(length[b].cpu().numpy(), l)
+        assert np.array_equal(nxt[b].cpu().numpy(), x)
+
+
+# ---- validation ------------------------------------------------------------------------------------------
+def test_validation_errors(api):
+    g = golden('pattern_random.npz')
+    x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
+         dev(g['iq256']), dev(g['ik256']), dev(g['hard']), dev(g['tau'])]
+    out, norm, state = api['fwd'].forward_hard(*x, save_state=True)
+    with pytest.raises(RuntimeError, match='too short'):
+        api['fwd'].hard_readout(*x[:6], state['boundary'], state['log_weights'][:, :128].contiguous())
+    with pytest.raises(RuntimeError, match='boundary'):
+        api['fwd'].hard_readout(*x[:6], state['boundary'].float(), state['log_weights'])
+    with pytest.raises(RuntimeError, match='token-level'):
+        api['fwd'].forward_hard(*x[:5], x[5][:, :, None].expand(2, 3, 256), x[6])
+    with pytest.raises(RuntimeError, match='CTA'):
+        api['summary'].summarize_hard(x[3], x[4], x[5], ctas=-1)
+    for bad in (x[3].long(), x[3].cpu(), x[3][:, :, :255], x[3][:, :, ::2]):
+        with pytest.raises(RuntimeError):
+            api['summary'].summarize_hard(bad, x[4], x[5])
+    with pytest.raises(RuntimeError, match='sequence hard flags'):
+        api['bwd'].backward_hard(*x[:3], x[2], *x[3:5], x[5][:, :, None].expand_as(x[3]).contiguous(), norm, state)
+    with pytest.raises(RuntimeError, match='head'):
+        api['summary'].hard_chunk_scan(state['summary'], heads=5)
