@@ -39,7 +39,7 @@ int check_dims(int r, int dv) {
 extern "C" {
 
 const char* dism_last_error(void) { return last_error; }
-int dism_abi_version(void) { return 1; }
+int dism_abi_version(void) { return 2; }
 
 int dism_labels(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t* labels, void* stream) {
@@ -81,19 +81,29 @@ int dism_hard_log_weights(const float* tau, int heads, int n, float* lut, void* 
 
 int dism_hard_readout(const void* sq, const void* sk, const void* v, const int32_t* iq, const int32_t* ik,
                       const uint8_t* hard, const int32_t* boundary, const float* lut, int lut_stride, int batch,
-                      int n, int heads, int r, int dv, int ctas, void* out, float* lse2, void* stream) {
+                      int n, int heads, int r, int dv, int ctas, void* out, float* lse2, void* workspace,
+                      size_t workspace_bytes, void* stream) {
     if (int status = check_shape(batch, heads, n)) return status;
     if (int status = check_dims(r, dv)) return status;
     if (!sq || !sk || !v || !iq || !ik || !hard || !lut || !out || !lse2) return fail(DISM_EINVAL, "null pointer");
     if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
     if (lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
-    if (!aligned(v, 8) || !aligned(out, 8)) return fail(DISM_EINVAL, "value and output tensors must be 8-byte aligned");
+    if (!aligned(sq, 16) || !aligned(sk, 16) || !aligned(v, 16) || !aligned(out, 16))
+        return fail(DISM_EINVAL, "vector tensors must be 16-byte aligned");
+    if (!workspace || workspace_bytes < dism::hard_forward_workspace_bytes(batch, heads, n) || !aligned(workspace, 256))
+        return fail(DISM_EINVAL, "workspace missing, too small or misaligned (see dism_hard_readout_workspace)");
     dism::HardShape shape{batch, heads, n, r, dv};
     using bf = __nv_bfloat16;
     return cuda_status(dism::launch_hard_forward(shape, static_cast<const bf*>(sq), static_cast<const bf*>(sk),
                                                  static_cast<const bf*>(v), iq, ik, hard, boundary, lut, lut_stride,
-                                                 ctas, static_cast<bf*>(out), lse2, static_cast<cudaStream_t>(stream)),
+                                                 ctas, static_cast<bf*>(out), lse2, workspace,
+                                                 static_cast<cudaStream_t>(stream)),
                        "hard_readout");
+}
+
+size_t dism_hard_readout_workspace(int batch, int heads, int n) {
+    if (batch <= 0 || heads <= 0 || n <= 0) return 0;
+    return dism::hard_forward_workspace_bytes(batch, heads, n);
 }
 
 size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride) {
@@ -113,10 +123,11 @@ int dism_hard_backward(const void* sq, const void* sk, const void* v, const void
         return fail(DISM_EINVAL, "null pointer");
     if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
     if (lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
-    if (workspace_bytes < dism::hard_backward_workspace_bytes(batch, heads, n, lut_stride) || !aligned(workspace, 4))
+    if (workspace_bytes < dism::hard_backward_workspace_bytes(batch, heads, n, lut_stride) || !aligned(workspace, 256))
         return fail(DISM_EINVAL, "workspace too small or misaligned (see dism_hard_backward_workspace)");
-    if (!aligned(v, 8) || !aligned(dout, 8) || !aligned(dv_out, 8))
-        return fail(DISM_EINVAL, "value-shaped tensors must be 8-byte aligned");
+    if (!aligned(sq, 16) || !aligned(sk, 16) || !aligned(v, 16) || !aligned(dout, 16) || !aligned(dsq, 16) ||
+        !aligned(dsk, 16) || !aligned(dv_out, 16))
+        return fail(DISM_EINVAL, "vector tensors must be 16-byte aligned");
     dism::HardShape shape{batch, heads, n, r, dv};
     using bf = __nv_bfloat16;
     return cuda_status(dism::launch_hard_backward(shape, static_cast<const bf*>(sq), static_cast<const bf*>(sk),
@@ -126,11 +137,18 @@ int dism_hard_backward(const void* sq, const void* sk, const void* v, const void
                                                   static_cast<cudaStream_t>(stream)), "hard_backward");
 }
 
+size_t dism_longest_match_workspace(int batch, int n) {
+    if (batch <= 0 || n <= 0) return 0;
+    return dism::longest_match_workspace_bytes(batch, n);
+}
+
 int dism_longest_match(const int32_t* streams, int batch, int n, int32_t* end, int32_t* length, int32_t* next,
-                       void* stream) {
+                       void* workspace, size_t workspace_bytes, void* stream) {
     if (!streams || !end || !length || !next) return fail(DISM_EINVAL, "null pointer");
     if (batch <= 0 || n <= 0 || n % 8) return fail(DISM_EINVAL, "positive batch and a stream length divisible by 8 required");
-    return cuda_status(dism::launch_longest_match(streams, batch, n, end, length, next,
+    if (!workspace || workspace_bytes < dism::longest_match_workspace_bytes(batch, n) || !aligned(workspace, 256))
+        return fail(DISM_EINVAL, "workspace missing, too small or misaligned (see dism_longest_match_workspace)");
+    return cuda_status(dism::launch_longest_match(streams, batch, n, end, length, next, workspace,
                                                   static_cast<cudaStream_t>(stream)), "longest_match");
 }
 

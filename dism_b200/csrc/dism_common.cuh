@@ -1,4 +1,12 @@
 // Shared device helpers and launch-side declarations for the flash_dism hard path on sm_100a.
+//
+// How the hard kernels find their work.  A pair (query i, key j <= i) has non-zero weight only
+// when its labels are equal, so the kernels never visit the N^2/2 pairs.  A small prepass sorts
+// the positions of one side by (label bucket, position); the owner of a row then reads only the
+// bucket of its own label (about N/256 entries), keeps the entries with the same label on the
+// causal side, and gets its matching partners already in ascending order.  Eight lane groups of
+// a warp each own one row and work through their queued partners together, so the per-pair
+// arithmetic (run length, table lookup, two short dot products, one axpy) runs eight pairs wide.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -8,6 +16,10 @@ namespace dism {
 
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float LOG_ZERO = -1000000.f;  // LUT entry of length 0 (dism_v3/src/hard_forward.cu:15)
+constexpr int BUCKETS = 256;            // label buckets of the position index
+constexpr int OWN = 8;                  // rows per warp (one per group of four lanes)
+constexpr int WARPS = 8;                // warps per CTA
+constexpr int BLOCK_ROWS = WARPS * OWN;
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -15,117 +27,150 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 __device__ __forceinline__ float bf2f(__nv_bfloat16 x) { return __bfloat162float(x); }
-__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-// PER consecutive bf16 values (PER = 1, 2 or 4) as floats, with one vector load.
-template <int PER>
-__device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float (&out)[PER]) {
-    if constexpr (PER == 1) out[0] = bf2f(*p);
-    else if constexpr (PER == 2) {
-        float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
-        out[0] = f.x; out[1] = f.y;
-    } else {
-        static_assert(PER == 4, "1, 2 or 4 values per lane");
-        uint2 raw = *reinterpret_cast<const uint2*>(p);
-        float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-        float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-        out[0] = lo.x; out[1] = lo.y; out[2] = hi.x; out[3] = hi.y;
-    }
-}
-template <int PER>
-__device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const float (&in)[PER]) {
-    if constexpr (PER == 1) *p = __float2bfloat16_rn(in[0]);
-    else if constexpr (PER == 2) *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(in[0], in[1]);
-    else {
-        static_assert(PER == 4, "1, 2 or 4 values per lane");
-        __nv_bfloat162 lo = __floats2bfloat162_rn(in[0], in[1]), hi = __floats2bfloat162_rn(in[2], in[3]);
-        uint2 raw{*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi)};
-        *reinterpret_cast<uint2*>(p) = raw;
-    }
-}
-__device__ __forceinline__ float warp_sum(float x) {
+
+// COUNT consecutive bf16 values (a multiple of 4, 8 bytes aligned) as floats.
+template <int COUNT>
+__device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float (&out)[COUNT]) {
+    static_assert(COUNT % 4 == 0, "vector loads of 4 or 8 values");
+    if constexpr (COUNT % 8 == 0) {
 #pragma unroll
-    for (int s = 16; s; s >>= 1) x += __shfl_xor_sync(FULL, x, s);
+        for (int c = 0; c < COUNT / 8; ++c) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p) + c);
+            const unsigned word[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                out[c * 8 + 2 * e] = __uint_as_float(word[e] << 16);
+                out[c * 8 + 2 * e + 1] = __uint_as_float(word[e] & 0xffff0000u);
+            }
+        }
+    } else {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+        out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
+        out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
+    }
+}
+template <int COUNT>
+__device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const float (&in)[COUNT]) {
+    static_assert(COUNT % 4 == 0, "vector stores of 4 or 8 values");
+    unsigned word[COUNT / 2];
+#pragma unroll
+    for (int e = 0; e < COUNT / 2; ++e) {
+        __nv_bfloat162 pair = __floats2bfloat162_rn(in[2 * e], in[2 * e + 1]);
+        word[e] = *reinterpret_cast<unsigned*>(&pair);
+    }
+    if constexpr (COUNT % 8 == 0) {
+#pragma unroll
+        for (int c = 0; c < COUNT / 8; ++c)
+            reinterpret_cast<uint4*>(p)[c] = make_uint4(word[4 * c], word[4 * c + 1], word[4 * c + 2], word[4 * c + 3]);
+    } else {
+        *reinterpret_cast<uint2*>(p) = make_uint2(word[0], word[1]);
+    }
+}
+// Sum over the four lanes of a group.
+__device__ __forceinline__ float group_sum(float x) {
+    x += __shfl_xor_sync(FULL, x, 1);
+    x += __shfl_xor_sync(FULL, x, 2);
     return x;
 }
 
-// Number of consecutive label matches on the diagonal that ends at (i, j), given that (i, j)
-// itself matches.  The whole warp calls this with the same (i, j).  With a boundary rectangle
-// (int32 [(N-1)/32, N] of this batch/head, boundary[c][col] = col - L(32c+31, col)) the walk
-// stops at the 32-row strip edge and reads the rest; without one it walks 32 cells per step.
-__device__ __forceinline__ int match_length(const int* __restrict__ q, const int* __restrict__ k,
-                                            const int* __restrict__ boundary, int n, int i, int j, int lane) {
-    int length = 1, bi = i - 1, bj = j - 1;
-    if (boundary) {
-        const int inside = i & 31;  // rows i-1 .. i-inside share the strip of row i
-        bool ok = lane < inside && bj - lane >= 0 && __ldg(q + bi - lane) == __ldg(k + bj - lane);
-        unsigned mask = __ballot_sync(FULL, ok);
-        int run = __ffs(~mask) - 1;
-        length += run;
-        int col = bj - inside;
-        if (run == inside && col >= 0 && i >= 32)
-            length += col - __ldg(boundary + int64_t((i >> 5) - 1) * n + col);
-        return length;
-    }
-    while (bj >= 0) {
-        bool ok = bj - lane >= 0 && __ldg(q + bi - lane) == __ldg(k + bj - lane);
-        unsigned mask = __ballot_sync(FULL, ok);
-        if (mask != FULL) return length + __ffs(~mask) - 1;
-        length += 32;
-        bi -= 32;
-        bj -= 32;
-    }
-    return length;
+__device__ __forceinline__ int bucket_of(int label) {
+    unsigned x = unsigned(label);
+    x ^= x >> 16;
+    x ^= x >> 8;
+    return int(x & (BUCKETS - 1));
 }
 
-// One warp owns OWN consecutive positions of one (batch, head) and streams the other side's
-// labels in slabs of 1024 (32 per lane, kept in registers), comparing with a ballot per
-// (owned position, 32 streamed positions).  Proc::hits handles the set bits in ascending order,
-// so every owned position sees its matches in ascending streamed order whatever the grid size.
-// QUERY_MAJOR: owned = queries, streamed = keys s <= owner.  Otherwise owned = keys and
-// streamed = queries s >= owner.
-constexpr int OWN = 8;
-constexpr int SLAB = 1024;
+// Number of consecutive label matches on the diagonal that ends at (i, j), given that (i, j)
+// itself matches; one thread walks one diagonal.  With a boundary rectangle
+// (int32 [(N-1)/32, N] of this batch/head, boundary[c][col] = col - L(32c+31, col)) the walk ends
+// at the 32-row strip edge and reads the rest of the run from the rectangle.
+__device__ __forceinline__ int run_length(const int* __restrict__ q, const int* __restrict__ k,
+                                          const int* __restrict__ boundary, int n, int i, int j) {
+    int s = 1;
+    if (boundary) {
+        const int inside = i & 31;  // rows i-1 .. i-inside share the strip of row i
+        for (; s <= inside && j - s >= 0; ++s)
+            if (__ldg(q + i - s) != __ldg(k + j - s)) return s;
+        const int col = j - s;
+        if (s == inside + 1 && col >= 0 && i >= 32) s += col - __ldg(boundary + int64_t((i >> 5) - 1) * n + col);
+        return s;
+    }
+    while (j - s >= 0 && __ldg(q + i - s) == __ldg(k + j - s)) ++s;
+    return s;
+}
 
-template <bool QUERY_MAJOR, class Proc, class State>
-__device__ __forceinline__ void stream_matches(State* st, const int* __restrict__ own_labels,
-                                               const int* __restrict__ stream_labels, int n, int row0,
-                                               int lane) {
-    const int own = __ldg(own_labels + row0 + (lane & (OWN - 1)));
-    const int first = QUERY_MAJOR ? 0 : (row0 & ~(SLAB - 1));
-    const int last = QUERY_MAJOR ? row0 + OWN - 1 : n - 1;  // last streamed position of interest
-    for (int s0 = first; s0 <= last; s0 += SLAB) {
-        int reg[32];
-#pragma unroll
-        for (int t = 0; t < 32; ++t) {
-            int s = s0 + t * 32 + lane;
-            reg[t] = s < n ? __ldg(stream_labels + s) : 0;
+// Position index of one side of one (batch, head): `entries` holds (position, label) sorted by
+// (bucket, position); bucket b occupies [starts[b], starts[b+1]).
+struct SideIndex {
+    const int2* entries;
+    const int* starts;
+};
+
+// First entry of bucket range [lo, hi) whose position is >= bound (positions ascend).
+__device__ __forceinline__ int lower_bound_position(const int2* __restrict__ entries, int lo, int hi, int bound) {
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(&entries[mid].x) < bound) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+// Per-warp queue of the partners found in one round: up to 32 per owned row.
+struct PairQueue {
+    int position[OWN][32];
+    int length[OWN][32];
+};
+
+// One round of partner search for the warp's OWN rows.  Lane r < OWN carries the label of row r
+// and its cursor into the other side's index; each row reads its next 32 bucket entries, keeps
+// those with the same label, computes their run lengths (one lane per partner) and queues them
+// in ascending position.  Returns in lane r the number queued for row r.
+// QUERY_MAJOR: owned rows are queries i = row0 + r and partners are keys; otherwise owned rows are
+// keys j = row0 + r and partners are queries.
+template <bool QUERY_MAJOR>
+__device__ __forceinline__ int find_partners(PairQueue* queue, const int2* __restrict__ entries,
+                                             const int* __restrict__ iq, const int* __restrict__ ik,
+                                             const int* __restrict__ boundary, int n, int row0, int label,
+                                             int& cursor, int end, int lane) {
+    int queued = 0;
+#pragma unroll 1
+    for (int r = 0; r < OWN; ++r) {
+        const int from = __shfl_sync(FULL, cursor, r), to = __shfl_sync(FULL, end, r);
+        if (from >= to) continue;  // uniform
+        const int wanted = __shfl_sync(FULL, label, r);
+        const int at = from + lane;
+        int2 entry = make_int2(0, 0);
+        if (at < to) entry = __ldg(entries + at);
+        const bool hit = at < to && entry.y == wanted;
+        int length = 0;
+        if (hit) length = QUERY_MAJOR ? run_length(iq, ik, boundary, n, row0 + r, entry.x)
+                                      : run_length(iq, ik, boundary, n, entry.x, row0 + r);
+        const unsigned mask = __ballot_sync(FULL, hit);
+        if (hit) {
+            const int slot = __popc(mask & ((1u << lane) - 1u));
+            queue->position[r][slot] = entry.x;
+            queue->length[r][slot] = length;
         }
-        const bool interior = QUERY_MAJOR ? (s0 + SLAB - 1 <= row0) : (s0 >= row0 + OWN - 1 && s0 + SLAB <= n);
-        if (interior) {
-            for (int r = 0; r < OWN; ++r) {
-                const int label = __shfl_sync(FULL, own, r);
-#pragma unroll
-                for (int t = 0; t < 32; ++t) {
-                    unsigned m = __ballot_sync(FULL, reg[t] == label);
-                    if (m) Proc::hits(st, r, s0 + t * 32, m);
-                }
-            }
-        } else {
-            for (int r = 0; r < OWN; ++r) {
-                const int label = __shfl_sync(FULL, own, r);
-                const int rel = row0 + r - s0;  // owner position relative to the slab
-#pragma unroll
-                for (int t = 0; t < 32; ++t) {
-                    if (s0 + t * 32 >= n || (QUERY_MAJOR && t * 32 > rel + OWN - 1 - r)) break;
-                    const int d = rel - t * 32;  // owner relative to this 32-wide tile
-                    unsigned valid;
-                    if (QUERY_MAJOR) valid = d >= 31 ? FULL : (d < 0 ? 0u : (2u << d) - 1u);
-                    else valid = d <= 0 ? FULL : (d > 31 ? 0u : FULL << d);
-                    unsigned m = __ballot_sync(FULL, reg[t] == label) & valid;
-                    if (m) Proc::hits(st, r, s0 + t * 32, m);
-                }
-            }
+        if (lane == r) {
+            queued = __popc(mask);
+            cursor = from + 32;
         }
+    }
+    return queued;
+}
+
+// Causal range of the bucket of `label` for owner position `row` (binary search on positions).
+template <bool QUERY_MAJOR>
+__device__ __forceinline__ void partner_range(const SideIndex& index, int label, int row, int& cursor, int& end) {
+    const int bucket = bucket_of(label);
+    const int lo = __ldg(index.starts + bucket), hi = __ldg(index.starts + bucket + 1);
+    if (QUERY_MAJOR) {  // keys at positions <= row
+        cursor = lo;
+        end = lower_bound_position(index.entries, lo, hi, row + 1);
+    } else {  // queries at positions >= row
+        cursor = lower_bound_position(index.entries, lo, hi, row);
+        end = hi;
     }
 }
 
@@ -134,24 +179,34 @@ struct HardShape {
     int batch, heads, n, r, dv;
 };
 
+int device_sm_count();
 cudaError_t launch_labels(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int batch, int n, int heads,
                           int d, int vocab, int* labels, cudaStream_t stream);
 cudaError_t launch_hard_summary(const int* iq, const int* ik, const uint8_t* hard, int batch, int heads, int n,
                                 int ctas, int* summary, cudaStream_t stream);
 cudaError_t launch_hard_chunk(const int* summary, int* boundary, int batch_heads, int n, cudaStream_t stream);
+
+// Index workspace: per (batch, head) N entries of int2 plus BUCKETS+1 starts, for `sides` sides.
+size_t index_bytes(int batch_heads, int n, int sides);
+// Builds the index of `labels` ([BH, N]) into `workspace` (side 0 at the front, side 1 after it).
+cudaError_t launch_build_index(const int* labels, int batch_heads, int n, void* workspace, int side, int sides,
+                               cudaStream_t stream);
+SideIndex side_index(void* workspace, int batch_heads, int n, int side, int sides);
+
+size_t longest_match_workspace_bytes(int batch, int n);
 cudaError_t launch_longest_match(const int* streams, int batch, int n, int* end, int* length, int* next,
-                                 cudaStream_t stream);
+                                 void* workspace, cudaStream_t stream);
 cudaError_t launch_log_weights(const float* tau, int heads, int n, float* lut, cudaStream_t stream);
+size_t hard_forward_workspace_bytes(int batch, int heads, int n);
 cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,
                                 const __nv_bfloat16* v, const int* iq, const int* ik, const uint8_t* hard,
                                 const int* boundary, const float* lut, int lut_stride, int ctas,
-                                __nv_bfloat16* out, float* lse2, cudaStream_t stream);
+                                __nv_bfloat16* out, float* lse2, void* workspace, cudaStream_t stream);
 size_t hard_backward_workspace_bytes(int batch, int heads, int n, int lut_stride);
 cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,
                                  const __nv_bfloat16* v, const __nv_bfloat16* dout, const int* iq, const int* ik,
                                  const uint8_t* hard, const int* boundary, const float* lut, int lut_stride,
                                  const float* lse2, int ctas, float* dsq, __nv_bfloat16* dsk, __nv_bfloat16* dv,
                                  float* dtau, void* workspace, cudaStream_t stream);
-int device_sm_count();
 
 }  // namespace dism

@@ -4,10 +4,11 @@
 // Replaces, behind the C ABI, the reference's hard_dlog_weights_kernel, hard_backward_kernel and
 // hard_tau_reduce_kernel (dism_v3/src/hard_backward.cu:7-197; formulas in
 // dism_v3/docs/HARD_BACKWARD_QUADRATIC.md:60-97).  Where the reference runs one key-major kernel
-// and adds dSQ and four per-query moments across CTAs with FP32 atomics, this design runs the
-// matched-pair stream twice, once owned by queries and once owned by keys: every gradient row is
-// then accumulated by exactly one warp in a fixed order, with no atomics, no zero-filled
-// accumulators and bit-identical results for any grid size.
+// and adds dSQ and four per-query moments across CTAs with FP32 atomics, this design walks the
+// matched pairs twice, once owned by queries and once owned by keys: every gradient row is then
+// accumulated by exactly one lane group in ascending partner order, with no atomics, no
+// zero-filled accumulators and bit-identical results for any grid size.  Pair coefficients stay
+// in FP32 (the reference rounds them to BF16 to feed its tensor-core tiles).
 #include "dism_common.cuh"
 
 namespace dism {
@@ -28,216 +29,163 @@ __global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __rest
     out[int64_t(head) * stride + l] = g;
 }
 
-// ---- query-major pass ------------------------------------------------------------------------
-template <int DV>
-struct QueryWarp {
-    float dsq[OWN][32], sq[OWN][32], dout[OWN][DV];
-    float u[OWN], v[OWN], w[OWN], z[OWN], norm[OWN], center[OWN];
-    const int *iq, *ik, *boundary;
-    const float *lut, *dlut;
-    const __nv_bfloat16 *sk, *value;
-    int n, row0, stride_r, stride_v;
-};
-
-template <int R, int DV>
-struct QueryProc {
-    static __device__ __noinline__ void hits(QueryWarp<DV>* w, int r, int base, unsigned mask) {
-        constexpr int PER = DV / 32;
-        const int lane = threadIdx.x & 31, i = w->row0 + r;
-        float dsq = w->dsq[r][lane], u = w->u[r], v = w->v[r], ww = w->w[r], z = w->z[r];
-        const float a = w->sq[r][lane], norm = w->norm[r], center = w->center[r];
-        float d[PER];
-#pragma unroll
-        for (int c = 0; c < PER; ++c) d[c] = w->dout[r][lane * PER + c];
-        do {
-            const int j = base + __ffs(mask) - 1;
-            mask &= mask - 1;
-            const int length = match_length(w->iq, w->ik, w->boundary, w->n, i, j, lane);
-            const float p = ex2(__ldg(w->lut + length) - norm);
-            const float g = __ldg(w->dlut + length) - center;
-            const float b = lane < R ? bf2f(w->sk[int64_t(j) * w->stride_r + lane]) : 0.f;
-            float value[PER], partial = 0.f;
-            load_bf16<PER>(w->value + int64_t(j) * w->stride_v + lane * PER, value);
-#pragma unroll
-            for (int c = 0; c < PER; ++c) partial = fmaf(d[c], value[c], partial);
-            const float s = warp_sum(a * b), e = warp_sum(partial);
-            const float pse = p * s * e;
-            u += pse;
-            v = fmaf(p, g, v);
-            ww = fmaf(pse, g, ww);
-            z += p;
-            dsq = fmaf(p * e, b, dsq);
-        } while (mask);
-        w->dsq[r][lane] = dsq;
-        w->u[r] = u; w->v[r] = v; w->w[r] = ww; w->z[r] = z;
-    }
-};
-
 struct BackwardArgs {
     const __nv_bfloat16 *sq, *sk, *v, *dout;
     const int *iq, *ik, *boundary;
     const uint8_t* hard;
     const float *lut, *dlut, *lse2;
+    SideIndex keys, queries;
     float *dsq, *dtau_rows;
     __nv_bfloat16 *dsk, *dv;
     int batch, heads, n, lut_stride, tasks;
 };
 
-constexpr int BACKWARD_WARPS = 8;
-constexpr int BLOCK_ROWS = BACKWARD_WARPS * OWN;
-
+// ---- query-major pass: dSQ and the per-row tau term ----------------------------------------------
 template <int R, int DV>
-__global__ __launch_bounds__(BACKWARD_WARPS * 32) void hard_backward_query_kernel(const BackwardArgs a) {
-    constexpr int PER = DV / 32;
-    extern __shared__ __align__(16) unsigned char storage[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    auto* w = reinterpret_cast<QueryWarp<DV>*>(storage) + warp;
+__global__ __launch_bounds__(WARPS * 32) void hard_backward_query_kernel(const BackwardArgs a) {
+    constexpr int RPL = R / 4, VPL = DV / 4;
+    __shared__ PairQueue queues[WARPS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group = lane >> 2, part = lane & 3;
+    PairQueue* queue = queues + warp;
     const int blocks = a.n / BLOCK_ROWS, half = blocks / 2;
     for (int task = blockIdx.x; task < a.tasks; task += gridDim.x) {
         const int bh = task / half, pair = task % half, b = bh / a.heads, h = bh % a.heads;
         const bool active = a.hard[bh];
         const int64_t vec0 = int64_t(b) * a.n * a.heads + h;
+        const int* iq = a.iq + int64_t(bh) * a.n;
+        const int* ik = a.ik + int64_t(bh) * a.n;
+        const int* boundary = a.boundary ? a.boundary + int64_t(bh) * ((a.n - 1) / 32) * a.n : nullptr;
+        const float* lut = a.lut + int64_t(h) * a.lut_stride;
         const float* dlut = a.dlut + int64_t(h) * a.lut_stride;
+        const SideIndex keys{a.keys.entries + int64_t(bh) * a.n, a.keys.starts + int64_t(bh) * (BUCKETS + 1)};
         for (int side = 0; side < 2; ++side) {
             const int row0 = (side ? blocks - 1 - pair : pair) * BLOCK_ROWS + warp * OWN;
-            if (active) {
-                __syncwarp();
-                if (lane == 0) {
-                    w->iq = a.iq + int64_t(bh) * a.n;
-                    w->ik = a.ik + int64_t(bh) * a.n;
-                    w->boundary = a.boundary ? a.boundary + int64_t(bh) * ((a.n - 1) / 32) * a.n : nullptr;
-                    w->lut = a.lut + int64_t(h) * a.lut_stride;
-                    w->dlut = dlut;
-                    w->sk = a.sk + vec0 * R;
-                    w->value = a.v + vec0 * DV;
-                    w->n = a.n; w->row0 = row0; w->stride_r = a.heads * R; w->stride_v = a.heads * DV;
-                }
-                for (int r = 0; r < OWN; ++r) {
-                    const int64_t row = vec0 + int64_t(row0 + r) * a.heads;
-                    float d[PER];
-                    load_bf16<PER>(a.dout + row * DV + lane * PER, d);
+            const int row = row0 + group;
+            float dsq[RPL], term = 0.f;
 #pragma unroll
-                    for (int c = 0; c < PER; ++c) w->dout[r][lane * PER + c] = d[c];
-                    w->sq[r][lane] = lane < R ? bf2f(a.sq[row * R + lane]) : 0.f;
-                    w->dsq[r][lane] = 0.f;
-                    if (lane == 0) {
-                        w->u[r] = w->v[r] = w->w[r] = w->z[r] = 0.f;
-                        w->norm[r] = a.lse2[int64_t(bh) * a.n + row0 + r];
-                        w->center[r] = dlut[row0 + r + 1];
+            for (int c = 0; c < RPL; ++c) dsq[c] = 0.f;
+            if (active) {
+                float query[RPL], derivative[VPL];
+                load_bf16<RPL>(a.sq + (vec0 + int64_t(row) * a.heads) * R + part * RPL, query);
+                load_bf16<VPL>(a.dout + (vec0 + int64_t(row) * a.heads) * DV + part * VPL, derivative);
+                const float norm = __ldg(a.lse2 + int64_t(bh) * a.n + row), center = __ldg(dlut + row + 1);
+                float u = 0.f, v = 0.f, w = 0.f, z = 0.f;
+                const int label = __ldg(iq + row0 + (lane & (OWN - 1)));
+                int cursor, end;
+                partner_range<true>(keys, label, row0 + (lane & (OWN - 1)), cursor, end);
+                while (__ballot_sync(FULL, lane < OWN && cursor < end)) {
+                    __syncwarp();
+                    const int queued = find_partners<true>(queue, keys.entries, iq, ik, boundary, a.n, row0, label,
+                                                           cursor, end, lane);
+                    __syncwarp();
+                    const int mine = __shfl_sync(FULL, queued, group);
+                    const int rounds = __reduce_max_sync(FULL, mine);
+                    for (int it = 0; it < rounds; ++it) {
+                        const bool live = it < mine;
+                        float key[RPL], partial_s = 0.f, partial_e = 0.f, p = 0.f, g = 0.f;
+                        if (live) {
+                            const int j = queue->position[group][it], length = queue->length[group][it];
+                            p = ex2(__ldg(lut + length) - norm);
+                            g = __ldg(dlut + length) - center;
+                            load_bf16<RPL>(a.sk + (vec0 + int64_t(j) * a.heads) * R + part * RPL, key);
+                            float value[VPL];
+                            load_bf16<VPL>(a.v + (vec0 + int64_t(j) * a.heads) * DV + part * VPL, value);
+#pragma unroll
+                            for (int c = 0; c < RPL; ++c) partial_s = fmaf(query[c], key[c], partial_s);
+#pragma unroll
+                            for (int c = 0; c < VPL; ++c) partial_e = fmaf(derivative[c], value[c], partial_e);
+                        }
+                        const float s = group_sum(partial_s), e = group_sum(partial_e);
+                        if (live) {
+                            const float pse = p * s * e, pe = p * e;
+                            u += pse;
+                            v = fmaf(p, g, v);
+                            w = fmaf(pse, g, w);
+                            z += p;
+#pragma unroll
+                            for (int c = 0; c < RPL; ++c) dsq[c] = fmaf(pe, key[c], dsq[c]);
+                        }
                     }
                 }
-                __syncwarp();
-                stream_matches<true, QueryProc<R, DV>>(w, a.iq + int64_t(bh) * a.n, a.ik + int64_t(bh) * a.n,
-                                                       a.n, row0, lane);
-                __syncwarp();
+                // Centred four-moment form: the fallback has unit weight and zero derivative.
+                const float fallback = ex2(-norm), inverse = __fdividef(1.f, z + fallback);
+                const float mean = fmaf(-fallback, center, v) * inverse;
+                term = fmaf(-u, mean, w) * inverse;
             }
-            for (int r = 0; r < OWN; ++r) {
-                const int i = row0 + r;
-                if (lane < R) a.dsq[(vec0 + int64_t(i) * a.heads) * R + lane] = active ? w->dsq[r][lane] : 0.f;
-                if (lane == 0) {
-                    float term = 0.f;
-                    if (active) {
-                        // Centred four-moment form: the fallback has unit weight and zero derivative.
-                        const float fallback = ex2(-w->norm[r]);
-                        const float inverse = __fdividef(1.f, w->z[r] + fallback);
-                        const float mean = fmaf(-fallback, w->center[r], w->v[r]) * inverse;
-                        term = fmaf(-w->u[r], mean, w->w[r]) * inverse;
-                    }
-                    a.dtau_rows[int64_t(bh) * a.n + i] = term;
-                }
-            }
+            float* out = a.dsq + (vec0 + int64_t(row) * a.heads) * R + part * RPL;
+#pragma unroll
+            for (int c = 0; c < RPL; c += 4) *reinterpret_cast<float4*>(out + c) = make_float4(dsq[c], dsq[c + 1], dsq[c + 2], dsq[c + 3]);
+            if (part == 0) a.dtau_rows[int64_t(bh) * a.n + row] = term;
         }
     }
 }
 
-// ---- key-major pass ----------------------------------------------------------------------------
-template <int DV>
-struct KeyWarp {
-    float dv[OWN][DV], value[OWN][DV], dsk[OWN][32], sk[OWN][32];
-    const int *iq, *ik, *boundary;
-    const float *lut, *lse2;
-    const __nv_bfloat16 *sq, *dout;
-    int n, row0, stride_r, stride_v;
-};
-
+// ---- key-major pass: dV and dSK ---------------------------------------------------------------------
 template <int R, int DV>
-struct KeyProc {
-    static __device__ __noinline__ void hits(KeyWarp<DV>* w, int r, int base, unsigned mask) {
-        constexpr int PER = DV / 32;
-        const int lane = threadIdx.x & 31, j = w->row0 + r;
-        float dsk = w->dsk[r][lane], dv[PER], value[PER];
-        const float b = w->sk[r][lane];
-#pragma unroll
-        for (int c = 0; c < PER; ++c) { dv[c] = w->dv[r][lane * PER + c]; value[c] = w->value[r][lane * PER + c]; }
-        do {
-            const int i = base + __ffs(mask) - 1;
-            mask &= mask - 1;
-            const int length = match_length(w->iq, w->ik, w->boundary, w->n, i, j, lane);
-            const float p = ex2(__ldg(w->lut + length) - __ldg(w->lse2 + i));
-            const float a = lane < R ? bf2f(w->sq[int64_t(i) * w->stride_r + lane]) : 0.f;
-            float d[PER], partial = 0.f;
-            load_bf16<PER>(w->dout + int64_t(i) * w->stride_v + lane * PER, d);
-#pragma unroll
-            for (int c = 0; c < PER; ++c) partial = fmaf(d[c], value[c], partial);
-            const float s = warp_sum(a * b), e = warp_sum(partial);
-            const float ps = p * s, pe = p * e;
-#pragma unroll
-            for (int c = 0; c < PER; ++c) dv[c] = fmaf(ps, d[c], dv[c]);
-            dsk = fmaf(pe, a, dsk);
-        } while (mask);
-        w->dsk[r][lane] = dsk;
-#pragma unroll
-        for (int c = 0; c < PER; ++c) w->dv[r][lane * PER + c] = dv[c];
-    }
-};
-
-template <int R, int DV>
-__global__ __launch_bounds__(BACKWARD_WARPS * 32) void hard_backward_key_kernel(const BackwardArgs a) {
-    constexpr int PER = DV / 32;
-    extern __shared__ __align__(16) unsigned char storage[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    auto* w = reinterpret_cast<KeyWarp<DV>*>(storage) + warp;
+__global__ __launch_bounds__(WARPS * 32) void hard_backward_key_kernel(const BackwardArgs a) {
+    constexpr int RPL = R / 4, VPL = DV / 4;
+    __shared__ PairQueue queues[WARPS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group = lane >> 2, part = lane & 3;
+    PairQueue* queue = queues + warp;
     const int blocks = a.n / BLOCK_ROWS, half = blocks / 2;
     for (int task = blockIdx.x; task < a.tasks; task += gridDim.x) {
         const int bh = task / half, pair = task % half, b = bh / a.heads, h = bh % a.heads;
         const bool active = a.hard[bh];
         const int64_t vec0 = int64_t(b) * a.n * a.heads + h;
+        const int* iq = a.iq + int64_t(bh) * a.n;
+        const int* ik = a.ik + int64_t(bh) * a.n;
+        const int* boundary = a.boundary ? a.boundary + int64_t(bh) * ((a.n - 1) / 32) * a.n : nullptr;
+        const float* lut = a.lut + int64_t(h) * a.lut_stride;
+        const float* lse2 = a.lse2 + int64_t(bh) * a.n;
+        const SideIndex queries{a.queries.entries + int64_t(bh) * a.n, a.queries.starts + int64_t(bh) * (BUCKETS + 1)};
         for (int side = 0; side < 2; ++side) {
             const int row0 = (side ? blocks - 1 - pair : pair) * BLOCK_ROWS + warp * OWN;
+            const int row = row0 + group;
+            float dv[VPL], dsk[RPL];
+#pragma unroll
+            for (int c = 0; c < VPL; ++c) dv[c] = 0.f;
+#pragma unroll
+            for (int c = 0; c < RPL; ++c) dsk[c] = 0.f;
             if (active) {
-                __syncwarp();
-                if (lane == 0) {
-                    w->iq = a.iq + int64_t(bh) * a.n;
-                    w->ik = a.ik + int64_t(bh) * a.n;
-                    w->boundary = a.boundary ? a.boundary + int64_t(bh) * ((a.n - 1) / 32) * a.n : nullptr;
-                    w->lut = a.lut + int64_t(h) * a.lut_stride;
-                    w->lse2 = a.lse2 + int64_t(bh) * a.n;
-                    w->sq = a.sq + vec0 * R;
-                    w->dout = a.dout + vec0 * DV;
-                    w->n = a.n; w->row0 = row0; w->stride_r = a.heads * R; w->stride_v = a.heads * DV;
-                }
-                for (int r = 0; r < OWN; ++r) {
-                    const int64_t row = vec0 + int64_t(row0 + r) * a.heads;
-                    float value[PER];
-                    load_bf16<PER>(a.v + row * DV + lane * PER, value);
+                float key[RPL], value[VPL];
+                load_bf16<RPL>(a.sk + (vec0 + int64_t(row) * a.heads) * R + part * RPL, key);
+                load_bf16<VPL>(a.v + (vec0 + int64_t(row) * a.heads) * DV + part * VPL, value);
+                const int label = __ldg(ik + row0 + (lane & (OWN - 1)));
+                int cursor, end;
+                partner_range<false>(queries, label, row0 + (lane & (OWN - 1)), cursor, end);
+                while (__ballot_sync(FULL, lane < OWN && cursor < end)) {
+                    __syncwarp();
+                    const int queued = find_partners<false>(queue, queries.entries, iq, ik, boundary, a.n, row0,
+                                                            label, cursor, end, lane);
+                    __syncwarp();
+                    const int mine = __shfl_sync(FULL, queued, group);
+                    const int rounds = __reduce_max_sync(FULL, mine);
+                    for (int it = 0; it < rounds; ++it) {
+                        const bool live = it < mine;
+                        float query[RPL], derivative[VPL], partial_s = 0.f, partial_e = 0.f, p = 0.f;
+                        if (live) {
+                            const int i = queue->position[group][it];
+                            p = ex2(__ldg(lut + queue->length[group][it]) - __ldg(lse2 + i));
+                            load_bf16<RPL>(a.sq + (vec0 + int64_t(i) * a.heads) * R + part * RPL, query);
+                            load_bf16<VPL>(a.dout + (vec0 + int64_t(i) * a.heads) * DV + part * VPL, derivative);
 #pragma unroll
-                    for (int c = 0; c < PER; ++c) { w->value[r][lane * PER + c] = value[c]; w->dv[r][lane * PER + c] = 0.f; }
-                    w->sk[r][lane] = lane < R ? bf2f(a.sk[row * R + lane]) : 0.f;
-                    w->dsk[r][lane] = 0.f;
-                }
-                __syncwarp();
-                stream_matches<false, KeyProc<R, DV>>(w, a.ik + int64_t(bh) * a.n, a.iq + int64_t(bh) * a.n,
-                                                      a.n, row0, lane);
-                __syncwarp();
-            }
-            for (int r = 0; r < OWN; ++r) {
-                const int64_t row = vec0 + int64_t(row0 + r) * a.heads;
-                float result[PER];
+                            for (int c = 0; c < RPL; ++c) partial_s = fmaf(query[c], key[c], partial_s);
 #pragma unroll
-                for (int c = 0; c < PER; ++c) result[c] = active ? w->dv[r][lane * PER + c] : 0.f;
-                store_bf16<PER>(a.dv + row * DV + lane * PER, result);
-                if (lane < R) a.dsk[row * R + lane] = __float2bfloat16_rn(active ? w->dsk[r][lane] : 0.f);
+                            for (int c = 0; c < VPL; ++c) partial_e = fmaf(derivative[c], value[c], partial_e);
+                        }
+                        const float s = group_sum(partial_s), e = group_sum(partial_e);
+                        if (live) {
+                            const float ps = p * s, pe = p * e;
+#pragma unroll
+                            for (int c = 0; c < VPL; ++c) dv[c] = fmaf(ps, derivative[c], dv[c]);
+#pragma unroll
+                            for (int c = 0; c < RPL; ++c) dsk[c] = fmaf(pe, query[c], dsk[c]);
+                        }
+                    }
+                }
             }
+            store_bf16<VPL>(a.dv + (vec0 + int64_t(row) * a.heads) * DV + part * VPL, dv);
+            store_bf16<RPL>(a.dsk + (vec0 + int64_t(row) * a.heads) * R + part * RPL, dsk);
         }
     }
 }
@@ -259,30 +207,26 @@ __global__ void tau_reduce_kernel(const float* __restrict__ rows, float* __restr
     if (threadIdx.x == 0) dtau[head] = partial[0];
 }
 
-// Workspace: the dlog table [H, lut_stride] followed by the per-row tau terms [B, H, N], FP32.
+// Workspace: both position indices, then the dlog table [H, lut_stride] and the per-row tau terms
+// [B, H, N] in FP32.
 size_t hard_backward_workspace_bytes(int batch, int heads, int n, int lut_stride) {
-    return sizeof(float) * (size_t(heads) * lut_stride + size_t(batch) * heads * n);
+    return index_bytes(batch * heads, n, 2) + sizeof(float) * (size_t(heads) * lut_stride + size_t(batch) * heads * n);
 }
 
 template <int R, int DV>
 static cudaError_t launch_backward_variant(const BackwardArgs& args, int ctas, cudaStream_t stream) {
     auto query = hard_backward_query_kernel<R, DV>;
     auto key = hard_backward_key_kernel<R, DV>;
-    const int query_shared = sizeof(QueryWarp<DV>) * BACKWARD_WARPS, key_shared = sizeof(KeyWarp<DV>) * BACKWARD_WARPS;
-    cudaError_t status = cudaFuncSetAttribute(query, cudaFuncAttributeMaxDynamicSharedMemorySize, query_shared);
-    if (status != cudaSuccess) return status;
-    status = cudaFuncSetAttribute(key, cudaFuncAttributeMaxDynamicSharedMemorySize, key_shared);
-    if (status != cudaSuccess) return status;
     int resident_q = 1, resident_k = 1;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_q, query, BACKWARD_WARPS * 32, query_shared);
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_k, key, BACKWARD_WARPS * 32, key_shared);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_q, query, WARPS * 32, 0);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_k, key, WARPS * 32, 0);
     const int sms = device_sm_count();
     int grid_q = ctas ? ctas : sms * (resident_q > 0 ? resident_q : 1);
     int grid_k = ctas ? ctas : sms * (resident_k > 0 ? resident_k : 1);
     if (grid_q > args.tasks) grid_q = args.tasks;
     if (grid_k > args.tasks) grid_k = args.tasks;
-    query<<<grid_q, BACKWARD_WARPS * 32, query_shared, stream>>>(args);
-    key<<<grid_k, BACKWARD_WARPS * 32, key_shared, stream>>>(args);
+    query<<<grid_q, WARPS * 32, 0, stream>>>(args);
+    key<<<grid_k, WARPS * 32, 0, stream>>>(args);
     return cudaGetLastError();
 }
 
@@ -291,13 +235,19 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
                                  const uint8_t* hard, const int* boundary, const float* lut, int lut_stride,
                                  const float* lse2, int ctas, float* dsq, __nv_bfloat16* dsk, __nv_bfloat16* dv,
                                  float* dtau, void* workspace, cudaStream_t stream) {
-    float* dlut = static_cast<float*>(workspace);
+    const int batch_heads = shape.batch * shape.heads;
+    cudaError_t status = launch_build_index(ik, batch_heads, shape.n, workspace, 0, 2, stream);
+    if (status != cudaSuccess) return status;
+    status = launch_build_index(iq, batch_heads, shape.n, workspace, 1, 2, stream);
+    if (status != cudaSuccess) return status;
+    float* dlut = reinterpret_cast<float*>(static_cast<char*>(workspace) + index_bytes(batch_heads, shape.n, 2));
     float* rows = dlut + size_t(shape.heads) * lut_stride;
     dlog_weights_kernel<<<dim3((lut_stride + 255) / 256, shape.heads), 256, 0, stream>>>(lut, dlut, lut_stride);
-    BackwardArgs args{sq, sk, v, dout, iq, ik, boundary, hard, lut, dlut, lse2, dsq, rows, dsk, dv,
-                      shape.batch, shape.heads, shape.n, lut_stride,
-                      shape.batch * shape.heads * (shape.n / BLOCK_ROWS / 2)};
-    cudaError_t status = cudaErrorInvalidValue;
+    BackwardArgs args{sq, sk, v, dout, iq, ik, boundary, hard, lut, dlut, lse2,
+                      side_index(workspace, batch_heads, shape.n, 0, 2), side_index(workspace, batch_heads, shape.n, 1, 2),
+                      dsq, rows, dsk, dv, shape.batch, shape.heads, shape.n, lut_stride,
+                      batch_heads * (shape.n / BLOCK_ROWS / 2)};
+    status = cudaErrorInvalidValue;
 #define DISM_CASE(RR, VV) \
     if (shape.r == RR && shape.dv == VV) status = launch_backward_variant<RR, VV>(args, ctas, stream);
     DISM_CASE(16, 32) DISM_CASE(16, 64) DISM_CASE(16, 128)

@@ -77,60 +77,54 @@ cudaError_t launch_hard_chunk(const int* summary, int* boundary, int batch_heads
 }
 
 // ---- single longest earlier match (symbol streams, iq = ik = s) ---------------------------------
-struct LongestWarp {
-    int best[OWN], arg[OWN];
-    const int* s;
-    int n, row0;
-};
-
-struct LongestProc {
-    static __device__ __noinline__ void hits(LongestWarp* w, int r, int base, unsigned mask) {
-        const int lane = threadIdx.x & 31, i = w->row0 + r;
-        int best = w->best[r], arg = w->arg[r];
-        do {
-            const int j = base + __ffs(mask) - 1;
-            mask &= mask - 1;
-            if (j == i) continue;  // the diagonal always matches itself
-            const int length = match_length(w->s, w->s, nullptr, w->n, i, j, lane);
-            if (length >= best) { best = length; arg = j; }
-        } while (mask);
-        w->best[r] = best;
-        w->arg[r] = arg;
-    }
-};
-
-__global__ __launch_bounds__(256) void longest_match_kernel(const int* __restrict__ streams, int batch, int n,
-                                                             int* __restrict__ end, int* __restrict__ length,
-                                                             int* __restrict__ next) {
-    __shared__ LongestWarp state[8];
+// Each lane group is not needed here: lane r < OWN carries row r, the warp reads the row's bucket
+// of the stream's own position index and keeps the longest run, the most recent one on ties.
+__global__ __launch_bounds__(WARPS * 32) void longest_match_kernel(const int* __restrict__ streams, SideIndex index,
+                                                                    int batch, int n, int* __restrict__ end,
+                                                                    int* __restrict__ length, int* __restrict__ next) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    LongestWarp* w = state + warp;
     const int groups = n / OWN;
-    for (int64_t task = int64_t(blockIdx.x) * 8 + warp; task < int64_t(batch) * groups; task += int64_t(gridDim.x) * 8) {
+    for (int64_t task = int64_t(blockIdx.x) * WARPS + warp; task < int64_t(batch) * groups;
+         task += int64_t(gridDim.x) * WARPS) {
         const int b = int(task / groups), row0 = int(task % groups) * OWN;
         const int* s = streams + int64_t(b) * n;
-        __syncwarp();
-        if (lane < OWN) { w->best[lane] = 0; w->arg[lane] = -1; }
-        if (lane == 0) { w->s = s; w->n = n; w->row0 = row0; }
-        __syncwarp();
-        stream_matches<true, LongestProc>(w, s, s, n, row0, lane);
-        __syncwarp();
-        if (lane < OWN) {
-            const int i = row0 + lane, arg = w->arg[lane];
-            end[int64_t(b) * n + i] = arg;
-            length[int64_t(b) * n + i] = w->best[lane];
-            next[int64_t(b) * n + i] = arg >= 0 ? s[arg + 1] : -1;
+        const SideIndex mine{index.entries + int64_t(b) * n, index.starts + int64_t(b) * (BUCKETS + 1)};
+        for (int r = 0; r < OWN; ++r) {
+            const int i = row0 + r, label = __ldg(s + i);
+            int from, to;
+            partner_range<true>(mine, label, i - 1, from, to);  // keys strictly before i
+            long long best = -1;  // (run length << 32) | position: larger run first, then later position
+            for (int at = from + lane; at < to; at += 32) {
+                const int2 entry = __ldg(mine.entries + at);
+                if (entry.y == label) {
+                    const long long key = (static_cast<long long>(run_length(s, s, nullptr, n, i, entry.x)) << 32) | entry.x;
+                    best = max(best, key);
+                }
+            }
+#pragma unroll
+            for (int step = 16; step; step >>= 1) best = max(best, __shfl_xor_sync(FULL, best, step));
+            if (lane == 0) {
+                const int arg = best < 0 ? -1 : int(best & 0xffffffff);
+                end[int64_t(b) * n + i] = arg;
+                length[int64_t(b) * n + i] = best < 0 ? 0 : int(best >> 32);
+                next[int64_t(b) * n + i] = arg >= 0 ? s[arg + 1] : -1;
+            }
         }
     }
 }
 
+size_t longest_match_workspace_bytes(int batch, int n) { return index_bytes(batch, n, 1); }
+
 cudaError_t launch_longest_match(const int* streams, int batch, int n, int* end, int* length, int* next,
-                                 cudaStream_t stream) {
-    int64_t blocks = (int64_t(batch) * (n / OWN) + 7) / 8;
+                                 void* workspace, cudaStream_t stream) {
+    cudaError_t status = launch_build_index(streams, batch, n, workspace, 0, 1, stream);
+    if (status != cudaSuccess) return status;
+    int64_t blocks = (int64_t(batch) * (n / OWN) + WARPS - 1) / WARPS;
     const int64_t cap = int64_t(device_sm_count()) * 8;
     if (blocks > cap) blocks = cap;
     if (!blocks) return cudaSuccess;
-    longest_match_kernel<<<int(blocks), 256, 0, stream>>>(streams, batch, n, end, length, next);
+    longest_match_kernel<<<int(blocks), WARPS * 32, 0, stream>>>(streams, side_index(workspace, batch, n, 0, 1), batch,
+                                                                 n, end, length, next);
     return cudaGetLastError();
 }
 

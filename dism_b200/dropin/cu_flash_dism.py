@@ -168,9 +168,12 @@ def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
     with torch.cuda.device(sq.device):
         out = torch.empty((b, n, h, dv), dtype=torch.bfloat16, device=sq.device)
         norm = torch.empty((b, h, n), dtype=torch.float32, device=sq.device)
+        size = _abi.dism_hard_readout_workspace(b, h, n)
+        workspace = torch.empty((size,), dtype=torch.uint8, device=sq.device)
         _lib.check(_abi.dism_hard_readout(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), iq.data_ptr(), ik.data_ptr(),
                                           hard.data_ptr(), boundary_ptr, lut.data_ptr(), lut.size(1), b, n, h, r, dv,
-                                          int(ctas), out.data_ptr(), norm.data_ptr(), _stream(sq)))
+                                          int(ctas), out.data_ptr(), norm.data_ptr(), workspace.data_ptr(), size,
+                                          _stream(sq)))
     return out, norm
 
 
@@ -234,8 +237,10 @@ def longest_match(streams):
     b, n = streams.shape
     with torch.cuda.device(streams.device):
         end, length, nxt = (torch.empty_like(streams) for _ in range(3))
+        size = _abi.dism_longest_match_workspace(b, n)
+        workspace = torch.empty((size,), dtype=torch.uint8, device=streams.device)
         _lib.check(_abi.dism_longest_match(streams.data_ptr(), b, n, end.data_ptr(), length.data_ptr(),
-                                           nxt.data_ptr(), _stream(streams)))
+                                           nxt.data_ptr(), workspace.data_ptr(), size, _stream(streams)))
     return end, length, nxt
 
 

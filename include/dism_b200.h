@@ -47,15 +47,19 @@ int dism_hard_chunk(const int32_t *summary, int32_t *boundary, int batch_heads, 
  * Stands in for cu_flash_dism.hard_log_weights (dism_v3/src/host/hard_forward.cpp:11-23). */
 int dism_hard_log_weights(const float *tau, int heads, int n, float *lut, void *stream);
 
+/* Bytes of scratch dism_hard_readout needs for this shape (the key-side position index). */
+size_t dism_hard_readout_workspace(int batch, int heads, int n);
+
 /* Fused hard readout.  `boundary` is the rectangle of dism_hard_chunk or NULL (the kernel then
  * derives run lengths from the labels alone); lut has row stride lut_stride > N.
  * out bf16 [B,N,H,DV], lse2 float [B,H,N]; soft (batch, head) rows are written as zeros.
- * R in {16,32}, DV in {32,64,128}.
+ * R in {16,32}, DV in {32,64,128}; vectors 16-byte aligned.  `workspace` is caller-owned scratch of
+ * dism_hard_readout_workspace bytes, 256-byte aligned; its contents are dead after the call.
  * Stands in for cu_flash_dism.hard_readout (dism_v3/src/host/hard_forward.cpp:25-113). */
 int dism_hard_readout(const void *sq, const void *sk, const void *v, const int32_t *iq, const int32_t *ik,
                       const uint8_t *hard, const int32_t *boundary, const float *lut, int lut_stride,
                       int batch, int n, int heads, int r, int dv, int ctas, void *out, float *lse2,
-                      void *stream);
+                      void *workspace, size_t workspace_bytes, void *stream);
 
 /* Bytes of scratch dism_hard_backward needs for this shape. */
 size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride);
@@ -74,8 +78,9 @@ int dism_hard_backward(const void *sq, const void *sk, const void *v, const void
  * the same stream): for every i the most recent j < i with the longest run L(i,j), its length,
  * and the symbol after it (-1 when nothing matches).  The reference defines L(i,j)
  * (dism_v3/python/flash_dism/summary.py:8-16) but no single winner: this reduction is ours. */
+size_t dism_longest_match_workspace(int batch, int n);
 int dism_longest_match(const int32_t *streams, int batch, int n, int32_t *end, int32_t *length,
-                       int32_t *next, void *stream);
+                       int32_t *next, void *workspace, size_t workspace_bytes, void *stream);
 
 #ifdef __cplusplus
 }

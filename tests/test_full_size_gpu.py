@@ -55,5 +55,6 @@ def test_full_size_forward_and_backward(workload, oracle):
     assert torch.equal(flipped, -out) and torch.equal(flipped_norm, norm)
     doubled = w['bwd'].backward_hard(sq, sk, v, (w['dout'].float() * 2).bfloat16(), iq, ik, hard, norm,
                                      dict(boundary=None, log_weights=lut), ctas=100)
-    assert torch.equal(doubled[0], grads[0] * 2)  # scaling dO by a power of two scales dSQ exactly
-    assert torch.equal(doubled[2].float(), grads[2].float() * 2)
+    # scaling dO by a power of two scales dSQ and dV exactly, except where FP32 partial sums are subnormal
+    assert (doubled[0] - grads[0] * 2).abs().max() < 1e-30
+    assert (doubled[2].float() - grads[2].float() * 2).abs().max() < 1e-30
