@@ -160,6 +160,11 @@ def run_ours(args):
         kernel_launches = launches[0]
         stage_ms = np.array([[a.elapsed_time(b) for a, b in zip(e, e[1:])] for e in stages]).mean(0)
 
+        if args.kernels_only:
+            if rank == 0:
+                print(json.dumps({'profiling_case': True, 'batch': s['batch'], 'ms_per_step': elapsed_ms / args.steps,
+                                  'stage_ms': dict(zip(('labels', 'forward', 'backward'), map(float, stage_ms)))}))
+            return
         # end to end: pinned host inputs in, results out, every step
         copy_names = ('q', 'k', 'sq', 'sk', 'v', 'dout')
         h2d = sum(host[k].numel() * host[k].element_size() for k in copy_names)
@@ -203,7 +208,7 @@ def run_ours(args):
             'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True,
             'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16 vectors, int32 labels, f32 accumulate',
             'data': 'synthetic (seeded N(0,1) q,k,v,dO; silu(N(0,1)) codebooks and readout features)',
-            'config': {'workload': 'training shape B8 H16 N8192 D64 R32 DV64 V512 per GPU, all rows hard, tau 0.5',
+            'config': {'workload': f"training shape B{s['batch']} H16 N8192 D64 R32 DV64 V512 per GPU, all rows hard, tau 0.5",
                        'parallelism': f'heads sharded, 16 heads per GPU x {world}, no collective',
                        'l2': 'inputs per step (671 MB) exceed L2'},
             'stage_ms': {'labels': float(stage_ms[0]), 'forward': forward_ms, 'backward': float(stage_ms[2])},
@@ -299,7 +304,11 @@ def main():
     parser.add_argument('--steps', type=int, default=10)
     parser.add_argument('--warmup', type=int, default=3)
     parser.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    # profiling aids (ncu captures want a small case and no host-side work); not for reported numbers
+    parser.add_argument('--batch', type=int, default=SHAPE['batch'])
+    parser.add_argument('--kernels-only', action='store_true', help='skip the end-to-end and CPU-baseline legs')
     args = parser.parse_args()
+    SHAPE['batch'] = args.batch
     if args.impl == 'reference':
         run_reference(args)
     else:

@@ -28,10 +28,10 @@ __device__ __forceinline__ float ex2(float x) {
 }
 __device__ __forceinline__ float bf2f(__nv_bfloat16 x) { return __bfloat162float(x); }
 
-// COUNT consecutive bf16 values (a multiple of 4, 8 bytes aligned) as floats.
+// COUNT consecutive bf16 values (a multiple of 8, 16 bytes aligned) as floats.
 template <int COUNT>
 __device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float (&out)[COUNT]) {
-    static_assert(COUNT % 4 == 0, "vector loads of 4 or 8 values");
+    static_assert(COUNT % 8 == 0, "vector loads of 8 values");
     if constexpr (COUNT % 8 == 0) {
 #pragma unroll
         for (int c = 0; c < COUNT / 8; ++c) {
@@ -43,15 +43,11 @@ __device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float (&out)[C
                 out[c * 8 + 2 * e + 1] = __uint_as_float(word[e] & 0xffff0000u);
             }
         }
-    } else {
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
-        out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
-        out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
     }
 }
 template <int COUNT>
 __device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const float (&in)[COUNT]) {
-    static_assert(COUNT % 4 == 0, "vector stores of 4 or 8 values");
+    static_assert(COUNT % 8 == 0, "vector stores of 8 values");
     unsigned word[COUNT / 2];
 #pragma unroll
     for (int e = 0; e < COUNT / 2; ++e) {
@@ -62,8 +58,6 @@ __device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const float (&in)[C
 #pragma unroll
         for (int c = 0; c < COUNT / 8; ++c)
             reinterpret_cast<uint4*>(p)[c] = make_uint4(word[4 * c], word[4 * c + 1], word[4 * c + 2], word[4 * c + 3]);
-    } else {
-        *reinterpret_cast<uint2*>(p) = make_uint2(word[0], word[1]);
     }
 }
 // Sum over the four lanes of a group.
@@ -116,61 +110,172 @@ __device__ __forceinline__ int lower_bound_position(const int2* __restrict__ ent
     return lo;
 }
 
-// Per-warp queue of the partners found in one round: up to 32 per owned row.
+// Per-warp queue of the partners found in one round: up to 32 per owned row, in ascending
+// position, each with its log2 weight (and, for the query-major backward, its dlog weight).
+template <bool EXTRA>
 struct PairQueue {
     int position[OWN][32];
-    int length[OWN][32];
+    float weight[OWN][32];
+    float extra[EXTRA ? OWN : 1][32];
 };
 
-// One round of partner search for the warp's OWN rows.  Lane r < OWN carries the label of row r
-// and its cursor into the other side's index; each row reads its next 32 bucket entries, keeps
-// those with the same label, computes their run lengths (one lane per partner) and queues them
-// in ascending position.  Returns in lane r the number queued for row r.
-// QUERY_MAJOR: owned rows are queries i = row0 + r and partners are keys; otherwise owned rows are
-// keys j = row0 + r and partners are queries.
-template <bool QUERY_MAJOR>
-__device__ __forceinline__ int find_partners(PairQueue* queue, const int2* __restrict__ entries,
-                                             const int* __restrict__ iq, const int* __restrict__ ik,
-                                             const int* __restrict__ boundary, int n, int row0, int label,
-                                             int& cursor, int end, int lane) {
-    int queued = 0;
-#pragma unroll 1
-    for (int r = 0; r < OWN; ++r) {
-        const int from = __shfl_sync(FULL, cursor, r), to = __shfl_sync(FULL, end, r);
-        if (from >= to) continue;  // uniform
-        const int wanted = __shfl_sync(FULL, label, r);
-        const int at = from + lane;
-        int2 entry = make_int2(0, 0);
-        if (at < to) entry = __ldg(entries + at);
-        const bool hit = at < to && entry.y == wanted;
-        int length = 0;
-        if (hit) length = QUERY_MAJOR ? run_length(iq, ik, boundary, n, row0 + r, entry.x)
-                                      : run_length(iq, ik, boundary, n, entry.x, row0 + r);
-        const unsigned mask = __ballot_sync(FULL, hit);
-        if (hit) {
-            const int slot = __popc(mask & ((1u << lane) - 1u));
-            queue->position[r][slot] = entry.x;
-            queue->length[r][slot] = length;
-        }
-        if (lane == r) {
-            queued = __popc(mask);
-            cursor = from + 32;
-        }
-    }
-    return queued;
-}
+// What one round of the search needs besides the index; lane r < OWN carries row r's values.
+struct SearchRow {
+    int label;     // label of the owned row
+    int previous;  // label of the owned side at row - 1 (the diagonal predecessor's own-side label)
+    int cursor, end;
+};
 
-// Causal range of the bucket of `label` for owner position `row` (binary search on positions).
+// Range of the bucket of `label` that can hold causal partners of owner position `row`.
 template <bool QUERY_MAJOR>
 __device__ __forceinline__ void partner_range(const SideIndex& index, int label, int row, int& cursor, int& end) {
     const int bucket = bucket_of(label);
     const int lo = __ldg(index.starts + bucket), hi = __ldg(index.starts + bucket + 1);
-    if (QUERY_MAJOR) {  // keys at positions <= row
-        cursor = lo;
-        end = lower_bound_position(index.entries, lo, hi, row + 1);
-    } else {  // queries at positions >= row
-        cursor = lower_bound_position(index.entries, lo, hi, row);
-        end = hi;
+    cursor = lo;
+    end = hi;
+    // Keys are scanned from the bucket start until a position beyond the row shows up.  Queries
+    // start at the first position >= row; small buckets are simply scanned from their start.
+    if (!QUERY_MAJOR && hi - lo > 64) cursor = lower_bound_position(index.entries, lo, hi, row);
+}
+
+// One round of partner search for the warp's OWN rows.  Each row reads its next 32 bucket
+// entries (all eight loads are issued before any is used), keeps the causal entries with its
+// label, and queues them in ascending position with the log2 weight of their run length.
+// `shift` is subtracted from the weight (the key-major backward passes the partner's log2
+// normaliser through `shift_by_position`).  Returns in lane r the number queued for row r.
+// QUERY_MAJOR: owned rows are queries i = row0 + r and partners are keys; otherwise owned rows are
+// keys j = row0 + r and partners are queries.
+template <bool QUERY_MAJOR, bool EXTRA>
+__device__ __forceinline__ int find_partners(PairQueue<EXTRA>* queue, const int2* __restrict__ entries,
+                                             const int* __restrict__ iq, const int* __restrict__ ik,
+                                             const int* __restrict__ boundary, const float* __restrict__ lut,
+                                             const float* __restrict__ dlut,
+                                             const float* __restrict__ shift_by_position, int n, int row0,
+                                             SearchRow& mine, int lane) {
+    const int* other_side = QUERY_MAJOR ? ik : iq;
+    int2 entry[OWN];
+    bool valid[OWN];
+#pragma unroll
+    for (int r = 0; r < OWN; ++r) {
+        const int from = __shfl_sync(FULL, mine.cursor, r), to = __shfl_sync(FULL, mine.end, r);
+        valid[r] = from + lane < to;
+        entry[r] = make_int2(QUERY_MAJOR ? 0x7fffffff : -1, 0);
+        if (valid[r]) entry[r] = __ldg(entries + from + lane);
+    }
+    int neighbour[OWN];
+    float shift[OWN];
+    bool hit[OWN];
+#pragma unroll
+    for (int r = 0; r < OWN; ++r) {
+        const int row = row0 + r, wanted = __shfl_sync(FULL, mine.label, r);
+        const bool causal = QUERY_MAJOR ? entry[r].x <= row : entry[r].x >= row;
+        hit[r] = valid[r] && causal && entry[r].y == wanted;
+        // the other side's label one step up the diagonal, and the partner's normaliser
+        neighbour[r] = 0;
+        shift[r] = 0.f;
+        if (hit[r] && entry[r].x > 0) neighbour[r] = __ldg(other_side + entry[r].x - 1);
+        if (hit[r] && shift_by_position) shift[r] = __ldg(shift_by_position + entry[r].x);
+        const unsigned beyond = QUERY_MAJOR ? __ballot_sync(FULL, valid[r] && entry[r].x > row) : 0u;
+        const int from = __shfl_sync(FULL, mine.cursor, r), to = __shfl_sync(FULL, mine.end, r);
+        if (lane == r && from < to) mine.cursor = beyond ? to : from + 32;
+    }
+    const float weight_one = __ldg(lut + 1), extra_one = EXTRA ? __ldg(dlut + 1) : 0.f;
+    int queued = 0;
+#pragma unroll
+    for (int r = 0; r < OWN; ++r) {
+        const int row = row0 + r, previous = __shfl_sync(FULL, mine.previous, r);
+        float weight = weight_one, extra = extra_one;
+        if (hit[r] && entry[r].x > 0 && row > 0 && neighbour[r] == previous) {  // the run is longer than one
+            const int i = QUERY_MAJOR ? row : entry[r].x, j = QUERY_MAJOR ? entry[r].x : row;
+            const int length = 1 + run_length(iq, ik, boundary, n, i - 1, j - 1);
+            weight = __ldg(lut + length);
+            if (EXTRA) extra = __ldg(dlut + length);
+        }
+        const unsigned mask = __ballot_sync(FULL, hit[r]);
+        if (hit[r]) {
+            const int slot = __popc(mask & ((1u << lane) - 1u));
+            queue->position[r][slot] = entry[r].x;
+            queue->weight[r][slot] = weight - shift[r];
+            if (EXTRA) queue->extra[r][slot] = extra;
+        }
+        if (lane == r) queued = __popc(mask);
+    }
+    return queued;
+}
+
+// ---- gather ring -------------------------------------------------------------------------------
+// The per-pair vectors (A: eight bf16 on the lanes that hold a slice of the R-wide vector, B: VPL
+// bf16 on every lane) are gathered with cp.async into a
+// small shared-memory ring that each lane reads back itself, so several pairs' loads are in
+// flight per lane group while earlier pairs are being accumulated.
+constexpr int STAGES = 4;
+
+__device__ __forceinline__ void cp_async16(void* shared, const void* global) {
+    const unsigned target = static_cast<unsigned>(__cvta_generic_to_shared(shared));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target), "l"(global));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
+template <int RPL, int VPL>
+struct GatherRing {
+    // [stage][lane] keeps consecutive lanes 16 or more bytes apart without bank conflicts
+    __nv_bfloat16 b[STAGES][32][VPL];
+    __nv_bfloat16 a[STAGES][32][RPL];
+};
+
+template <int COUNT>
+__device__ __forceinline__ void unpack_bf16(const __nv_bfloat16* shared, float (&out)[COUNT]) {
+    if constexpr (COUNT % 8 == 0) {
+#pragma unroll
+        for (int c = 0; c < COUNT / 8; ++c) {
+            const uint4 raw = reinterpret_cast<const uint4*>(shared)[c];
+            const unsigned word[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                out[c * 8 + 2 * e] = __uint_as_float(word[e] << 16);
+                out[c * 8 + 2 * e + 1] = __uint_as_float(word[e] & 0xffff0000u);
+            }
+        }
+    }
+}
+
+// Works through the queued partners of the warp's rows: lane group g takes row g's queue in
+// order.  `a_base` / `b_base` point at this lane's slice of position 0; positions are
+// `a_stride` / `b_stride` elements apart.  consume(live, slot, a, b) is called once per round by
+// every lane (group sums inside it need the whole warp); live lanes have their vectors loaded.
+template <int RPL, int VPL, class Consume>
+__device__ __forceinline__ void drain_partners(const int* positions /* queue->position[group] */, int mine, int rounds,
+                                               GatherRing<RPL, VPL>* ring, const __nv_bfloat16* a_base,
+                                               int64_t a_stride, bool has_a, const __nv_bfloat16* b_base,
+                                               int64_t b_stride, int lane, Consume&& consume) {
+    static_assert(RPL == 8 && VPL % 8 == 0, "every gathered slice is a whole number of 16-byte pieces");
+    auto issue = [&](int slot) {
+        if (slot < mine) {
+            const int position = positions[slot], stage = slot % STAGES;
+            const __nv_bfloat16* a = a_base + position * a_stride;
+            const __nv_bfloat16* b = b_base + position * b_stride;
+            if (has_a) cp_async16(&ring->a[stage][lane][0], a);
+#pragma unroll
+            for (int c = 0; c < VPL / 8; ++c) cp_async16(&ring->b[stage][lane][c * 8], b + c * 8);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int slot = 0; slot < STAGES - 1; ++slot) issue(slot);
+    for (int slot = 0; slot < rounds; ++slot) {
+        issue(slot + STAGES - 1);
+        cp_async_wait<STAGES - 1>();
+        const bool live = slot < mine;
+        float a[RPL], b[VPL];
+#pragma unroll
+        for (int c = 0; c < RPL; ++c) a[c] = 0.f;
+        if (live) {
+            if (has_a) unpack_bf16<RPL>(&ring->a[slot % STAGES][lane][0], a);
+            unpack_bf16<VPL>(&ring->b[slot % STAGES][lane][0], b);
+        }
+        consume(live, slot, a, b);
     }
 }
 

@@ -41,12 +41,20 @@ struct BackwardArgs {
 };
 
 // ---- query-major pass: dSQ and the per-row tau term ----------------------------------------------
+template <int R, int DV, bool EXTRA>
+struct BackwardShared {
+    PairQueue<EXTRA> queue[WARPS];
+    GatherRing<8, DV / 4> ring[WARPS];
+};
+
 template <int R, int DV>
 __global__ __launch_bounds__(WARPS * 32) void hard_backward_query_kernel(const BackwardArgs a) {
-    constexpr int RPL = R / 4, VPL = DV / 4;
-    __shared__ PairQueue queues[WARPS];
+    constexpr int RPL = 8, VPL = DV / 4;
+    extern __shared__ __align__(16) unsigned char storage[];
+    auto& shared = *reinterpret_cast<BackwardShared<R, DV, true>*>(storage);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group = lane >> 2, part = lane & 3;
-    PairQueue* queue = queues + warp;
+    const bool has_r = part * RPL < R;  // this lane holds a slice of the R-wide vectors
+    PairQueue<true>* queue = shared.queue + warp;
     const int blocks = a.n / BLOCK_ROWS, half = blocks / 2;
     for (int task = blockIdx.x; task < a.tasks; task += gridDim.x) {
         const int bh = task / half, pair = task % half, b = bh / a.heads, h = bh % a.heads;
@@ -66,46 +74,48 @@ __global__ __launch_bounds__(WARPS * 32) void hard_backward_query_kernel(const B
             for (int c = 0; c < RPL; ++c) dsq[c] = 0.f;
             if (active) {
                 float query[RPL], derivative[VPL];
-                load_bf16<RPL>(a.sq + (vec0 + int64_t(row) * a.heads) * R + part * RPL, query);
+#pragma unroll
+                for (int c = 0; c < RPL; ++c) query[c] = 0.f;
+                if (has_r) load_bf16<RPL>(a.sq + (vec0 + int64_t(row) * a.heads) * R + part * RPL, query);
                 load_bf16<VPL>(a.dout + (vec0 + int64_t(row) * a.heads) * DV + part * VPL, derivative);
                 const float norm = __ldg(a.lse2 + int64_t(bh) * a.n + row), center = __ldg(dlut + row + 1);
                 float u = 0.f, v = 0.f, w = 0.f, z = 0.f;
-                const int label = __ldg(iq + row0 + (lane & (OWN - 1)));
-                int cursor, end;
-                partner_range<true>(keys, label, row0 + (lane & (OWN - 1)), cursor, end);
-                while (__ballot_sync(FULL, lane < OWN && cursor < end)) {
+                const int searched = row0 + (lane & (OWN - 1));
+                SearchRow search;
+                search.label = __ldg(iq + searched);
+                search.previous = searched ? __ldg(iq + searched - 1) : 0;
+                partner_range<true>(keys, search.label, searched, search.cursor, search.end);
+                while (__ballot_sync(FULL, lane < OWN && search.cursor < search.end)) {
                     __syncwarp();
-                    const int queued = find_partners<true>(queue, keys.entries, iq, ik, boundary, a.n, row0, label,
-                                                           cursor, end, lane);
+                    const int queued = find_partners<true, true>(queue, keys.entries, iq, ik, boundary, lut, dlut, nullptr,
+                                                                 a.n, row0, search, lane);
                     __syncwarp();
                     const int mine = __shfl_sync(FULL, queued, group);
                     const int rounds = __reduce_max_sync(FULL, mine);
-                    for (int it = 0; it < rounds; ++it) {
-                        const bool live = it < mine;
-                        float key[RPL], partial_s = 0.f, partial_e = 0.f, p = 0.f, g = 0.f;
-                        if (live) {
-                            const int j = queue->position[group][it], length = queue->length[group][it];
-                            p = ex2(__ldg(lut + length) - norm);
-                            g = __ldg(dlut + length) - center;
-                            load_bf16<RPL>(a.sk + (vec0 + int64_t(j) * a.heads) * R + part * RPL, key);
-                            float value[VPL];
-                            load_bf16<VPL>(a.v + (vec0 + int64_t(j) * a.heads) * DV + part * VPL, value);
+                    drain_partners<RPL, VPL>(
+                        queue->position[group], mine, rounds, shared.ring + warp,
+                        a.sk + vec0 * R + part * RPL, int64_t(a.heads) * R, has_r, a.v + vec0 * DV + part * VPL,
+                        int64_t(a.heads) * DV, lane, [&](bool live, int slot, const float(&key)[RPL], const float(&value)[VPL]) {
+                            float partial_s = 0.f, partial_e = 0.f;
+                            if (live) {
 #pragma unroll
-                            for (int c = 0; c < RPL; ++c) partial_s = fmaf(query[c], key[c], partial_s);
+                                for (int c = 0; c < RPL; ++c) partial_s = fmaf(query[c], key[c], partial_s);
 #pragma unroll
-                            for (int c = 0; c < VPL; ++c) partial_e = fmaf(derivative[c], value[c], partial_e);
-                        }
-                        const float s = group_sum(partial_s), e = group_sum(partial_e);
-                        if (live) {
-                            const float pse = p * s * e, pe = p * e;
-                            u += pse;
-                            v = fmaf(p, g, v);
-                            w = fmaf(pse, g, w);
-                            z += p;
+                                for (int c = 0; c < VPL; ++c) partial_e = fmaf(derivative[c], value[c], partial_e);
+                            }
+                            const float s = group_sum(partial_s), e = group_sum(partial_e);
+                            if (live) {
+                                const float p = ex2(queue->weight[group][slot] - norm);
+                                const float g = queue->extra[group][slot] - center;
+                                const float pse = p * s * e, pe = p * e;
+                                u += pse;
+                                v = fmaf(p, g, v);
+                                w = fmaf(pse, g, w);
+                                z += p;
 #pragma unroll
-                            for (int c = 0; c < RPL; ++c) dsq[c] = fmaf(pe, key[c], dsq[c]);
-                        }
-                    }
+                                for (int c = 0; c < RPL; ++c) dsq[c] = fmaf(pe, key[c], dsq[c]);
+                            }
+                        });
                 }
                 // Centred four-moment form: the fallback has unit weight and zero derivative.
                 const float fallback = ex2(-norm), inverse = __fdividef(1.f, z + fallback);
@@ -113,8 +123,11 @@ __global__ __launch_bounds__(WARPS * 32) void hard_backward_query_kernel(const B
                 term = fmaf(-u, mean, w) * inverse;
             }
             float* out = a.dsq + (vec0 + int64_t(row) * a.heads) * R + part * RPL;
+            if (has_r) {
 #pragma unroll
-            for (int c = 0; c < RPL; c += 4) *reinterpret_cast<float4*>(out + c) = make_float4(dsq[c], dsq[c + 1], dsq[c + 2], dsq[c + 3]);
+                for (int c = 0; c < RPL; c += 4)
+                    *reinterpret_cast<float4*>(out + c) = make_float4(dsq[c], dsq[c + 1], dsq[c + 2], dsq[c + 3]);
+            }
             if (part == 0) a.dtau_rows[int64_t(bh) * a.n + row] = term;
         }
     }
@@ -123,10 +136,12 @@ __global__ __launch_bounds__(WARPS * 32) void hard_backward_query_kernel(const B
 // ---- key-major pass: dV and dSK ---------------------------------------------------------------------
 template <int R, int DV>
 __global__ __launch_bounds__(WARPS * 32) void hard_backward_key_kernel(const BackwardArgs a) {
-    constexpr int RPL = R / 4, VPL = DV / 4;
-    __shared__ PairQueue queues[WARPS];
+    constexpr int RPL = 8, VPL = DV / 4;
+    extern __shared__ __align__(16) unsigned char storage[];
+    auto& shared = *reinterpret_cast<BackwardShared<R, DV, false>*>(storage);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group = lane >> 2, part = lane & 3;
-    PairQueue* queue = queues + warp;
+    const bool has_r = part * RPL < R;  // this lane holds a slice of the R-wide vectors
+    PairQueue<false>* queue = shared.queue + warp;
     const int blocks = a.n / BLOCK_ROWS, half = blocks / 2;
     for (int task = blockIdx.x; task < a.tasks; task += gridDim.x) {
         const int bh = task / half, pair = task % half, b = bh / a.heads, h = bh % a.heads;
@@ -148,67 +163,77 @@ __global__ __launch_bounds__(WARPS * 32) void hard_backward_key_kernel(const Bac
             for (int c = 0; c < RPL; ++c) dsk[c] = 0.f;
             if (active) {
                 float key[RPL], value[VPL];
-                load_bf16<RPL>(a.sk + (vec0 + int64_t(row) * a.heads) * R + part * RPL, key);
+#pragma unroll
+                for (int c = 0; c < RPL; ++c) key[c] = 0.f;
+                if (has_r) load_bf16<RPL>(a.sk + (vec0 + int64_t(row) * a.heads) * R + part * RPL, key);
                 load_bf16<VPL>(a.v + (vec0 + int64_t(row) * a.heads) * DV + part * VPL, value);
-                const int label = __ldg(ik + row0 + (lane & (OWN - 1)));
-                int cursor, end;
-                partner_range<false>(queries, label, row0 + (lane & (OWN - 1)), cursor, end);
-                while (__ballot_sync(FULL, lane < OWN && cursor < end)) {
+                const int searched = row0 + (lane & (OWN - 1));
+                SearchRow search;
+                search.label = __ldg(ik + searched);
+                search.previous = searched ? __ldg(ik + searched - 1) : 0;
+                partner_range<false>(queries, search.label, searched, search.cursor, search.end);
+                while (__ballot_sync(FULL, lane < OWN && search.cursor < search.end)) {
                     __syncwarp();
-                    const int queued = find_partners<false>(queue, queries.entries, iq, ik, boundary, a.n, row0,
-                                                            label, cursor, end, lane);
+                    const int queued = find_partners<false, false>(queue, queries.entries, iq, ik, boundary, lut, nullptr,
+                                                                   lse2, a.n, row0, search, lane);
                     __syncwarp();
                     const int mine = __shfl_sync(FULL, queued, group);
                     const int rounds = __reduce_max_sync(FULL, mine);
-                    for (int it = 0; it < rounds; ++it) {
-                        const bool live = it < mine;
-                        float query[RPL], derivative[VPL], partial_s = 0.f, partial_e = 0.f, p = 0.f;
-                        if (live) {
-                            const int i = queue->position[group][it];
-                            p = ex2(__ldg(lut + queue->length[group][it]) - __ldg(lse2 + i));
-                            load_bf16<RPL>(a.sq + (vec0 + int64_t(i) * a.heads) * R + part * RPL, query);
-                            load_bf16<VPL>(a.dout + (vec0 + int64_t(i) * a.heads) * DV + part * VPL, derivative);
+                    drain_partners<RPL, VPL>(
+                        queue->position[group], mine, rounds, shared.ring + warp,
+                        a.sq + vec0 * R + part * RPL, int64_t(a.heads) * R, has_r, a.dout + vec0 * DV + part * VPL,
+                        int64_t(a.heads) * DV, lane,
+                        [&](bool live, int slot, const float(&query)[RPL], const float(&derivative)[VPL]) {
+                            float partial_s = 0.f, partial_e = 0.f;
+                            if (live) {
 #pragma unroll
-                            for (int c = 0; c < RPL; ++c) partial_s = fmaf(query[c], key[c], partial_s);
+                                for (int c = 0; c < RPL; ++c) partial_s = fmaf(query[c], key[c], partial_s);
 #pragma unroll
-                            for (int c = 0; c < VPL; ++c) partial_e = fmaf(derivative[c], value[c], partial_e);
-                        }
-                        const float s = group_sum(partial_s), e = group_sum(partial_e);
-                        if (live) {
-                            const float ps = p * s, pe = p * e;
+                                for (int c = 0; c < VPL; ++c) partial_e = fmaf(derivative[c], value[c], partial_e);
+                            }
+                            const float s = group_sum(partial_s), e = group_sum(partial_e);
+                            if (live) {
+                                const float p = ex2(queue->weight[group][slot]);  // table entry minus the query's normaliser
+                                const float ps = p * s, pe = p * e;
 #pragma unroll
-                            for (int c = 0; c < VPL; ++c) dv[c] = fmaf(ps, derivative[c], dv[c]);
+                                for (int c = 0; c < VPL; ++c) dv[c] = fmaf(ps, derivative[c], dv[c]);
 #pragma unroll
-                            for (int c = 0; c < RPL; ++c) dsk[c] = fmaf(pe, query[c], dsk[c]);
-                        }
-                    }
+                                for (int c = 0; c < RPL; ++c) dsk[c] = fmaf(pe, query[c], dsk[c]);
+                            }
+                        });
                 }
             }
             store_bf16<VPL>(a.dv + (vec0 + int64_t(row) * a.heads) * DV + part * VPL, dv);
-            store_bf16<RPL>(a.dsk + (vec0 + int64_t(row) * a.heads) * R + part * RPL, dsk);
+            if (has_r) store_bf16<RPL>(a.dsk + (vec0 + int64_t(row) * a.heads) * R + part * RPL, dsk);
         }
     }
 }
 
-// dtau[h] = sum over batch and rows of the per-row terms, in a fixed order.
-__global__ void tau_reduce_kernel(const float* __restrict__ rows, float* __restrict__ dtau, int batch, int heads,
-                                  int n) {
+// dtau[h] = sum over batch and rows of the per-row terms, in a fixed order (thread-strided partial
+// sums, then a tree), so the result is the same for every launch.
+__global__ __launch_bounds__(1024) void tau_reduce_kernel(const float* __restrict__ rows, float* __restrict__ dtau,
+                                                          int batch, int heads, int n) {
     const int head = blockIdx.x;
-    float sum = 0.f;
-    for (int64_t e = threadIdx.x; e < int64_t(batch) * n; e += blockDim.x)
-        sum += rows[(e / n * heads + head) * n + e % n];
-    __shared__ float partial[256];
-    partial[threadIdx.x] = sum;
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int b = 0; b < batch; ++b) {
+        const float4* source = reinterpret_cast<const float4*>(rows + (int64_t(b) * heads + head) * n);
+        for (int e = threadIdx.x; e < n / 4; e += blockDim.x) {
+            const float4 x = __ldg(source + e);
+            sum[0] += x.x; sum[1] += x.y; sum[2] += x.z; sum[3] += x.w;
+        }
+    }
+    __shared__ float partial[1024];
+    partial[threadIdx.x] = (sum[0] + sum[1]) + (sum[2] + sum[3]);
     __syncthreads();
-    for (int s = 128; s; s >>= 1) {
+    for (int s = 512; s; s >>= 1) {
         if (threadIdx.x < s) partial[threadIdx.x] += partial[threadIdx.x + s];
         __syncthreads();
     }
     if (threadIdx.x == 0) dtau[head] = partial[0];
 }
 
-// Workspace: both position indices, then the dlog table [H, lut_stride] and the per-row tau terms
-// [B, H, N] in FP32.
+// Workspace: both position indices, then the per-row tau terms [B, H, N] (read back as float4, so
+// they come first and stay 16-byte aligned) and the dlog table [H, lut_stride], all FP32.
 size_t hard_backward_workspace_bytes(int batch, int heads, int n, int lut_stride) {
     return index_bytes(batch * heads, n, 2) + sizeof(float) * (size_t(heads) * lut_stride + size_t(batch) * heads * n);
 }
@@ -217,16 +242,21 @@ template <int R, int DV>
 static cudaError_t launch_backward_variant(const BackwardArgs& args, int ctas, cudaStream_t stream) {
     auto query = hard_backward_query_kernel<R, DV>;
     auto key = hard_backward_key_kernel<R, DV>;
+    const int shared_q = sizeof(BackwardShared<R, DV, true>), shared_k = sizeof(BackwardShared<R, DV, false>);
+    cudaError_t status = cudaFuncSetAttribute(query, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_q);
+    if (status != cudaSuccess) return status;
+    status = cudaFuncSetAttribute(key, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_k);
+    if (status != cudaSuccess) return status;
     int resident_q = 1, resident_k = 1;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_q, query, WARPS * 32, 0);
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_k, key, WARPS * 32, 0);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_q, query, WARPS * 32, shared_q);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_k, key, WARPS * 32, shared_k);
     const int sms = device_sm_count();
     int grid_q = ctas ? ctas : sms * (resident_q > 0 ? resident_q : 1);
     int grid_k = ctas ? ctas : sms * (resident_k > 0 ? resident_k : 1);
     if (grid_q > args.tasks) grid_q = args.tasks;
     if (grid_k > args.tasks) grid_k = args.tasks;
-    query<<<grid_q, WARPS * 32, 0, stream>>>(args);
-    key<<<grid_k, WARPS * 32, 0, stream>>>(args);
+    query<<<grid_q, WARPS * 32, shared_q, stream>>>(args);
+    key<<<grid_k, WARPS * 32, shared_k, stream>>>(args);
     return cudaGetLastError();
 }
 
@@ -240,8 +270,8 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     if (status != cudaSuccess) return status;
     status = launch_build_index(iq, batch_heads, shape.n, workspace, 1, 2, stream);
     if (status != cudaSuccess) return status;
-    float* dlut = reinterpret_cast<float*>(static_cast<char*>(workspace) + index_bytes(batch_heads, shape.n, 2));
-    float* rows = dlut + size_t(shape.heads) * lut_stride;
+    float* rows = reinterpret_cast<float*>(static_cast<char*>(workspace) + index_bytes(batch_heads, shape.n, 2));
+    float* dlut = rows + size_t(batch_heads) * shape.n;
     dlog_weights_kernel<<<dim3((lut_stride + 255) / 256, shape.heads), 256, 0, stream>>>(lut, dlut, lut_stride);
     BackwardArgs args{sq, sk, v, dout, iq, ik, boundary, hard, lut, dlut, lse2,
                       side_index(workspace, batch_heads, shape.n, 0, 2), side_index(workspace, batch_heads, shape.n, 1, 2),
@@ -254,7 +284,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     DISM_CASE(32, 32) DISM_CASE(32, 64) DISM_CASE(32, 128)
 #undef DISM_CASE
     if (status != cudaSuccess) return status;
-    tau_reduce_kernel<<<shape.heads, 256, 0, stream>>>(rows, dtau, shape.batch, shape.heads, shape.n);
+    tau_reduce_kernel<<<shape.heads, 1024, 0, stream>>>(rows, dtau, shape.batch, shape.heads, shape.n);
     return cudaGetLastError();
 }
 

@@ -44,11 +44,19 @@ struct ForwardArgs {
 };
 
 template <int R, int DV>
+struct ForwardShared {
+    PairQueue<false> queue[WARPS];
+    GatherRing<8, DV / 4> ring[WARPS];
+};
+
+template <int R, int DV>
 __global__ __launch_bounds__(WARPS * 32) void hard_forward_kernel(const ForwardArgs a) {
-    constexpr int RPL = R / 4, VPL = DV / 4;  // elements per lane of a four-lane group
-    __shared__ PairQueue queues[WARPS];
+    constexpr int RPL = 8, VPL = DV / 4;  // elements per lane of a four-lane group (R=16: two lanes hold sq/sk)
+    extern __shared__ __align__(16) unsigned char storage[];
+    auto& shared = *reinterpret_cast<ForwardShared<R, DV>*>(storage);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group = lane >> 2, part = lane & 3;
-    PairQueue* queue = queues + warp;
+    const bool has_r = part * RPL < R;  // this lane holds a slice of the R-wide vectors
+    PairQueue<false>* queue = shared.queue + warp;
     const int blocks = a.n / BLOCK_ROWS, half = blocks / 2;
     for (int task = blockIdx.x; task < a.tasks; task += gridDim.x) {
         const int bh = task / half, pair = task % half, b = bh / a.heads, h = bh % a.heads;
@@ -68,47 +76,47 @@ __global__ __launch_bounds__(WARPS * 32) void hard_forward_kernel(const ForwardA
             for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
             if (active) {
                 float query[RPL];
-                load_bf16<RPL>(a.sq + (vec0 + int64_t(row) * a.heads) * R + part * RPL, query);
-                const int label = __ldg(iq + row0 + (lane & (OWN - 1)));
-                int cursor, end;
-                partner_range<true>(keys, label, row0 + (lane & (OWN - 1)), cursor, end);
-                while (__ballot_sync(FULL, lane < OWN && cursor < end)) {
+#pragma unroll
+                for (int c = 0; c < RPL; ++c) query[c] = 0.f;
+                if (has_r) load_bf16<RPL>(a.sq + (vec0 + int64_t(row) * a.heads) * R + part * RPL, query);
+                const int searched = row0 + (lane & (OWN - 1));
+                SearchRow search;
+                search.label = __ldg(iq + searched);
+                search.previous = searched ? __ldg(iq + searched - 1) : 0;
+                partner_range<true>(keys, search.label, searched, search.cursor, search.end);
+                while (__ballot_sync(FULL, lane < OWN && search.cursor < search.end)) {
                     __syncwarp();
-                    const int queued = find_partners<true>(queue, keys.entries, iq, ik, boundary, a.n, row0, label,
-                                                           cursor, end, lane);
+                    const int queued = find_partners<true, false>(queue, keys.entries, iq, ik, boundary, lut, nullptr,
+                                                                  nullptr, a.n, row0, search, lane);
                     __syncwarp();
                     const int mine = __shfl_sync(FULL, queued, group);
                     const int rounds = __reduce_max_sync(FULL, mine);
-                    for (int it = 0; it < rounds; ++it) {
-                        const bool live = it < mine;
-                        float partial = 0.f, x = 0.f;
-                        int j = 0;
-                        if (live) {
-                            j = queue->position[group][it];
-                            x = __ldg(lut + queue->length[group][it]);
-                            float key[RPL];
-                            load_bf16<RPL>(a.sk + (vec0 + int64_t(j) * a.heads) * R + part * RPL, key);
+                    drain_partners<RPL, VPL>(
+                        queue->position[group], mine, rounds, shared.ring + warp,
+                        a.sk + vec0 * R + part * RPL, int64_t(a.heads) * R, has_r, a.v + vec0 * DV + part * VPL,
+                        int64_t(a.heads) * DV, lane, [&](bool live, int slot, const float(&key)[RPL], const float(&value)[VPL]) {
+                            float partial = 0.f;
+                            if (live) {
 #pragma unroll
-                            for (int c = 0; c < RPL; ++c) partial = fmaf(query[c], key[c], partial);
-                        }
-                        const float s = group_sum(partial);
-                        if (live) {
-                            if (x > maximum) {
-                                const float alpha = ex2(maximum - x);
-                                denominator *= alpha;
-#pragma unroll
-                                for (int c = 0; c < VPL; ++c) acc[c] *= alpha;
-                                maximum = x;
+                                for (int c = 0; c < RPL; ++c) partial = fmaf(query[c], key[c], partial);
                             }
-                            const float p = ex2(x - maximum);
-                            denominator += p;
-                            const float weight = p * s;
-                            float value[VPL];
-                            load_bf16<VPL>(a.v + (vec0 + int64_t(j) * a.heads) * DV + part * VPL, value);
+                            const float s = group_sum(partial);
+                            if (live) {
+                                const float x = queue->weight[group][slot];
+                                if (x > maximum) {
+                                    const float alpha = ex2(maximum - x);
+                                    denominator *= alpha;
 #pragma unroll
-                            for (int c = 0; c < VPL; ++c) acc[c] = fmaf(weight, value[c], acc[c]);
-                        }
-                    }
+                                    for (int c = 0; c < VPL; ++c) acc[c] *= alpha;
+                                    maximum = x;
+                                }
+                                const float p = ex2(x - maximum);
+                                denominator += p;
+                                const float weight = p * s;
+#pragma unroll
+                                for (int c = 0; c < VPL; ++c) acc[c] = fmaf(weight, value[c], acc[c]);
+                            }
+                        });
                 }
             }
             float normalizer = 0.f;
@@ -134,12 +142,15 @@ int device_sm_count() {
 template <int R, int DV>
 static cudaError_t launch_forward_variant(const ForwardArgs& args, int ctas, cudaStream_t stream) {
     auto kernel = hard_forward_kernel<R, DV>;
+    const int shared = sizeof(ForwardShared<R, DV>);
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+    if (status != cudaSuccess) return status;
     int resident = 1;
-    cudaError_t status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, WARPS * 32, 0);
+    status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, WARPS * 32, shared);
     if (status != cudaSuccess) return status;
     int grid = ctas ? ctas : device_sm_count() * (resident > 0 ? resident : 1);
     if (grid > args.tasks) grid = args.tasks;
-    kernel<<<grid, WARPS * 32, 0, stream>>>(args);
+    kernel<<<grid, WARPS * 32, shared, stream>>>(args);
     return cudaGetLastError();
 }
 

@@ -92,14 +92,17 @@ __global__ __launch_bounds__(WARPS * 32) void longest_match_kernel(const int* __
         for (int r = 0; r < OWN; ++r) {
             const int i = row0 + r, label = __ldg(s + i);
             int from, to;
-            partner_range<true>(mine, label, i - 1, from, to);  // keys strictly before i
+            partner_range<true>(mine, label, i, from, to);
             long long best = -1;  // (run length << 32) | position: larger run first, then later position
-            for (int at = from + lane; at < to; at += 32) {
-                const int2 entry = __ldg(mine.entries + at);
-                if (entry.y == label) {
+            for (int base = from; base < to; base += 32) {  // positions ascend: stop at the first one >= i
+                const int at = base + lane;
+                int2 entry = make_int2(0x7fffffff, 0);
+                if (at < to) entry = __ldg(mine.entries + at);
+                if (entry.x < i && entry.y == label) {
                     const long long key = (static_cast<long long>(run_length(s, s, nullptr, n, i, entry.x)) << 32) | entry.x;
                     best = max(best, key);
                 }
+                if (__ballot_sync(FULL, entry.x >= i)) break;
             }
 #pragma unroll
             for (int step = 16; step; step >>= 1) best = max(best, __shfl_xor_sync(FULL, best, step));
