@@ -119,13 +119,6 @@ struct PairQueue {
     float extra[EXTRA ? OWN : 1][32];
 };
 
-// What one round of the search needs besides the index; lane r < OWN carries row r's values.
-struct SearchRow {
-    int label;     // label of the owned row
-    int previous;  // label of the owned side at row - 1 (the diagonal predecessor's own-side label)
-    int cursor, end;
-};
-
 // Range of the bucket of `label` that can hold causal partners of owner position `row`.
 template <bool QUERY_MAJOR>
 __device__ __forceinline__ void partner_range(const SideIndex& index, int label, int row, int& cursor, int& end) {
@@ -136,71 +129,6 @@ __device__ __forceinline__ void partner_range(const SideIndex& index, int label,
     // Keys are scanned from the bucket start until a position beyond the row shows up.  Queries
     // start at the first position >= row; small buckets are simply scanned from their start.
     if (!QUERY_MAJOR && hi - lo > 64) cursor = lower_bound_position(index.entries, lo, hi, row);
-}
-
-// One round of partner search for the warp's OWN rows.  Each row reads its next 32 bucket
-// entries (all eight loads are issued before any is used), keeps the causal entries with its
-// label, and queues them in ascending position with the log2 weight of their run length.
-// `shift` is subtracted from the weight (the key-major backward passes the partner's log2
-// normaliser through `shift_by_position`).  Returns in lane r the number queued for row r.
-// QUERY_MAJOR: owned rows are queries i = row0 + r and partners are keys; otherwise owned rows are
-// keys j = row0 + r and partners are queries.
-template <bool QUERY_MAJOR, bool EXTRA>
-__device__ __forceinline__ int find_partners(PairQueue<EXTRA>* queue, const int2* __restrict__ entries,
-                                             const int* __restrict__ iq, const int* __restrict__ ik,
-                                             const int* __restrict__ boundary, const float* __restrict__ lut,
-                                             const float* __restrict__ dlut,
-                                             const float* __restrict__ shift_by_position, int n, int row0,
-                                             SearchRow& mine, int lane) {
-    const int* other_side = QUERY_MAJOR ? ik : iq;
-    int2 entry[OWN];
-    bool valid[OWN];
-#pragma unroll
-    for (int r = 0; r < OWN; ++r) {
-        const int from = __shfl_sync(FULL, mine.cursor, r), to = __shfl_sync(FULL, mine.end, r);
-        valid[r] = from + lane < to;
-        entry[r] = make_int2(QUERY_MAJOR ? 0x7fffffff : -1, 0);
-        if (valid[r]) entry[r] = __ldg(entries + from + lane);
-    }
-    int neighbour[OWN];
-    float shift[OWN];
-    bool hit[OWN];
-#pragma unroll
-    for (int r = 0; r < OWN; ++r) {
-        const int row = row0 + r, wanted = __shfl_sync(FULL, mine.label, r);
-        const bool causal = QUERY_MAJOR ? entry[r].x <= row : entry[r].x >= row;
-        hit[r] = valid[r] && causal && entry[r].y == wanted;
-        // the other side's label one step up the diagonal, and the partner's normaliser
-        neighbour[r] = 0;
-        shift[r] = 0.f;
-        if (hit[r] && entry[r].x > 0) neighbour[r] = __ldg(other_side + entry[r].x - 1);
-        if (hit[r] && shift_by_position) shift[r] = __ldg(shift_by_position + entry[r].x);
-        const unsigned beyond = QUERY_MAJOR ? __ballot_sync(FULL, valid[r] && entry[r].x > row) : 0u;
-        const int from = __shfl_sync(FULL, mine.cursor, r), to = __shfl_sync(FULL, mine.end, r);
-        if (lane == r && from < to) mine.cursor = beyond ? to : from + 32;
-    }
-    const float weight_one = __ldg(lut + 1), extra_one = EXTRA ? __ldg(dlut + 1) : 0.f;
-    int queued = 0;
-#pragma unroll
-    for (int r = 0; r < OWN; ++r) {
-        const int row = row0 + r, previous = __shfl_sync(FULL, mine.previous, r);
-        float weight = weight_one, extra = extra_one;
-        if (hit[r] && entry[r].x > 0 && row > 0 && neighbour[r] == previous) {  // the run is longer than one
-            const int i = QUERY_MAJOR ? row : entry[r].x, j = QUERY_MAJOR ? entry[r].x : row;
-            const int length = 1 + run_length(iq, ik, boundary, n, i - 1, j - 1);
-            weight = __ldg(lut + length);
-            if (EXTRA) extra = __ldg(dlut + length);
-        }
-        const unsigned mask = __ballot_sync(FULL, hit[r]);
-        if (hit[r]) {
-            const int slot = __popc(mask & ((1u << lane) - 1u));
-            queue->position[r][slot] = entry[r].x;
-            queue->weight[r][slot] = weight - shift[r];
-            if (EXTRA) queue->extra[r][slot] = extra;
-        }
-        if (lane == r) queued = __popc(mask);
-    }
-    return queued;
 }
 
 // ---- gather ring -------------------------------------------------------------------------------
@@ -219,7 +147,7 @@ template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
 template <int RPL, int VPL>
-struct GatherRing {
+struct alignas(16) GatherRing {  // 16-byte pieces: the struct keeps that alignment wherever it is embedded
     // [stage][lane] keeps consecutive lanes 16 or more bytes apart without bank conflicts
     __nv_bfloat16 b[STAGES][32][VPL];
     __nv_bfloat16 a[STAGES][32][RPL];
@@ -278,6 +206,18 @@ __device__ __forceinline__ void drain_partners(const int* positions /* queue->po
         consume(live, slot, a, b);
     }
 }
+
+// Arguments of the row-owned kernels; pointers a kernel does not use stay null.
+struct RowsArgs {
+    const __nv_bfloat16 *sq, *sk, *v, *dout;
+    const int *iq, *ik, *boundary;
+    const uint8_t* hard;
+    const float *lut, *dlut, *lse2;
+    SideIndex index;  // position index of the partner side
+    __nv_bfloat16 *out, *dsk, *dv;
+    float *lse2_out, *dsq, *dtau_rows;
+    int batch, heads, n, lut_stride, tasks;
+};
 
 // ---- launch-side entry points (defined in the .cu files, called from the C ABI) -------------
 struct HardShape {

@@ -8,7 +8,7 @@
 // order with the online max / unit-fallback normalisation of the reference (maximum starts at 0,
 // denominator at 1).  A row is reduced by one group in a fixed order, so outputs do not depend on
 // the grid size.
-#include "dism_common.cuh"
+#include "hard_rows.cuh"
 
 namespace dism {
 
@@ -32,126 +32,65 @@ cudaError_t launch_log_weights(const float* tau, int heads, int n, float* lut, c
     return cudaGetLastError();
 }
 
-struct ForwardArgs {
-    const __nv_bfloat16 *sq, *sk, *v;
-    const int *iq, *ik, *boundary;
-    const uint8_t* hard;
-    const float* lut;
-    SideIndex keys;
-    __nv_bfloat16* out;
-    float* lse2;
-    int batch, heads, n, lut_stride, tasks;
-};
+template <int R_, int DV>
+struct ForwardPolicy {
+    static constexpr bool QUERY_MAJOR = true, EXTRA = false;
+    static constexpr int R = R_, VPL = DV / 4;
+    using Args = RowsArgs;
+    static __device__ __forceinline__ const __nv_bfloat16* gather_a(const Args& a) { return a.sk; }
+    static __device__ __forceinline__ const __nv_bfloat16* gather_b(const Args& a) { return a.v; }
 
-template <int R, int DV>
-struct ForwardShared {
-    PairQueue<false> queue[WARPS];
-    GatherRing<8, DV / 4> ring[WARPS];
-};
+    float query[8], acc[VPL], maximum, denominator;
 
-template <int R, int DV>
-__global__ __launch_bounds__(WARPS * 32) void hard_forward_kernel(const ForwardArgs a) {
-    constexpr int RPL = 8, VPL = DV / 4;  // elements per lane of a four-lane group (R=16: two lanes hold sq/sk)
-    extern __shared__ __align__(16) unsigned char storage[];
-    auto& shared = *reinterpret_cast<ForwardShared<R, DV>*>(storage);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group = lane >> 2, part = lane & 3;
-    const bool has_r = part * RPL < R;  // this lane holds a slice of the R-wide vectors
-    PairQueue<false>* queue = shared.queue + warp;
-    const int blocks = a.n / BLOCK_ROWS, half = blocks / 2;
-    for (int task = blockIdx.x; task < a.tasks; task += gridDim.x) {
-        const int bh = task / half, pair = task % half, b = bh / a.heads, h = bh % a.heads;
-        const bool active = a.hard[bh];
-        const int64_t vec0 = int64_t(b) * a.n * a.heads + h;  // (b, 0, h) in units of one vector
-        const int* iq = a.iq + int64_t(bh) * a.n;
-        const int* ik = a.ik + int64_t(bh) * a.n;
-        const int* boundary = a.boundary ? a.boundary + int64_t(bh) * ((a.n - 1) / 32) * a.n : nullptr;
-        const float* lut = a.lut + int64_t(h) * a.lut_stride;
-        const SideIndex keys{a.keys.entries + int64_t(bh) * a.n, a.keys.starts + int64_t(bh) * (BUCKETS + 1)};
-        // A light and a heavy row block per task keep the causal work per task constant.
-        for (int side = 0; side < 2; ++side) {
-            const int row0 = (side ? blocks - 1 - pair : pair) * BLOCK_ROWS + warp * OWN;
-            const int row = row0 + group;
-            float acc[VPL], maximum = 0.f, denominator = 1.f;
+    __device__ __forceinline__ void begin(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active) {
+        maximum = 0.f;
+        denominator = 1.f;
 #pragma unroll
-            for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
-            if (active) {
-                float query[RPL];
+        for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
 #pragma unroll
-                for (int c = 0; c < RPL; ++c) query[c] = 0.f;
-                if (has_r) load_bf16<RPL>(a.sq + (vec0 + int64_t(row) * a.heads) * R + part * RPL, query);
-                const int searched = row0 + (lane & (OWN - 1));
-                SearchRow search;
-                search.label = __ldg(iq + searched);
-                search.previous = searched ? __ldg(iq + searched - 1) : 0;
-                partner_range<true>(keys, search.label, searched, search.cursor, search.end);
-                while (__ballot_sync(FULL, lane < OWN && search.cursor < search.end)) {
-                    __syncwarp();
-                    const int queued = find_partners<true, false>(queue, keys.entries, iq, ik, boundary, lut, nullptr,
-                                                                  nullptr, a.n, row0, search, lane);
-                    __syncwarp();
-                    const int mine = __shfl_sync(FULL, queued, group);
-                    const int rounds = __reduce_max_sync(FULL, mine);
-                    drain_partners<RPL, VPL>(
-                        queue->position[group], mine, rounds, shared.ring + warp,
-                        a.sk + vec0 * R + part * RPL, int64_t(a.heads) * R, has_r, a.v + vec0 * DV + part * VPL,
-                        int64_t(a.heads) * DV, lane, [&](bool live, int slot, const float(&key)[RPL], const float(&value)[VPL]) {
-                            float partial = 0.f;
-                            if (live) {
+        for (int c = 0; c < 8; ++c) query[c] = 0.f;
+        if (active && has_r) load_bf16<8>(a.sq + (ctx.vec0 + int64_t(row) * ctx.heads) * R + part * 8, query);
+    }
+    __device__ __forceinline__ void pair(bool live, float x, float, const float (&key)[8], const float (&value)[VPL]) {
+        float partial = 0.f;
+        if (live) {
 #pragma unroll
-                                for (int c = 0; c < RPL; ++c) partial = fmaf(query[c], key[c], partial);
-                            }
-                            const float s = group_sum(partial);
-                            if (live) {
-                                const float x = queue->weight[group][slot];
-                                if (x > maximum) {
-                                    const float alpha = ex2(maximum - x);
-                                    denominator *= alpha;
+            for (int c = 0; c < 8; ++c) partial = fmaf(query[c], key[c], partial);
+        }
+        const float s = group_sum(partial);
+        if (live) {
+            if (x > maximum) {
+                const float alpha = ex2(maximum - x);
+                denominator *= alpha;
 #pragma unroll
-                                    for (int c = 0; c < VPL; ++c) acc[c] *= alpha;
-                                    maximum = x;
-                                }
-                                const float p = ex2(x - maximum);
-                                denominator += p;
-                                const float weight = p * s;
-#pragma unroll
-                                for (int c = 0; c < VPL; ++c) acc[c] = fmaf(weight, value[c], acc[c]);
-                            }
-                        });
-                }
+                for (int c = 0; c < VPL; ++c) acc[c] *= alpha;
+                maximum = x;
             }
-            float normalizer = 0.f;
-            if (active) {
-                const float inverse = 1.f / denominator;
+            const float p = ex2(x - maximum);
+            denominator += p;
+            const float weight = p * s;
 #pragma unroll
-                for (int c = 0; c < VPL; ++c) acc[c] *= inverse;
-                normalizer = maximum + log2f(denominator);
-            }
-            store_bf16<VPL>(a.out + (vec0 + int64_t(row) * a.heads) * DV + part * VPL, acc);
-            if (part == 0) a.lse2[int64_t(bh) * a.n + row] = normalizer;
+            for (int c = 0; c < VPL; ++c) acc[c] = fmaf(weight, value[c], acc[c]);
         }
     }
-}
+    __device__ __forceinline__ void finish(const Args& a, const RowContext& ctx, int row, int part, bool, bool active) {
+        float normalizer = 0.f;
+        if (active) {
+            const float inverse = 1.f / denominator;
+#pragma unroll
+            for (int c = 0; c < VPL; ++c) acc[c] *= inverse;
+            normalizer = maximum + log2f(denominator);
+        }
+        store_bf16<VPL>(a.out + (ctx.vec0 + int64_t(row) * ctx.heads) * DV + part * VPL, acc);
+        if (part == 0) a.lse2_out[int64_t(ctx.bh) * ctx.n + row] = normalizer;
+    }
+};
 
 int device_sm_count() {
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     return sms;
-}
-
-template <int R, int DV>
-static cudaError_t launch_forward_variant(const ForwardArgs& args, int ctas, cudaStream_t stream) {
-    auto kernel = hard_forward_kernel<R, DV>;
-    const int shared = sizeof(ForwardShared<R, DV>);
-    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
-    if (status != cudaSuccess) return status;
-    int resident = 1;
-    status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, WARPS * 32, shared);
-    if (status != cudaSuccess) return status;
-    int grid = ctas ? ctas : device_sm_count() * (resident > 0 ? resident : 1);
-    if (grid > args.tasks) grid = args.tasks;
-    kernel<<<grid, WARPS * 32, shared, stream>>>(args);
-    return cudaGetLastError();
 }
 
 size_t hard_forward_workspace_bytes(int batch, int heads, int n) { return index_bytes(batch * heads, n, 1); }
@@ -163,11 +102,16 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
     const int batch_heads = shape.batch * shape.heads;
     cudaError_t status = launch_build_index(ik, batch_heads, shape.n, workspace, 0, 1, stream);
     if (status != cudaSuccess) return status;
-    ForwardArgs args{sq, sk, v, iq, ik, boundary, hard, lut, side_index(workspace, batch_heads, shape.n, 0, 1),
-                     out, lse2, shape.batch, shape.heads, shape.n, lut_stride,
-                     batch_heads * (shape.n / BLOCK_ROWS / 2)};
+    RowsArgs args{};
+    args.sq = sq; args.sk = sk; args.v = v;
+    args.iq = iq; args.ik = ik; args.boundary = boundary; args.hard = hard;
+    args.lut = lut;
+    args.index = side_index(workspace, batch_heads, shape.n, 0, 1);
+    args.out = out; args.lse2_out = lse2;
+    args.batch = shape.batch; args.heads = shape.heads; args.n = shape.n; args.lut_stride = lut_stride;
+    args.tasks = batch_heads * (shape.n / TASK_ROWS);
 #define DISM_CASE(RR, VV) \
-    if (shape.r == RR && shape.dv == VV) return launch_forward_variant<RR, VV>(args, ctas, stream);
+    if (shape.r == RR && shape.dv == VV) return launch_rows_kernel<ForwardPolicy<RR, VV>>(args, ctas, stream);
     DISM_CASE(16, 32) DISM_CASE(16, 64) DISM_CASE(16, 128)
     DISM_CASE(32, 32) DISM_CASE(32, 64) DISM_CASE(32, 128)
 #undef DISM_CASE
