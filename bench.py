@@ -28,9 +28,17 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SHAPE = dict(batch=8, heads=16, n=8192, d=64, r=32, dv=64, vocab=512)
-FWD_BYTES = 396   # per position: labels 8, sq+sk 128, v 128, out 128, lse2 4
-BWD_BYTES = 716   # per position: sq,sk 128 + v,dO 256 + labels 8 + lse2 4 read; dsq 128, dsk 64, dv 128 written
-LABEL_BYTES = 264  # per position: q,k rows 256 read, two labels 8 written
+# Algorithmic bytes per query position of each kernel launch (inputs read once, outputs written once).
+KERNEL_BYTES = {
+    'labels': 132,               # one bf16 row of 64 read, one label written (one launch per tensor)
+    'hard_forward': 396,         # labels 8, sq+sk 128, v 128 read; out 128, lse2 4 written
+    'hard_backward_query': 524,  # sq,sk 128, v,dO 256, labels 8, lse2 4 read; dsq (f32) 128 written
+    'hard_backward_key': 588,    # the same reads; dsk 64, dv 128 written
+}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at the full shape, from the ncu captures
+# summarised under profiles/ (captured at batch 2 and scaled by 4: traffic grows with the rows).
+TRAFFIC = {}
+STEP_BYTES = 2 * 132 + 396 + 716  # whole path: two label launches, forward, backward (inputs counted once)
 
 
 def measured_peak():
@@ -160,10 +168,22 @@ def run_ours(args):
         kernel_launches = launches[0]
         stage_ms = np.array([[a.elapsed_time(b) for a, b in zip(e, e[1:])] for e in stages]).mean(0)
 
+        # per-kernel device times: K more steps with the library's event timing switched on
+        from dism_b200 import _lib
+        _lib.load().dism_profile_enable(1)
+        for _ in range(args.steps):
+            step(resident)
+        torch.cuda.synchronize()
+        kernel_ms = {}
+        for name, ms in _lib.kernel_timings():
+            kernel_ms.setdefault(name, []).append(ms)
+        _lib.load().dism_profile_enable(0)
+        kernel_ms = {name: float(np.mean(v)) for name, v in kernel_ms.items()}
         if args.kernels_only:
             if rank == 0:
                 print(json.dumps({'profiling_case': True, 'batch': s['batch'], 'ms_per_step': elapsed_ms / args.steps,
-                                  'stage_ms': dict(zip(('labels', 'forward', 'backward'), map(float, stage_ms)))}))
+                                  'stage_ms': dict(zip(('labels', 'forward', 'backward'), map(float, stage_ms))),
+                                  'kernel_ms': kernel_ms}))
             return
         # end to end: pinned host inputs in, results out, every step
         copy_names = ('q', 'k', 'sq', 'sk', 'v', 'dout')
@@ -200,8 +220,8 @@ def run_ours(args):
     if rank == 0:
         peak, peak_kind = measured_peak()
         ms_per_step = elapsed_ms / args.steps
-        forward_ms = float(stage_ms[1])
-        achieved = FWD_BYTES * positions / (forward_ms * 1e-3) / 1e9
+        dominant = max(KERNEL_BYTES, key=lambda name: kernel_ms.get(name, 0.))
+        achieved = KERNEL_BYTES[dominant] * positions / (kernel_ms[dominant] * 1e-3) / 1e9
         line = {
             'metric': 'DISM fwd+bwd query-positions/s (labels + hard forward + hard backward)',
             'value': positions * world / (ms_per_step * 1e-3), 'unit': 'positions/s', 'n_gpus': world,
@@ -211,15 +231,17 @@ def run_ours(args):
             'config': {'workload': f"training shape B{s['batch']} H16 N8192 D64 R32 DV64 V512 per GPU, all rows hard, tau 0.5",
                        'parallelism': f'heads sharded, 16 heads per GPU x {world}, no collective',
                        'l2': 'inputs per step (671 MB) exceed L2'},
-            'stage_ms': {'labels': float(stage_ms[0]), 'forward': forward_ms, 'backward': float(stage_ms[2])},
+            'stage_ms': {'labels': float(stage_ms[0]), 'forward': float(stage_ms[1]), 'backward': float(stage_ms[2])},
+            'kernel_ms': kernel_ms,
             'per_gpu_value': positions / (ms_per_step * 1e-3),
             'e2e': {'value': positions * world / (e2e_ms / e2e_steps * 1e-3), 'unit': 'positions/s',
                     'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'steps': e2e_steps},
             'gpu_launches': kernel_launches,
             'clocks': clocks.summary(),
-            'roofline': {'bound': 'hbm', 'kernel': 'hard_forward_kernel<32,64>', 'achieved': achieved, 'peak': peak,
-                         'unit': 'GB/s', 'frac': achieved / peak, 'peak_kind': peak_kind, 'traffic': None,
-                         'algorithmic_bytes_per_launch': FWD_BYTES * positions},
+            'roofline': {'bound': 'hbm', 'kernel': dominant, 'achieved': achieved, 'peak': peak,
+                         'unit': 'GB/s', 'frac': achieved / peak, 'peak_kind': peak_kind, 'traffic': TRAFFIC.get(dominant),
+                         'algorithmic_bytes_per_launch': KERNEL_BYTES[dominant] * positions,
+                         'whole_step_frac': STEP_BYTES * positions / (ms_per_step * 1e-3) / 1e9 / peak},
             'cpu_baseline': cpu_baseline() if world == 1 else None,
         }
         print(json.dumps(line))
@@ -227,33 +249,41 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def cpu_sample(heads, threads, seed=0):
-    """Time the CPU port on `heads` (batch, head) slices of the benchmark shape; returns seconds."""
+def cpu_inputs(heads, seed=0):
+    """Synthetic operands of `heads` (batch, head) slices of the benchmark shape, as numpy arrays."""
     from oracle import dism_oracle as o
     s = SHAPE
     rng = np.random.default_rng(seed)
     b, n = 1, s['n']
     f = lambda *shape: o.bf16_round(rng.standard_normal(shape).astype(np.float32))
-    q, k = f(b, n, heads, s['d']), f(b, n, heads, s['d'])
-    eq, ek = f(heads, s['vocab'], s['d']), f(heads, s['vocab'], s['d'])
-    sq, sk = f(b, n, heads, s['r']) * np.float32(.25), f(b, n, heads, s['r']) * np.float32(.25)
-    v, dout = f(b, n, heads, s['dv']), f(b, n, heads, s['dv'])
-    tau, hard = np.full(heads, .5, np.float32), np.ones((b, heads), bool)
+    silu = lambda x: o.bf16_round((x / (1 + np.exp(-x))).astype(np.float32))
+    return dict(q=f(b, n, heads, s['d']), k=f(b, n, heads, s['d']),
+                eq=silu(rng.standard_normal((heads, s['vocab'], s['d']))),
+                ek=silu(rng.standard_normal((heads, s['vocab'], s['d']))),
+                sq=silu(rng.standard_normal((b, n, heads, s['r']))) * np.float32(.5),
+                sk=silu(rng.standard_normal((b, n, heads, s['r']))) * np.float32(.5),
+                v=f(b, n, heads, s['dv']), dout=f(b, n, heads, s['dv']),
+                tau=np.full(heads, .5, np.float32), hard=np.ones((b, heads), bool))
+
+
+def cpu_sample(x, threads):
+    """Time the CPU port on prepared operands; returns seconds per stage (inputs are not timed)."""
+    from oracle import dism_oracle as o
     # the discretiser on the CPU side is a plain fp32 GEMM + argmax (what the reference's torch path does)
     t0 = time.perf_counter()
     torch.set_num_threads(threads)
-    iq = torch.argmax(torch.einsum('bnhd,hvd->bnhv', torch.from_numpy(q), torch.from_numpy(eq)), -1)
-    ik = torch.argmax(torch.einsum('bnhd,hvd->bnhv', torch.from_numpy(k), torch.from_numpy(ek)), -1)
+    iq = torch.argmax(torch.einsum('bnhd,hvd->bnhv', torch.from_numpy(x['q']), torch.from_numpy(x['eq'])), -1)
+    ik = torch.argmax(torch.einsum('bnhd,hvd->bnhv', torch.from_numpy(x['k']), torch.from_numpy(x['ek'])), -1)
     iq, ik = [t.transpose(1, 2).contiguous().int().numpy() for t in (iq, ik)]
     t1 = time.perf_counter()
-    o.forward(sq, sk, v, iq, ik, hard, tau, threads=threads)
+    o.forward(x['sq'], x['sk'], x['v'], iq, ik, x['hard'], x['tau'], threads=threads)
     t2 = time.perf_counter()
-    o.backward(sq, sk, v, dout, iq, ik, hard, tau, threads=threads)
+    o.backward(x['sq'], x['sk'], x['v'], x['dout'], iq, ik, x['hard'], x['tau'], threads=threads)
     t3 = time.perf_counter()
     native = None
     if o.reference_lib() is not None:
         t = time.perf_counter()
-        o.reference_forward(sq[0, :, 0], sk[0, :, 0], v[0, :, 0], iq[0, 0], ik[0, 0], .5)
+        o.reference_forward(x['sq'][0, :, 0], x['sk'][0, :, 0], x['v'][0, :, 0], iq[0, 0], ik[0, 0], .5)
         native = time.perf_counter() - t
     return dict(labels=t1 - t0, forward=t2 - t1, backward=t3 - t2, native_forward_one_head=native)
 
@@ -261,12 +291,12 @@ def cpu_sample(heads, threads, seed=0):
 def cpu_baseline(heads=None):
     cores = os.cpu_count() or 1
     heads = heads or max(cores, 8)
-    cpu_sample(min(heads, 2), cores)  # warm caches and the thread pool
-    t = cpu_sample(heads, cores)
+    cpu_sample(cpu_inputs(2), cores)  # warm caches and the thread pool
+    t = cpu_sample(cpu_inputs(heads), cores)
     total = t['labels'] + t['forward'] + t['backward']
     return {'value': heads * SHAPE['n'] / total, 'unit': 'positions/s', 'cores': cores, 'kind': 'port',
             'sample': f'{heads} of the 128 (batch, head) slices at N=8192, all {cores} host threads, '
-                      f'oracle C port (sparse-aware dense recurrence) + torch fp32 argmax for labels',
+                      f'oracle C port (dense L recurrence, weights only where labels match) + torch fp32 argmax for labels',
             'seconds': {k: v for k, v in t.items() if v is not None}}
 
 
@@ -276,13 +306,14 @@ def run_reference(args):
         return
     cores = os.cpu_count() or 1
     heads = max(cores, 8)
+    small, inputs = cpu_inputs(2), cpu_inputs(heads)
     for _ in range(args.warmup):
-        cpu_sample(2, cores)
-    start = time.perf_counter()
-    native = []
+        cpu_sample(small, cores)
+    native, elapsed = [], 0.
     for step in range(args.steps):
-        native.append(cpu_sample(heads, cores, seed=step)['native_forward_one_head'])
-    elapsed = time.perf_counter() - start
+        t = cpu_sample(inputs, cores)
+        elapsed += t['labels'] + t['forward'] + t['backward']
+        native.append(t['native_forward_one_head'])
     value = heads * SHAPE['n'] * args.steps / elapsed
     base = {'value': value, 'unit': 'positions/s', 'cores': cores, 'kind': 'port',
             'sample': f'each step = {heads} of the 128 (batch, head) slices at N=8192 on all {cores} host threads; '

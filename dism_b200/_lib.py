@@ -20,6 +20,9 @@ SIGNATURES = {
     'dism_hard_backward_workspace': (_Z, [_I, _I, _I, _I]),
     'dism_hard_backward': (_I, [_P] * 9 + [_I, _P] + [_I] * 6 + [_P, _P, _P, _P, _P, _Z, _P]),
     'dism_longest_match_workspace': (_Z, [_I, _I]),
+    'dism_profile_enable': (_I, [_I]),
+    'dism_profile_count': (_I, []),
+    'dism_profile_read': (_I, [_I, _c.c_char_p, _I, _c.POINTER(_c.c_float)]),
     'dism_longest_match': (_I, [_P, _I, _I, _P, _P, _P, _P, _Z, _P]),
 }
 
@@ -44,3 +47,13 @@ def check(status):
     """Turn a non-zero status of the last call into RuntimeError with the library's message."""
     if status:
         raise RuntimeError(load().dism_last_error().decode())
+
+
+def kernel_timings():
+    """Records collected since dism_profile_enable(1): list of (kernel name, milliseconds)."""
+    lib, out = load(), []
+    name, ms = ctypes.create_string_buffer(64), ctypes.c_float()
+    for index in range(lib.dism_profile_count()):
+        check(lib.dism_profile_read(index, name, 64, ctypes.byref(ms)))
+        out.append((name.value.decode(), ms.value))
+    return out

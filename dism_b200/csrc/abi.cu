@@ -36,7 +36,53 @@ int check_dims(int r, int dv) {
 }
 }  // namespace
 
+// ---- optional per-kernel timing ---------------------------------------------------------------------
+namespace {
+constexpr int MAX_RECORDS = 256;
+struct Record {
+    cudaEvent_t start, stop;
+    char name[48];
+};
+bool timing_on = false;
+int record_count = 0, events_made = 0;
+Record records[MAX_RECORDS];
+}  // namespace
+
+namespace dism {
+KernelTimer::KernelTimer(const char* name, cudaStream_t s) : slot(-1), stream(s) {
+    if (!timing_on || record_count >= MAX_RECORDS) return;
+    slot = record_count++;
+    if (slot >= events_made) {
+        cudaEventCreate(&records[slot].start);
+        cudaEventCreate(&records[slot].stop);
+        events_made = slot + 1;
+    }
+    snprintf(records[slot].name, sizeof(records[slot].name), "%s", name);
+    cudaEventRecord(records[slot].start, stream);
+}
+KernelTimer::~KernelTimer() {
+    if (slot >= 0) cudaEventRecord(records[slot].stop, stream);
+}
+}  // namespace dism
+
 extern "C" {
+
+int dism_profile_enable(int on) {
+    timing_on = on != 0;
+    record_count = 0;
+    return DISM_OK;
+}
+
+int dism_profile_count(void) { return record_count; }
+
+int dism_profile_read(int index, char* name, int capacity, float* milliseconds) {
+    if (index < 0 || index >= record_count || !name || capacity <= 0 || !milliseconds)
+        return fail(DISM_EINVAL, "no such timing record");
+    if (cudaError_t status = cudaEventSynchronize(records[index].stop); status != cudaSuccess)
+        return cuda_status(status, "profile_read");
+    snprintf(name, size_t(capacity), "%s", records[index].name);
+    return cuda_status(cudaEventElapsedTime(milliseconds, records[index].start, records[index].stop), "profile_read");
+}
 
 const char* dism_last_error(void) { return last_error; }
 int dism_abi_version(void) { return 2; }

@@ -219,6 +219,15 @@ struct RowsArgs {
     int batch, heads, n, lut_stride, tasks;
 };
 
+// Optional per-kernel timing: when switched on through the C ABI, every launcher brackets its
+// kernels with CUDA events on the launch stream.  Off by default (one branch per launch).
+struct KernelTimer {
+    KernelTimer(const char* name, cudaStream_t stream);
+    ~KernelTimer();
+    int slot;
+    cudaStream_t stream;
+};
+
 // ---- launch-side entry points (defined in the .cu files, called from the C ABI) -------------
 struct HardShape {
     int batch, heads, n, r, dv;

@@ -35,6 +35,7 @@ struct QueryBackwardPolicy {
     static constexpr bool QUERY_MAJOR = true, EXTRA = true;
     static constexpr int R = R_, VPL = DV / 4;
     using Args = RowsArgs;
+    static const char* name() { return "hard_backward_query"; }
     static __device__ __forceinline__ const __nv_bfloat16* gather_a(const Args& a) { return a.sk; }
     static __device__ __forceinline__ const __nv_bfloat16* gather_b(const Args& a) { return a.v; }
 
@@ -97,6 +98,7 @@ struct KeyBackwardPolicy {
     static constexpr bool QUERY_MAJOR = false, EXTRA = false;
     static constexpr int R = R_, VPL = DV / 4;
     using Args = RowsArgs;
+    static const char* name() { return "hard_backward_key"; }
     static __device__ __forceinline__ const __nv_bfloat16* gather_a(const Args& a) { return a.sq; }
     static __device__ __forceinline__ const __nv_bfloat16* gather_b(const Args& a) { return a.dout; }
 
@@ -179,7 +181,10 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     if (status != cudaSuccess) return status;
     float* rows = reinterpret_cast<float*>(static_cast<char*>(workspace) + index_bytes(batch_heads, shape.n, 2));
     float* dlut = rows + size_t(batch_heads) * shape.n;
-    dlog_weights_kernel<<<dim3((lut_stride + 255) / 256, shape.heads), 256, 0, stream>>>(lut, dlut, lut_stride);
+    {
+        KernelTimer timer("dlog_weights", stream);
+        dlog_weights_kernel<<<dim3((lut_stride + 255) / 256, shape.heads), 256, 0, stream>>>(lut, dlut, lut_stride);
+    }
     RowsArgs args{};
     args.sq = sq; args.sk = sk; args.v = v; args.dout = dout;
     args.iq = iq; args.ik = ik; args.boundary = boundary; args.hard = hard;
@@ -200,6 +205,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     DISM_CASE(32, 32) DISM_CASE(32, 64) DISM_CASE(32, 128)
 #undef DISM_CASE
     if (status != cudaSuccess) return status;
+    KernelTimer timer("tau_reduce", stream);
     tau_reduce_kernel<<<shape.heads, 1024, 0, stream>>>(rows, dtau, shape.batch, shape.heads, shape.n);
     return cudaGetLastError();
 }

@@ -28,6 +28,7 @@ __global__ void log_weights_kernel(const float* __restrict__ tau, float* __restr
 }
 
 cudaError_t launch_log_weights(const float* tau, int heads, int n, float* lut, cudaStream_t stream) {
+    KernelTimer timer("log_weights", stream);
     log_weights_kernel<<<dim3((n + 256) / 256, heads), 256, 0, stream>>>(tau, lut, n + 1);
     return cudaGetLastError();
 }
@@ -37,6 +38,7 @@ struct ForwardPolicy {
     static constexpr bool QUERY_MAJOR = true, EXTRA = false;
     static constexpr int R = R_, VPL = DV / 4;
     using Args = RowsArgs;
+    static const char* name() { return "hard_forward"; }
     static __device__ __forceinline__ const __nv_bfloat16* gather_a(const Args& a) { return a.sk; }
     static __device__ __forceinline__ const __nv_bfloat16* gather_b(const Args& a) { return a.v; }
 

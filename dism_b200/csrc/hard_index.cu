@@ -83,6 +83,7 @@ SideIndex side_index(void* workspace, int batch_heads, int n, int side, int side
 cudaError_t launch_build_index(const int* labels, int batch_heads, int n, void* workspace, int side, int sides,
                                cudaStream_t stream) {
     SideIndex index = side_index(workspace, batch_heads, n, side, sides);
+    KernelTimer timer("build_index", stream);
     build_index_kernel<<<batch_heads, INDEX_THREADS, 0, stream>>>(labels, n, const_cast<int2*>(index.entries),
                                                                   const_cast<int*>(index.starts));
     return cudaGetLastError();

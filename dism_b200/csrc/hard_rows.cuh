@@ -215,7 +215,10 @@ cudaError_t launch_rows_kernel(const typename Policy::Args& args, int ctas, cuda
     if (status != cudaSuccess) return status;
     int grid = ctas ? ctas : device_sm_count() * (resident > 0 ? resident : 1);
     if (grid > args.tasks) grid = args.tasks;
-    kernel<<<grid, WARPS * 32, shared, stream>>>(args);
+    {
+        KernelTimer timer(Policy::name(), stream);
+        kernel<<<grid, WARPS * 32, shared, stream>>>(args);
+    }
     return cudaGetLastError();
 }
 

@@ -39,6 +39,7 @@ cudaError_t launch_hard_summary(const int* iq, const int* ik, const uint8_t* har
     int64_t blocks = (total + 255) / 256;
     const int64_t cap = ctas ? ctas : int64_t(device_sm_count()) * 32;
     if (blocks > cap) blocks = cap;
+    KernelTimer timer("hard_summary", stream);
     hard_summary_kernel<<<int(blocks), 256, 0, stream>>>(iq, ik, hard, batch * heads, n, summary);
     return cudaGetLastError();
 }
@@ -72,6 +73,7 @@ cudaError_t launch_hard_chunk(const int* summary, int* boundary, int batch_heads
     int64_t blocks = (int64_t(batch_heads) * checkpoints * 32 + 127) / 128;
     const int64_t cap = int64_t(device_sm_count()) * 64;
     if (blocks > cap) blocks = cap;
+    KernelTimer timer("hard_chunk", stream);
     hard_chunk_kernel<<<int(blocks), 128, 0, stream>>>(summary, boundary, batch_heads, n);
     return cudaGetLastError();
 }
@@ -126,6 +128,7 @@ cudaError_t launch_longest_match(const int* streams, int batch, int n, int* end,
     const int64_t cap = int64_t(device_sm_count()) * 8;
     if (blocks > cap) blocks = cap;
     if (!blocks) return cudaSuccess;
+    KernelTimer timer("longest_match", stream);
     longest_match_kernel<<<int(blocks), WARPS * 32, 0, stream>>>(streams, side_index(workspace, batch, n, 0, 1), batch,
                                                                  n, end, length, next);
     return cudaGetLastError();

@@ -82,6 +82,15 @@ size_t dism_longest_match_workspace(int batch, int n);
 int dism_longest_match(const int32_t *streams, int batch, int n, int32_t *end, int32_t *length,
                        int32_t *next, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Per-kernel device timing for benchmarks (no counterpart in the reference, which times whole
+ * calls with CUDA events from Python).  dism_profile_enable(1) clears the records and makes every
+ * later launch record CUDA events around each kernel on its launch stream;
+ * dism_profile_read(i, ...) waits for record i and returns its kernel name and milliseconds.
+ * Process-wide and not thread-safe: switch it on from one thread, around the calls to be timed. */
+int dism_profile_enable(int on);
+int dism_profile_count(void);
+int dism_profile_read(int index, char *name, int capacity, float *milliseconds);
+
 #ifdef __cplusplus
 }
 #endif
