@@ -110,15 +110,6 @@ __device__ __forceinline__ int lower_bound_position(const int2* __restrict__ ent
     return lo;
 }
 
-// Per-warp queue of the partners found in one round: up to 32 per owned row, in ascending
-// position, each with its log2 weight (and, for the query-major backward, its dlog weight).
-template <bool EXTRA>
-struct PairQueue {
-    int position[OWN][32];
-    float weight[OWN][32];
-    float extra[EXTRA ? OWN : 1][32];
-};
-
 // Range of the bucket of `label` that can hold causal partners of owner position `row`.
 template <bool QUERY_MAJOR>
 __device__ __forceinline__ void partner_range(const SideIndex& index, int label, int row, int& cursor, int& end) {
@@ -136,7 +127,7 @@ __device__ __forceinline__ void partner_range(const SideIndex& index, int label,
 // bf16 on every lane) are gathered with cp.async into a
 // small shared-memory ring that each lane reads back itself, so several pairs' loads are in
 // flight per lane group while earlier pairs are being accumulated.
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 
 __device__ __forceinline__ void cp_async16(void* shared, const void* global) {
     const unsigned target = static_cast<unsigned>(__cvta_generic_to_shared(shared));

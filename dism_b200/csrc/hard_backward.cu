@@ -33,7 +33,7 @@ __global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __rest
 template <int R_, int DV>
 struct QueryBackwardPolicy {
     static constexpr bool QUERY_MAJOR = true, EXTRA = true;
-    static constexpr int R = R_, VPL = DV / 4;
+    static constexpr int R = R_, VPL = DV / 4, MIN_CTAS = 2;
     using Args = RowsArgs;
     static const char* name() { return "hard_backward_query"; }
     static __device__ __forceinline__ const __nv_bfloat16* gather_a(const Args& a) { return a.sk; }
@@ -96,7 +96,7 @@ struct QueryBackwardPolicy {
 template <int R_, int DV>
 struct KeyBackwardPolicy {
     static constexpr bool QUERY_MAJOR = false, EXTRA = false;
-    static constexpr int R = R_, VPL = DV / 4;
+    static constexpr int R = R_, VPL = DV / 4, MIN_CTAS = 2;
     using Args = RowsArgs;
     static const char* name() { return "hard_backward_key"; }
     static __device__ __forceinline__ const __nv_bfloat16* gather_a(const Args& a) { return a.sq; }

@@ -36,7 +36,7 @@ cudaError_t launch_log_weights(const float* tau, int heads, int n, float* lut, c
 template <int R_, int DV>
 struct ForwardPolicy {
     static constexpr bool QUERY_MAJOR = true, EXTRA = false;
-    static constexpr int R = R_, VPL = DV / 4;
+    static constexpr int R = R_, VPL = DV / 4, MIN_CTAS = DV <= 64 ? 3 : 2;
     using Args = RowsArgs;
     static const char* name() { return "hard_forward"; }
     static __device__ __forceinline__ const __nv_bfloat16* gather_a(const Args& a) { return a.sk; }

@@ -24,91 +24,110 @@ struct RowContext {  // what a task's rows share
 };
 
 struct RowsShared {
-    int order[TASK_ROWS];
+    int order[TASK_ROWS];                       // local row numbers, heaviest first
+    int label[TASK_ROWS], previous[TASK_ROWS];  // own-side labels of the row and of the row before it
+    int first[TASK_ROWS], last[TASK_ROWS];      // the row's bucket range in the partner index
     int bin_count[LOAD_BINS], bin_start[LOAD_BINS];
     int next_group;
 };
 
-// lane r < OWN carries the search state of the warp's r-th row
+// Search state of one owned row, replicated in the four lanes of its group.
 struct SearchRow {
     int row;
     int label;     // label of the owned row
     int previous;  // label of the owned side at row - 1 (the diagonal predecessor's own-side label)
     int cursor, end;
+    int queued;    // partners waiting in the group's queue
 };
 
-// One round of partner search for the warp's OWN rows.  Each row reads its next 32 bucket
-// entries (all eight loads are issued before any is used), keeps the causal entries with its
-// label, and queues them in ascending position with the log2 weight of their run length
-// (minus the partner's log2 normaliser when `shift_by_position` is given).  Returns in lane r
-// the number queued for row r.  QUERY_MAJOR: owned rows are queries and partners are keys;
-// otherwise owned rows are keys and partners are queries.
+constexpr int QUEUE_DEPTH = 48;  // a scan step adds at most 32 partners and runs only with room for them
+
+// Per-warp queues: one per owned row, partners in ascending position with their log2 weight
+// (and, for the query-major backward, the dlog weight).
+template <bool EXTRA>
+struct PartnerQueues {
+    int position[OWN][QUEUE_DEPTH];
+    float weight[OWN][QUEUE_DEPTH];
+    float extra[EXTRA ? OWN : 1][QUEUE_DEPTH];
+};
+
+// One scan step of a lane group: its row's next 32 bucket entries, eight per lane.  Entries with
+// the row's label on the causal side are appended to the group's queue in ascending position.
+// Only positions are recorded here; weights are filled in by finish_partners() for the whole
+// queue at once, so that the dependent loads of many partners overlap.
+// Every lane of the warp calls this (the prefix sums use full-warp shuffles); `scan` says whether
+// this lane's group takes part.
 template <bool QUERY_MAJOR, bool EXTRA>
-__device__ __forceinline__ int find_partners(PairQueue<EXTRA>* queue, const RowContext& ctx,
-                                             const float* __restrict__ shift_by_position, SearchRow& mine, int lane) {
+__device__ __forceinline__ void scan_partners(PartnerQueues<EXTRA>* queue, const int2* __restrict__ entries,
+                                              SearchRow& mine, bool scan, int group, int part, int lane) {
+    int2 entry[8];
+    const int base = mine.cursor + part * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        entry[e] = make_int2(QUERY_MAJOR ? 0x7fffffff : -1, 0);
+        if (scan && base + e < mine.end) entry[e] = __ldg(entries + base + e);
+    }
+    unsigned hits = 0;
+    bool beyond = false;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const bool inside = scan && base + e < mine.end;
+        const bool causal = QUERY_MAJOR ? entry[e].x <= mine.row : entry[e].x >= mine.row;
+        if (inside && causal && entry[e].y == mine.label) hits |= 1u << e;
+        if (QUERY_MAJOR && inside && !causal) beyond = true;  // keys ascend: nothing causal follows
+    }
+    const int count = __popc(hits);
+    const int first = lane & ~3;
+    const int c0 = __shfl_sync(FULL, count, first), c1 = __shfl_sync(FULL, count, first + 1);
+    const int c2 = __shfl_sync(FULL, count, first + 2), c3 = __shfl_sync(FULL, count, first + 3);
+    const unsigned ended = __ballot_sync(FULL, beyond);
+    int slot = mine.queued + (part > 0 ? c0 : 0) + (part > 1 ? c1 : 0) + (part > 2 ? c2 : 0);
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+        if (hits & (1u << e)) queue->position[group][slot++] = entry[e].x;
+    if (scan) {
+        mine.queued += c0 + c1 + c2 + c3;
+        mine.cursor = ((ended >> first) & 15u) ? mine.end : min(mine.cursor + 32, mine.end);
+    }
+}
+
+// Fills in the weights of the group's queued partners from `from` on, four partners at a time
+// (one per lane).  The run is longer than one only when the diagonal predecessor matches too;
+// that lane then walks it.
+template <bool QUERY_MAJOR, bool EXTRA>
+__device__ __forceinline__ void finish_partners(PartnerQueues<EXTRA>* queue, const RowContext& ctx,
+                                                const float* __restrict__ shift_by_position, const SearchRow& mine,
+                                                int from, int group, int part) {
     const int* other_side = QUERY_MAJOR ? ctx.ik : ctx.iq;
-    int2 entry[OWN];
-    bool valid[OWN];
-#pragma unroll
-    for (int r = 0; r < OWN; ++r) {
-        const int from = __shfl_sync(FULL, mine.cursor, r), to = __shfl_sync(FULL, mine.end, r);
-        valid[r] = from + lane < to;
-        entry[r] = make_int2(QUERY_MAJOR ? 0x7fffffff : -1, 0);
-        if (valid[r]) entry[r] = __ldg(ctx.index.entries + from + lane);
-    }
-    int neighbour[OWN];
-    float shift[OWN];
-    bool hit[OWN];
-#pragma unroll
-    for (int r = 0; r < OWN; ++r) {
-        const int row = __shfl_sync(FULL, mine.row, r), wanted = __shfl_sync(FULL, mine.label, r);
-        const bool causal = QUERY_MAJOR ? entry[r].x <= row : entry[r].x >= row;
-        hit[r] = valid[r] && causal && entry[r].y == wanted;
-        // the other side's label one step up the diagonal, and the partner's normaliser
-        neighbour[r] = 0;
-        shift[r] = 0.f;
-        if (hit[r] && entry[r].x > 0) neighbour[r] = __ldg(other_side + entry[r].x - 1);
-        if (hit[r] && shift_by_position) shift[r] = __ldg(shift_by_position + entry[r].x);
-        // keys ascend inside a bucket: a position beyond the row ends the row's search
-        const unsigned beyond = QUERY_MAJOR ? __ballot_sync(FULL, valid[r] && entry[r].x > row) : 0u;
-        const int from = __shfl_sync(FULL, mine.cursor, r), to = __shfl_sync(FULL, mine.end, r);
-        if (lane == r && from < to) mine.cursor = beyond ? to : from + 32;
-    }
     const float weight_one = __ldg(ctx.lut + 1), extra_one = EXTRA ? __ldg(ctx.dlut + 1) : 0.f;
-    int queued = 0;
-#pragma unroll
-    for (int r = 0; r < OWN; ++r) {
-        const int row = __shfl_sync(FULL, mine.row, r), previous = __shfl_sync(FULL, mine.previous, r);
+#pragma unroll 2
+    for (int slot = from + part; slot < mine.queued; slot += 4) {
+        const int position = queue->position[group][slot];
+        const int neighbour = position > 0 ? __ldg(other_side + position - 1) : 0;
+        const float shift = shift_by_position ? __ldg(shift_by_position + position) : 0.f;
         float weight = weight_one, extra = extra_one;
-        if (hit[r] && entry[r].x > 0 && row > 0 && neighbour[r] == previous) {  // the run is longer than one
-            const int i = QUERY_MAJOR ? row : entry[r].x, j = QUERY_MAJOR ? entry[r].x : row;
+        if (position > 0 && mine.row > 0 && neighbour == mine.previous) {
+            const int i = QUERY_MAJOR ? mine.row : position, j = QUERY_MAJOR ? position : mine.row;
             const int length = 1 + run_length(ctx.iq, ctx.ik, ctx.boundary, ctx.n, i - 1, j - 1);
             weight = __ldg(ctx.lut + length);
             if (EXTRA) extra = __ldg(ctx.dlut + length);
         }
-        const unsigned mask = __ballot_sync(FULL, hit[r]);
-        if (hit[r]) {
-            const int slot = __popc(mask & ((1u << lane) - 1u));
-            queue->position[r][slot] = entry[r].x;
-            queue->weight[r][slot] = weight - shift[r];
-            if (EXTRA) queue->extra[r][slot] = extra;
-        }
-        if (lane == r) queued = __popc(mask);
+        queue->weight[group][slot] = weight - shift;
+        if (EXTRA) queue->extra[group][slot] = extra;
     }
-    return queued;
 }
 
 template <class Policy>
 struct RowsKernelShared {
     RowsShared rows;
-    PairQueue<Policy::EXTRA> queue[WARPS];
+    PartnerQueues<Policy::EXTRA> queue[WARPS];
     GatherRing<8, Policy::VPL> ring[WARPS];
 };
 
-// Policy supplies: QUERY_MAJOR, EXTRA, VPL, R; Args with the common fields used below;
+// Policy supplies: QUERY_MAJOR, EXTRA, VPL, R, MIN_CTAS (resident CTAs per SM to compile for); Args with the common fields used below;
 // per-lane state with begin(), pair(), finish(); the two gathered tensors.
 template <class Policy>
-__global__ __launch_bounds__(WARPS * 32) void rows_kernel(const typename Policy::Args a) {
+__global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(const typename Policy::Args a) {
     constexpr bool QM = Policy::QUERY_MAJOR;
     constexpr int VPL = Policy::VPL, R = Policy::R;
     extern __shared__ __align__(16) unsigned char storage[];
@@ -145,10 +164,17 @@ __global__ __launch_bounds__(WARPS * 32) void rows_kernel(const typename Policy:
         const int my_row = block * TASK_ROWS + threadIdx.x;
         int bin = 0;
         if (active) {
-            const int bucket = bucket_of(__ldg(own_labels + my_row));
-            const int size = __ldg(ctx.index.starts + bucket + 1) - __ldg(ctx.index.starts + bucket);
+            // every thread prepares one row's search: labels and bucket range go to shared memory, so
+            // the lane groups start from there instead of from a chain of dependent global loads
+            const int label = __ldg(own_labels + my_row);
+            int first, last;
+            partner_range<QM>(ctx.index, label, my_row, first, last);
+            shared.rows.label[threadIdx.x] = label;
+            shared.rows.previous[threadIdx.x] = my_row ? __ldg(own_labels + my_row - 1) : 0;
+            shared.rows.first[threadIdx.x] = first;
+            shared.rows.last[threadIdx.x] = last;
             // about size * (causal share of the sequence) entries lie on the causal side
-            const int64_t estimate = int64_t(size) * (QM ? my_row + 1 : a.n - my_row) / a.n;
+            const int64_t estimate = int64_t(last - first) * (QM ? my_row + 1 : a.n - my_row) / a.n;
             bin = estimate <= 0 ? 0 : min(LOAD_BINS - 1, 32 - __clz(int(estimate)));
         }
         const int rank_in_bin = atomicAdd(&shared.rows.bin_count[bin], 1);
@@ -164,7 +190,7 @@ __global__ __launch_bounds__(WARPS * 32) void rows_kernel(const typename Policy:
             shared.rows.bin_start[LOAD_BINS - 1 - lane] = prefix - count;
         }
         __syncthreads();
-        shared.rows.order[shared.rows.bin_start[bin] + rank_in_bin] = my_row;
+        shared.rows.order[shared.rows.bin_start[bin] + rank_in_bin] = threadIdx.x;
         __syncthreads();
 
         // ---- warps pull groups of eight rows ----------------------------------------------------------
@@ -173,21 +199,30 @@ __global__ __launch_bounds__(WARPS * 32) void rows_kernel(const typename Policy:
             if (lane == 0) chosen = atomicAdd(&shared.rows.next_group, 1);
             chosen = __shfl_sync(FULL, chosen, 0);
             if (chosen >= TASK_ROWS / OWN) break;
-            const int row = shared.rows.order[chosen * OWN + group];  // the row this lane group accumulates
+            const int local = shared.rows.order[chosen * OWN + group];
+            const int row = block * TASK_ROWS + local;  // the row this lane group owns
             Policy state;
             state.begin(a, ctx, row, part, has_r, active);
             if (active) {
                 SearchRow search;
-                search.row = shared.rows.order[chosen * OWN + (lane & (OWN - 1))];
-                search.label = __ldg(own_labels + search.row);
-                search.previous = search.row ? __ldg(own_labels + search.row - 1) : 0;
-                partner_range<QM>(ctx.index, search.label, search.row, search.cursor, search.end);
-                while (__ballot_sync(FULL, lane < OWN && search.cursor < search.end)) {
+                search.row = row;
+                search.label = shared.rows.label[local];
+                search.previous = shared.rows.previous[local];
+                search.cursor = shared.rows.first[local];
+                search.end = shared.rows.last[local];
+                search.queued = 0;
+                for (;;) {
+                    // scan while some group can take 32 more; otherwise weigh and drain every queue
+                    const bool scan = search.cursor < search.end && search.queued <= QUEUE_DEPTH - 32;
+                    if (__ballot_sync(FULL, scan)) {
+                        scan_partners<QM, Policy::EXTRA>(queue, ctx.index.entries, search, scan, group, part, lane);
+                        continue;
+                    }
+                    if (!__ballot_sync(FULL, search.queued > 0)) break;
                     __syncwarp();
-                    const int queued = find_partners<QM, Policy::EXTRA>(queue, ctx, QM ? nullptr : ctx.lse2, search, lane);
+                    finish_partners<QM, Policy::EXTRA>(queue, ctx, QM ? nullptr : ctx.lse2, search, 0, group, part);
                     __syncwarp();
-                    const int mine = __shfl_sync(FULL, queued, group);
-                    const int rounds = __reduce_max_sync(FULL, mine);
+                    const int mine = search.queued, rounds = __reduce_max_sync(FULL, mine);
                     drain_partners<8, VPL>(
                         queue->position[group], mine, rounds, shared.ring + warp,
                         Policy::gather_a(a) + ctx.vec0 * R + part * 8, int64_t(a.heads) * R, has_r,
@@ -197,6 +232,8 @@ __global__ __launch_bounds__(WARPS * 32) void rows_kernel(const typename Policy:
                             const float extra = (Policy::EXTRA && live) ? queue->extra[group][slot] : 0.f;
                             state.pair(live, weight, extra, va, vb);
                         });
+                    search.queued = 0;
+                    __syncwarp();
                 }
             }
             state.finish(a, ctx, row, part, has_r, active);
