@@ -61,6 +61,22 @@ int dism_hard_readout(const void *sq, const void *sk, const void *v, const int32
                       int batch, int n, int heads, int r, int dv, int ctas, void *out, float *lse2,
                       void *workspace, size_t workspace_bytes, void *stream);
 
+/* The same readout for callers that cannot supply scratch memory (an operator hook that only gets its
+ * input and output buffers, a server whose memory pool already holds the whole GPU: cudaMalloc there
+ * serialises the device and may fail).  It has no counterpart in the reference.  The position index
+ * lives in a fixed array inside the library (DISM_READOUT_STATIC_BYTES, held on every GPU that loads
+ * the library until the process exits); the call allocates nothing.  Limits: the shape's index
+ * (B*H*N*8 + B*H*1028 bytes, rounded up to 256) must fit, otherwise DISM_EINVAL; all calls on a
+ * device share the array, so calls that overlap on the GPU race and must be serialised by the caller;
+ * the first call on each device resolves the array's address and should be made before any stream
+ * capture starts.  The message of a failing call is in dism_hard_readout_static_error(). */
+#define DISM_READOUT_STATIC_BYTES 2621440 /* 2.5 MiB: e.g. 32 (batch x head) rows of 8192 positions */
+int dism_hard_readout_static(const void *sq, const void *sk, const void *v, const int32_t *iq,
+                             const int32_t *ik, const uint8_t *hard, const int32_t *boundary,
+                             const float *lut, int lut_stride, int batch, int n, int heads, int r, int dv,
+                             int ctas, void *out, float *lse2, void *stream);
+const char *dism_hard_readout_static_error(void);
+
 /* Bytes of scratch dism_hard_backward needs for this shape. */
 size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride);
 
