@@ -3,7 +3,7 @@
 // How the hard kernels find their work.  A pair (query i, key j <= i) has non-zero weight only
 // when its labels are equal, so the kernels never visit the N^2/2 pairs.  A small prepass sorts
 // the positions of one side by (label bucket, position); the owner of a row then reads only the
-// bucket of its own label (about N/256 entries), keeps the entries with the same label on the
+// bucket of its own label (with 4096 buckets, almost always exactly the positions with that label), keeps the entries with the same label on the
 // causal side, and gets its matching partners already in ascending order.  Eight lane groups of
 // a warp each own one row and work through their queued partners together, so the per-pair
 // arithmetic (run length, table lookup, two short dot products, one axpy) runs eight pairs wide.
@@ -16,7 +16,7 @@ namespace dism {
 
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float LOG_ZERO = -1000000.f;  // LUT entry of length 0 (dism_v3/src/hard_forward.cu:15)
-constexpr int BUCKETS = 256;            // label buckets of the position index
+constexpr int BUCKETS = 4096;           // label buckets of the position index
 constexpr int OWN = 8;                  // rows per warp (one per group of four lanes)
 constexpr int WARPS = 8;                // warps per CTA
 constexpr int BLOCK_ROWS = WARPS * OWN;
@@ -68,9 +68,8 @@ __device__ __forceinline__ float group_sum(float x) {
 }
 
 __device__ __forceinline__ int bucket_of(int label) {
-    unsigned x = unsigned(label);
-    x ^= x >> 16;
-    x ^= x >> 8;
+    unsigned x = unsigned(label);  // labels below 4096 keep a bucket each
+    x ^= (x >> 12) ^ (x >> 24);
     return int(x & (BUCKETS - 1));
 }
 
@@ -115,11 +114,9 @@ template <bool QUERY_MAJOR>
 __device__ __forceinline__ void partner_range(const SideIndex& index, int label, int row, int& cursor, int& end) {
     const int bucket = bucket_of(label);
     const int lo = __ldg(index.starts + bucket), hi = __ldg(index.starts + bucket + 1);
-    cursor = lo;
-    end = hi;
-    // Keys are scanned from the bucket start until a position beyond the row shows up.  Queries
-    // start at the first position >= row; small buckets are simply scanned from their start.
-    if (!QUERY_MAJOR && hi - lo > 64) cursor = lower_bound_position(index.entries, lo, hi, row);
+    // positions ascend inside a bucket: keys up to the row, queries from the row on
+    cursor = QUERY_MAJOR ? lo : lower_bound_position(index.entries, lo, hi, row);
+    end = QUERY_MAJOR ? lower_bound_position(index.entries, lo, hi, row + 1) : hi;
 }
 
 // ---- gather ring -------------------------------------------------------------------------------

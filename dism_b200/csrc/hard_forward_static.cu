@@ -47,7 +47,7 @@ int dism_hard_readout_static(const void* sq, const void* sk, const void* v, cons
     const size_t needed = dism_hard_readout_workspace(batch, heads, n);
     if (needed > size_t(DISM_READOUT_STATIC_BYTES)) {
         snprintf(static_error, sizeof(static_error),
-                 "shape needs %zu bytes of index but the built-in scratch holds %zu (B*H*N*8 + B*H*1028 bytes must fit); "
+                 "shape needs %zu bytes of index but the built-in scratch holds %zu (B*H*N*16 + B*H*16388 bytes must fit); "
                  "use dism_hard_readout with a caller-owned workspace",
                  needed, size_t(DISM_READOUT_STATIC_BYTES));
         return DISM_EINVAL;

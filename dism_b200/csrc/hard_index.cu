@@ -1,55 +1,57 @@
 // Position index: the positions of one side of every (batch, head), sorted by
-// (label bucket, position) with a stable counting sort, one CTA per (batch, head).
+// (label bucket, position).  One CTA per (batch, head) runs a stable two-pass counting sort
+// (64 bins per pass, 4096 buckets in all); with that many buckets a bucket almost always holds a
+// single label, so a row's partners are one contiguous, position-ordered range of the index.
 #include "dism_common.cuh"
 
 namespace dism {
 
 constexpr int INDEX_THREADS = 1024;
+constexpr int PASS_BINS = 64;
+static_assert(PASS_BINS * PASS_BINS == BUCKETS, "two passes cover the bucket number");
 
-__global__ __launch_bounds__(INDEX_THREADS) void build_index_kernel(const int* __restrict__ labels, int n,
-                                                                    int2* __restrict__ entries,
-                                                                    int* __restrict__ starts) {
-    __shared__ int base[BUCKETS], total[BUCKETS];
-    __shared__ unsigned short counts[INDEX_THREADS / 32][BUCKETS];
+// One stable counting pass over n items of this (batch, head).  FIRST reads labels in position
+// order and sorts by the low six bucket bits; the second pass reads the first pass's entries and
+// sorts by the high six bits.
+template <bool FIRST>
+__device__ __forceinline__ void counting_pass(const int* __restrict__ labels, const int2* __restrict__ source,
+                                              int2* __restrict__ target, int n, int* base, int* total,
+                                              unsigned short (*counts)[PASS_BINS]) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    labels += int64_t(blockIdx.x) * n;
-    entries += int64_t(blockIdx.x) * n;
-    starts += int64_t(blockIdx.x) * (BUCKETS + 1);
-    if (tid < BUCKETS) total[tid] = 0;
+    if (tid < PASS_BINS) total[tid] = 0;
     __syncthreads();
-    for (int pos = tid; pos < n; pos += INDEX_THREADS) atomicAdd(&total[bucket_of(labels[pos])], 1);
+    for (int at = tid; at < n; at += INDEX_THREADS) {
+        const int bucket = bucket_of(FIRST ? labels[at] : source[at].y);
+        atomicAdd(&total[FIRST ? bucket & (PASS_BINS - 1) : bucket >> 6], 1);
+    }
     __syncthreads();
-    if (warp == 0) {  // exclusive scan of the 256 bucket sizes, 8 per lane
-        int local[BUCKETS / 32], sum = 0;
-#pragma unroll
-        for (int e = 0; e < BUCKETS / 32; ++e) { local[e] = sum; sum += total[lane * (BUCKETS / 32) + e]; }
-        int prefix = sum;
+    if (warp == 0) {  // exclusive scan of the 64 bin sizes, two per lane
+        const int a = total[2 * lane], b = total[2 * lane + 1];
+        int prefix = a + b;
 #pragma unroll
         for (int s = 1; s < 32; s <<= 1) {
-            int other = __shfl_up_sync(FULL, prefix, s);
+            const int other = __shfl_up_sync(FULL, prefix, s);
             if (lane >= s) prefix += other;
         }
-        prefix -= sum;
-#pragma unroll
-        for (int e = 0; e < BUCKETS / 32; ++e) {
-            base[lane * (BUCKETS / 32) + e] = prefix + local[e];
-            starts[lane * (BUCKETS / 32) + e] = prefix + local[e];
-        }
-        if (lane == 31) starts[BUCKETS] = n;
+        prefix -= a + b;
+        base[2 * lane] = prefix;
+        base[2 * lane + 1] = prefix + a;
     }
     __syncthreads();
     for (int chunk = 0; chunk < n; chunk += INDEX_THREADS) {
-        const int pos = chunk + tid;
-        const bool valid = pos < n;
-        const int label = valid ? labels[pos] : 0;
-        const int bucket = valid ? bucket_of(label) : BUCKETS;  // invalid lanes match only each other
-        for (int e = tid; e < (INDEX_THREADS / 32) * BUCKETS; e += INDEX_THREADS) (&counts[0][0])[e] = 0;
+        const int at = chunk + tid;
+        const bool valid = at < n;
+        int2 item = make_int2(0, 0);
+        if (valid) item = FIRST ? make_int2(at, labels[at]) : source[at];
+        const int bucket = bucket_of(item.y);
+        const int bin = valid ? (FIRST ? bucket & (PASS_BINS - 1) : bucket >> 6) : PASS_BINS;  // invalid lanes pair up only with each other
+        for (int e = tid; e < (INDEX_THREADS / 32) * PASS_BINS; e += INDEX_THREADS) (&counts[0][0])[e] = 0;
         __syncthreads();
-        const unsigned peers = __match_any_sync(FULL, bucket);
+        const unsigned peers = __match_any_sync(FULL, bin);
         const int rank = __popc(peers & ((1u << lane) - 1u));
-        if (valid && rank == 0) counts[warp][bucket] = (unsigned short)__popc(peers);
+        if (valid && rank == 0) counts[warp][bin] = (unsigned short)__popc(peers);
         __syncthreads();
-        if (tid < BUCKETS) {  // exclusive prefix over the warps, in position order
+        if (tid < PASS_BINS) {  // exclusive prefix over the warps, which are in input order
             int running = 0;
             for (int w = 0; w < INDEX_THREADS / 32; ++w) {
                 const int c = counts[w][tid];
@@ -59,15 +61,69 @@ __global__ __launch_bounds__(INDEX_THREADS) void build_index_kernel(const int* _
             total[tid] = running;
         }
         __syncthreads();
-        if (valid) entries[base[bucket] + counts[warp][bucket] + rank] = make_int2(pos, label);
+        if (valid) target[base[bin] + counts[warp][bin] + rank] = item;
         __syncthreads();
-        if (tid < BUCKETS) base[tid] += total[tid];
+        if (tid < PASS_BINS) base[tid] += total[tid];
         __syncthreads();
     }
 }
 
+__global__ __launch_bounds__(INDEX_THREADS) void build_index_kernel(const int* __restrict__ labels, int n,
+                                                                    int2* __restrict__ entries,
+                                                                    int2* __restrict__ scratch,
+                                                                    int* __restrict__ starts) {
+    __shared__ int base[PASS_BINS], total[PASS_BINS];
+    __shared__ unsigned short counts[INDEX_THREADS / 32][PASS_BINS];
+    __shared__ int histogram[BUCKETS];
+    __shared__ int warp_sum[INDEX_THREADS / 32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    labels += int64_t(blockIdx.x) * n;
+    entries += int64_t(blockIdx.x) * n;
+    scratch += int64_t(blockIdx.x) * n;
+    starts += int64_t(blockIdx.x) * (BUCKETS + 1);
+    // bucket starts: histogram of all 4096 buckets and its exclusive scan (four buckets per thread)
+    for (int e = tid; e < BUCKETS; e += INDEX_THREADS) histogram[e] = 0;
+    __syncthreads();
+    for (int at = tid; at < n; at += INDEX_THREADS) atomicAdd(&histogram[bucket_of(labels[at])], 1);
+    __syncthreads();
+    {
+        constexpr int PER = BUCKETS / INDEX_THREADS;
+        int local[PER], sum = 0;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) { local[e] = sum; sum += histogram[tid * PER + e]; }
+        int prefix = sum;
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+            const int other = __shfl_up_sync(FULL, prefix, s);
+            if (lane >= s) prefix += other;
+        }
+        if (lane == 31) warp_sum[warp] = prefix;
+        __syncthreads();
+        if (warp == 0) {
+            const int mine = warp_sum[lane];
+            int scan = mine;
+#pragma unroll
+            for (int s = 1; s < 32; s <<= 1) {
+                const int other = __shfl_up_sync(FULL, scan, s);
+                if (lane >= s) scan += other;
+            }
+            warp_sum[lane] = scan - mine;
+        }
+        __syncthreads();
+        const int before = warp_sum[warp] + prefix - sum;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) starts[tid * PER + e] = before + local[e];
+        if (tid == INDEX_THREADS - 1) starts[BUCKETS] = n;
+    }
+    __syncthreads();
+    counting_pass<true>(labels, nullptr, scratch, n, base, total, counts);
+    __syncthreads();
+    counting_pass<false>(nullptr, scratch, entries, n, base, total, counts);
+}
+
+// Per side: entries int2 [BH, N], sort scratch int2 [BH, N], starts int [BH, BUCKETS + 1].
 size_t index_bytes(int batch_heads, int n, int sides) {
-    size_t one = size_t(batch_heads) * n * sizeof(int2) + size_t(batch_heads) * (BUCKETS + 1) * sizeof(int);
+    size_t one = 2 * size_t(batch_heads) * n * sizeof(int2) + size_t(batch_heads) * (BUCKETS + 1) * sizeof(int);
     one = (one + 255) & ~size_t(255);
     return one * sides;
 }
@@ -77,14 +133,15 @@ SideIndex side_index(void* workspace, int batch_heads, int n, int side, int side
     char* p = static_cast<char*>(workspace) + one * side;
     (void)sides;
     return SideIndex{reinterpret_cast<const int2*>(p),
-                     reinterpret_cast<const int*>(p + size_t(batch_heads) * n * sizeof(int2))};
+                     reinterpret_cast<const int*>(p + 2 * size_t(batch_heads) * n * sizeof(int2))};
 }
 
 cudaError_t launch_build_index(const int* labels, int batch_heads, int n, void* workspace, int side, int sides,
                                cudaStream_t stream) {
     SideIndex index = side_index(workspace, batch_heads, n, side, sides);
+    int2* entries = const_cast<int2*>(index.entries);
     KernelTimer timer("build_index", stream);
-    build_index_kernel<<<batch_heads, INDEX_THREADS, 0, stream>>>(labels, n, const_cast<int2*>(index.entries),
+    build_index_kernel<<<batch_heads, INDEX_THREADS, 0, stream>>>(labels, n, entries, entries + size_t(batch_heads) * n,
                                                                   const_cast<int*>(index.starts));
     return cudaGetLastError();
 }

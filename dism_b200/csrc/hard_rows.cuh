@@ -13,7 +13,7 @@
 namespace dism {
 
 constexpr int TASK_ROWS = 256;  // rows per CTA task (sequence lengths are multiples of 256)
-constexpr int LOAD_BINS = 32;
+constexpr int LOAD_BINS = 64;
 
 struct RowContext {  // what a task's rows share
     const int *iq, *ik, *boundary;
@@ -173,21 +173,25 @@ __global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(cons
             shared.rows.previous[threadIdx.x] = my_row ? __ldg(own_labels + my_row - 1) : 0;
             shared.rows.first[threadIdx.x] = first;
             shared.rows.last[threadIdx.x] = last;
-            // about size * (causal share of the sequence) entries lie on the causal side
-            const int64_t estimate = int64_t(last - first) * (QM ? my_row + 1 : a.n - my_row) / a.n;
-            bin = estimate <= 0 ? 0 : min(LOAD_BINS - 1, 32 - __clz(int(estimate)));
+            // the causal range is, up to bucket collisions, the row's partner count: exact bins for
+            // small counts, steps of 16 above
+            const int count = last - first;
+            bin = count < 48 ? count : min(LOAD_BINS - 1, 48 + (count - 48) / 16);
         }
         const int rank_in_bin = atomicAdd(&shared.rows.bin_count[bin], 1);
         __syncthreads();
-        if (warp == 0) {  // descending bins: exclusive scan from the top
-            const int count = shared.rows.bin_count[LOAD_BINS - 1 - lane];
-            int prefix = count;
+        if (warp == 0) {  // descending bins: exclusive scan from the top, two bins per lane
+            const int heavy = shared.rows.bin_count[LOAD_BINS - 1 - 2 * lane];
+            const int light = shared.rows.bin_count[LOAD_BINS - 2 - 2 * lane];
+            int prefix = heavy + light;
 #pragma unroll
             for (int s = 1; s < 32; s <<= 1) {
                 const int other = __shfl_up_sync(FULL, prefix, s);
                 if (lane >= s) prefix += other;
             }
-            shared.rows.bin_start[LOAD_BINS - 1 - lane] = prefix - count;
+            prefix -= heavy + light;
+            shared.rows.bin_start[LOAD_BINS - 1 - 2 * lane] = prefix;
+            shared.rows.bin_start[LOAD_BINS - 2 - 2 * lane] = prefix + heavy;
         }
         __syncthreads();
         shared.rows.order[shared.rows.bin_start[bin] + rank_in_bin] = threadIdx.x;
