@@ -74,22 +74,32 @@ __device__ __forceinline__ int bucket_of(int label) {
 }
 
 // Number of consecutive label matches on the diagonal that ends at (i, j), given that (i, j)
-// itself matches; one thread walks one diagonal.  With a boundary rectangle
-// (int32 [(N-1)/32, N] of this batch/head, boundary[c][col] = col - L(32c+31, col)) the walk ends
-// at the 32-row strip edge and reads the rest of the run from the rectangle.
+// itself matches.  The whole warp calls this with the same (i, j) and checks 32 cells per step.
+// With a boundary rectangle (int32 [(N-1)/32, N] of this batch/head,
+// boundary[c][col] = col - L(32c+31, col)) the walk ends at the 32-row strip edge and reads the
+// rest of the run from the rectangle.
 __device__ __forceinline__ int run_length(const int* __restrict__ q, const int* __restrict__ k,
-                                          const int* __restrict__ boundary, int n, int i, int j) {
-    int s = 1;
+                                          const int* __restrict__ boundary, int n, int i, int j, int lane) {
+    int length = 1, bi = i - 1, bj = j - 1;
     if (boundary) {
         const int inside = i & 31;  // rows i-1 .. i-inside share the strip of row i
-        for (; s <= inside && j - s >= 0; ++s)
-            if (__ldg(q + i - s) != __ldg(k + j - s)) return s;
-        const int col = j - s;
-        if (s == inside + 1 && col >= 0 && i >= 32) s += col - __ldg(boundary + int64_t((i >> 5) - 1) * n + col);
-        return s;
+        const bool ok = lane < inside && bj - lane >= 0 && __ldg(q + bi - lane) == __ldg(k + bj - lane);
+        const int run = __ffs(~__ballot_sync(FULL, ok)) - 1;
+        length += run;
+        const int col = bj - inside;
+        if (run == inside && col >= 0 && i >= 32)
+            length += col - __ldg(boundary + int64_t((i >> 5) - 1) * n + col);
+        return length;
     }
-    while (j - s >= 0 && __ldg(q + i - s) == __ldg(k + j - s)) ++s;
-    return s;
+    while (bj >= 0) {
+        const bool ok = bj - lane >= 0 && __ldg(q + bi - lane) == __ldg(k + bj - lane);
+        const unsigned mask = __ballot_sync(FULL, ok);
+        if (mask != FULL) return length + __ffs(~mask) - 1;
+        length += 32;
+        bi -= 32;
+        bj -= 32;
+    }
+    return length;
 }
 
 // Position index of one side of one (batch, head): `entries` holds (position, label) sorted by

@@ -91,29 +91,43 @@ __device__ __forceinline__ void scan_partners(PartnerQueues<EXTRA>* queue, const
     }
 }
 
-// Fills in the weights of the group's queued partners from `from` on, four partners at a time
-// (one per lane).  The run is longer than one only when the diagonal predecessor matches too;
-// that lane then walks it.
+// Fills in the weights of the queued partners, four per group at a time (one per lane).  A run
+// is longer than one only when the diagonal predecessor matches too; those partners are then
+// handled one after the other by the whole warp, which walks 32 cells of the diagonal per step.
+// Every lane of the warp calls this.
 template <bool QUERY_MAJOR, bool EXTRA>
 __device__ __forceinline__ void finish_partners(PartnerQueues<EXTRA>* queue, const RowContext& ctx,
                                                 const float* __restrict__ shift_by_position, const SearchRow& mine,
-                                                int from, int group, int part) {
+                                                int group, int part, int lane) {
     const int* other_side = QUERY_MAJOR ? ctx.ik : ctx.iq;
     const float weight_one = __ldg(ctx.lut + 1), extra_one = EXTRA ? __ldg(ctx.dlut + 1) : 0.f;
+    unsigned long long longer = 0;  // slots of this lane whose run continues up the diagonal
 #pragma unroll 2
-    for (int slot = from + part; slot < mine.queued; slot += 4) {
+    for (int slot = part; slot < mine.queued; slot += 4) {
         const int position = queue->position[group][slot];
         const int neighbour = position > 0 ? __ldg(other_side + position - 1) : 0;
         const float shift = shift_by_position ? __ldg(shift_by_position + position) : 0.f;
-        float weight = weight_one, extra = extra_one;
-        if (position > 0 && mine.row > 0 && neighbour == mine.previous) {
-            const int i = QUERY_MAJOR ? mine.row : position, j = QUERY_MAJOR ? position : mine.row;
-            const int length = 1 + run_length(ctx.iq, ctx.ik, ctx.boundary, ctx.n, i - 1, j - 1);
-            weight = __ldg(ctx.lut + length);
-            if (EXTRA) extra = __ldg(ctx.dlut + length);
+        if (position > 0 && mine.row > 0 && neighbour == mine.previous) longer |= 1ull << slot;
+        queue->weight[group][slot] = weight_one - shift;
+        if (EXTRA) queue->extra[group][slot] = extra_one;
+    }
+    for (unsigned waiting = __ballot_sync(FULL, longer != 0); waiting; waiting = __ballot_sync(FULL, longer != 0)) {
+        const int owner = __ffs(waiting) - 1;
+        int slot = 0, position = 0;
+        if (lane == owner) {
+            slot = __ffsll((long long)longer) - 1;
+            longer &= longer - 1;
+            position = queue->position[group][slot];
         }
-        queue->weight[group][slot] = weight - shift;
-        if (EXTRA) queue->extra[group][slot] = extra;
+        position = __shfl_sync(FULL, position, owner);
+        const int row = __shfl_sync(FULL, mine.row, owner);
+        const int i = QUERY_MAJOR ? row : position, j = QUERY_MAJOR ? position : row;
+        const int length = run_length(ctx.iq, ctx.ik, ctx.boundary, ctx.n, i, j, lane);
+        if (lane == owner) {
+            const float shift = shift_by_position ? __ldg(shift_by_position + position) : 0.f;
+            queue->weight[group][slot] = __ldg(ctx.lut + length) - shift;
+            if (EXTRA) queue->extra[group][slot] = __ldg(ctx.dlut + length);
+        }
     }
 }
 
@@ -224,7 +238,7 @@ __global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(cons
                     }
                     if (!__ballot_sync(FULL, search.queued > 0)) break;
                     __syncwarp();
-                    finish_partners<QM, Policy::EXTRA>(queue, ctx, QM ? nullptr : ctx.lse2, search, 0, group, part);
+                    finish_partners<QM, Policy::EXTRA>(queue, ctx, QM ? nullptr : ctx.lse2, search, group, part, lane);
                     __syncwarp();
                     const int mine = search.queued, rounds = __reduce_max_sync(FULL, mine);
                     drain_partners<8, VPL>(

@@ -100,9 +100,14 @@ __global__ __launch_bounds__(WARPS * 32) void longest_match_kernel(const int* __
                 const int at = base + lane;
                 int2 entry = make_int2(0x7fffffff, 0);
                 if (at < to) entry = __ldg(mine.entries + at);
-                if (entry.x < i && entry.y == label) {
-                    const long long key = (static_cast<long long>(run_length(s, s, nullptr, n, i, entry.x)) << 32) | entry.x;
-                    best = max(best, key);
+                const bool hit = entry.x < i && entry.y == label;
+                // a run longer than one needs the diagonal predecessor to match as well
+                const bool longer = hit && entry.x > 0 && i > 0 && __ldg(s + entry.x - 1) == __ldg(s + i - 1);
+                if (hit && !longer) best = max(best, (1ll << 32) | entry.x);
+                for (unsigned waiting = __ballot_sync(FULL, longer); waiting; waiting &= waiting - 1) {
+                    const int owner = __ffs(waiting) - 1, j = __shfl_sync(FULL, entry.x, owner);
+                    const int length = run_length(s, s, nullptr, n, i, j, lane);
+                    best = max(best, (static_cast<long long>(length) << 32) | j);
                 }
                 if (__ballot_sync(FULL, entry.x >= i)) break;
             }

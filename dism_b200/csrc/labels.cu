@@ -27,9 +27,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 struct Best {
     float first, second;
     int arg;
+    // branch-free: the old maximum or the newcomer, whichever is smaller, competes for second place
     __device__ __forceinline__ void offer(float x, int index) {
-        if (x > first) { second = first; first = x; arg = index; }
-        else second = fmaxf(second, x);
+        second = fmaxf(second, fminf(first, x));
+        arg = x > first ? index : arg;
+        first = fmaxf(first, x);
     }
     __device__ __forceinline__ void merge(float other_first, float other_second, int other_arg) {
         if (other_first > first || (other_first == first && other_arg < arg)) {
@@ -84,12 +86,24 @@ __global__ __launch_bounds__(LABEL_ROWS) void labels_kernel(const __nv_bfloat16*
         for (int half = 0; half < 2; ++half) best[m][half] = Best{-INFINITY, -INFINITY, 0};
     float code_max = 0.f;  // largest squared code norm seen while staging
 
+    // The next codebook tile is fetched into registers while the current one is multiplied.
+    constexpr int PIECES = LABEL_CODES * (D / 8) / LABEL_ROWS;  // 16-byte pieces per thread and tile
+    uint4 staged[PIECES];
+    auto fetch = [&](int v0) {
+#pragma unroll
+        for (int piece = 0; piece < PIECES; ++piece) {
+            const int e = threadIdx.x + piece * LABEL_ROWS, v = e / (D / 8), c = e % (D / 8);
+            staged[piece] = make_uint4(0, 0, 0, 0);
+            if (v0 + v < vocab) staged[piece] = __ldg(reinterpret_cast<const uint4*>(head_codes + int64_t(v0 + v) * D) + c);
+        }
+    };
+    fetch(0);
     for (int v0 = 0; v0 < vocab; v0 += LABEL_CODES) {
         __syncthreads();
-        for (int e = threadIdx.x; e < LABEL_CODES * (D / 8); e += LABEL_ROWS) {
-            const int v = e / (D / 8), c = e % (D / 8);
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (v0 + v < vocab) raw = __ldg(reinterpret_cast<const uint4*>(head_codes + int64_t(v0 + v) * D) + c);
+#pragma unroll
+        for (int piece = 0; piece < PIECES; ++piece) {
+            const int e = threadIdx.x + piece * LABEL_ROWS, v = e / (D / 8), c = e % (D / 8);
+            const uint4 raw = staged[piece];
             *reinterpret_cast<uint4*>(&codes[v][c * 8]) = raw;
             const unsigned word[4] = {raw.x, raw.y, raw.z, raw.w};
             float squares = 0.f;
@@ -103,6 +117,7 @@ __global__ __launch_bounds__(LABEL_ROWS) void labels_kernel(const __nv_bfloat16*
             for (int s = 1; s < D / 8; s <<= 1) squares += __shfl_xor_sync(FULL, squares, s);
             code_max = fmaxf(code_max, squares);
         }
+        if (v0 + LABEL_CODES < vocab) fetch(v0 + LABEL_CODES);
         __syncthreads();
 #pragma unroll
         for (int tile = 0; tile < LABEL_CODES / 8; ++tile) {
@@ -115,13 +130,23 @@ __global__ __launch_bounds__(LABEL_ROWS) void labels_kernel(const __nv_bfloat16*
                 mma_bf16(c[1], a[1][k], b0, b1);
             }
             const int column = v0 + tile * 8 + 2 * t;
+            if (v0 + LABEL_CODES <= vocab) {  // whole tile inside the codebook: no bound checks
 #pragma unroll
-            for (int m = 0; m < 2; ++m)
+                for (int m = 0; m < 2; ++m)
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    if (column < vocab) best[m][half].offer(c[m][2 * half], column);
-                    if (column + 1 < vocab) best[m][half].offer(c[m][2 * half + 1], column + 1);
-                }
+                    for (int half = 0; half < 2; ++half) {
+                        best[m][half].offer(c[m][2 * half], column);
+                        best[m][half].offer(c[m][2 * half + 1], column + 1);
+                    }
+            } else {
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        if (column < vocab) best[m][half].offer(c[m][2 * half], column);
+                        if (column + 1 < vocab) best[m][half].offer(c[m][2 * half + 1], column + 1);
+                    }
+            }
         }
     }
     // Largest squared code norm of this head (every thread staged a share of every tile).

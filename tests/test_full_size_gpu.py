@@ -58,3 +58,29 @@ def test_full_size_forward_and_backward(workload, oracle):
     # scaling dO by a power of two scales dSQ and dV exactly, except where FP32 partial sums are subnormal
     assert (doubled[0] - grads[0] * 2).abs().max() < 1e-30
     assert (doubled[2].float() - grads[2].float() * 2).abs().max() < 1e-30
+
+
+def test_long_context_with_planted_runs(oracle):
+    """Long-context shape in miniature: N = 32768, and every 4096 positions a 1024-long window of
+    query labels repeats an earlier window of key labels, so run lengths reach 1024."""
+    import dism_b200
+    dism_b200.install_dropin()
+    from flash_dism import hard_forward
+    b, h, n, r, dv = 1, 2, 32768, 32, 64
+    g = torch.Generator().manual_seed(4)
+    sq, sk = [(torch.nn.functional.silu(torch.randn(b, n, h, r, generator=g)) * .4).bfloat16() for _ in range(2)]
+    v = torch.randn(b, n, h, dv, generator=g).bfloat16()
+    iq, ik = [torch.randint(0, 512, (b, h, n), generator=g, dtype=torch.int32) for _ in range(2)]
+    rng = np.random.default_rng(4)
+    for start in range(4096, n, 4096):
+        target = start + int(rng.integers(0, 3072))
+        source = int(rng.integers(0, target - 1024))
+        iq[:, :, target:target + 1024] = ik[:, :, source:source + 1024]
+    hard = torch.ones(b, h, dtype=torch.bool)
+    tau = torch.tensor([.05, -.2])
+    out, norm = hard_forward.forward_hard(sq.cuda(), sk.cuda(), v.cuda(), iq.cuda(), ik.cuda(), hard.cuda(), tau.cuda())
+    f = lambda t: t.float().numpy()
+    expected, lse2 = oracle.forward(f(sq), f(sk), f(v), iq.numpy(), ik.numpy(), hard.numpy(), tau.numpy(), threads=2)
+    torch.testing.assert_close(out.double().cpu(), torch.from_numpy(expected), atol=.008, rtol=.025)
+    torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
+    assert lse2.max() > 30  # the planted runs dominate their rows' normalisers
