@@ -85,7 +85,7 @@ int dism_profile_read(int index, char* name, int capacity, float* milliseconds) 
 }
 
 const char* dism_last_error(void) { return last_error; }
-int dism_abi_version(void) { return 2; }
+int dism_abi_version(void) { return 3; }
 
 int dism_labels(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t* labels, void* stream) {
@@ -125,15 +125,30 @@ int dism_hard_log_weights(const float* tau, int heads, int n, float* lut, void* 
                        "hard_log_weights");
 }
 
+static int check_documents(const int32_t* documents, int hard_rows, const int32_t* boundary, int batch, int n) {
+    if (!documents) {
+        if (hard_rows != batch) return fail(DISM_EINVAL, "fixed hard must be [B,H]");
+        return DISM_OK;
+    }
+    if (batch != 1) return fail(DISM_EINVAL, "packed labels/layout length mismatch: packed layouts use one batch row");
+    if (boundary) return fail(DISM_EUNSUPPORTED, "the boundary rectangle is not used with packed layouts; pass NULL");
+    if (hard_rows <= 0 || n % hard_rows || (n / hard_rows) % 256)
+        return fail(DISM_EINVAL, "packed hard rows must evenly divide tokens into 256-aligned training rows");
+    if (!aligned(documents, 8)) return fail(DISM_EINVAL, "document table must be 8-byte aligned");
+    return DISM_OK;
+}
+
 int dism_hard_readout(const void* sq, const void* sk, const void* v, const int32_t* iq, const int32_t* ik,
-                      const uint8_t* hard, const int32_t* boundary, const float* lut, int lut_stride, int batch,
+                      const uint8_t* hard, const int32_t* boundary, const int32_t* documents, int hard_rows,
+                      const float* lut, int lut_stride, int batch,
                       int n, int heads, int r, int dv, int ctas, void* out, float* lse2, void* workspace,
                       size_t workspace_bytes, void* stream) {
     if (int status = check_shape(batch, heads, n)) return status;
     if (int status = check_dims(r, dv)) return status;
     if (!sq || !sk || !v || !iq || !ik || !hard || !lut || !out || !lse2) return fail(DISM_EINVAL, "null pointer");
     if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
-    if (lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
+    if (!documents && lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
+    if (int status = check_documents(documents, hard_rows, boundary, batch, n)) return status;
     if (!aligned(sq, 16) || !aligned(sk, 16) || !aligned(v, 16) || !aligned(out, 16))
         return fail(DISM_EINVAL, "vector tensors must be 16-byte aligned");
     if (!workspace || workspace_bytes < dism::hard_forward_workspace_bytes(batch, heads, n) || !aligned(workspace, 256))
@@ -141,7 +156,8 @@ int dism_hard_readout(const void* sq, const void* sk, const void* v, const int32
     dism::HardShape shape{batch, heads, n, r, dv};
     using bf = __nv_bfloat16;
     return cuda_status(dism::launch_hard_forward(shape, static_cast<const bf*>(sq), static_cast<const bf*>(sk),
-                                                 static_cast<const bf*>(v), iq, ik, hard, boundary, lut, lut_stride,
+                                                 static_cast<const bf*>(v), iq, ik, hard, boundary,
+                                                 reinterpret_cast<const int2*>(documents), hard_rows, lut, lut_stride,
                                                  ctas, static_cast<bf*>(out), lse2, workspace,
                                                  static_cast<cudaStream_t>(stream)),
                        "hard_readout");
@@ -158,8 +174,9 @@ size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride)
 }
 
 int dism_hard_backward(const void* sq, const void* sk, const void* v, const void* dout, const int32_t* iq,
-                       const int32_t* ik, const uint8_t* hard, const int32_t* boundary, const float* lut,
-                       int lut_stride, const float* lse2, int batch, int n, int heads, int r, int dv, int ctas,
+                       const int32_t* ik, const uint8_t* hard, const int32_t* boundary, const int32_t* documents,
+                       int hard_rows, const float* lut, int lut_stride, const float* lse2, int batch, int n, int heads,
+                       int r, int dv, int ctas,
                        float* dsq, void* dsk, void* dv_out, float* dtau, void* workspace, size_t workspace_bytes,
                        void* stream) {
     if (int status = check_shape(batch, heads, n)) return status;
@@ -168,7 +185,8 @@ int dism_hard_backward(const void* sq, const void* sk, const void* v, const void
         !workspace)
         return fail(DISM_EINVAL, "null pointer");
     if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
-    if (lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
+    if (!documents && lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
+    if (int status = check_documents(documents, hard_rows, boundary, batch, n)) return status;
     if (workspace_bytes < dism::hard_backward_workspace_bytes(batch, heads, n, lut_stride) || !aligned(workspace, 256))
         return fail(DISM_EINVAL, "workspace too small or misaligned (see dism_hard_backward_workspace)");
     if (!aligned(sq, 16) || !aligned(sk, 16) || !aligned(v, 16) || !aligned(dout, 16) || !aligned(dsq, 16) ||
@@ -178,7 +196,8 @@ int dism_hard_backward(const void* sq, const void* sk, const void* v, const void
     using bf = __nv_bfloat16;
     return cuda_status(dism::launch_hard_backward(shape, static_cast<const bf*>(sq), static_cast<const bf*>(sk),
                                                   static_cast<const bf*>(v), static_cast<const bf*>(dout), iq, ik,
-                                                  hard, boundary, lut, lut_stride, lse2, ctas, dsq,
+                                                  hard, boundary, reinterpret_cast<const int2*>(documents), hard_rows, lut,
+                                                  lut_stride, lse2, ctas, dsq,
                                                   static_cast<bf*>(dsk), static_cast<bf*>(dv_out), dtau, workspace,
                                                   static_cast<cudaStream_t>(stream)), "hard_backward");
 }

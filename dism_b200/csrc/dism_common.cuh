@@ -79,11 +79,12 @@ __device__ __forceinline__ int bucket_of(int label) {
 // boundary[c][col] = col - L(32c+31, col)) the walk ends at the 32-row strip edge and reads the
 // rest of the run from the rectangle.
 __device__ __forceinline__ int run_length(const int* __restrict__ q, const int* __restrict__ k,
-                                          const int* __restrict__ boundary, int n, int i, int j, int lane) {
+                                          const int* __restrict__ boundary, int n, int i, int j, int lane,
+                                          int begin = 0) {  // positions below `begin` belong to another document
     int length = 1, bi = i - 1, bj = j - 1;
     if (boundary) {
         const int inside = i & 31;  // rows i-1 .. i-inside share the strip of row i
-        const bool ok = lane < inside && bj - lane >= 0 && __ldg(q + bi - lane) == __ldg(k + bj - lane);
+        const bool ok = lane < inside && bj - lane >= begin && __ldg(q + bi - lane) == __ldg(k + bj - lane);
         const int run = __ffs(~__ballot_sync(FULL, ok)) - 1;
         length += run;
         const int col = bj - inside;
@@ -91,8 +92,8 @@ __device__ __forceinline__ int run_length(const int* __restrict__ q, const int* 
             length += col - __ldg(boundary + int64_t((i >> 5) - 1) * n + col);
         return length;
     }
-    while (bj >= 0) {
-        const bool ok = bj - lane >= 0 && __ldg(q + bi - lane) == __ldg(k + bj - lane);
+    while (bj >= begin) {
+        const bool ok = bj - lane >= begin && __ldg(q + bi - lane) == __ldg(k + bj - lane);
         const unsigned mask = __ballot_sync(FULL, ok);
         if (mask != FULL) return length + __ffs(~mask) - 1;
         length += 32;
@@ -121,12 +122,19 @@ __device__ __forceinline__ int lower_bound_position(const int2* __restrict__ ent
 
 // Range of the bucket of `label` that can hold causal partners of owner position `row`.
 template <bool QUERY_MAJOR>
-__device__ __forceinline__ void partner_range(const SideIndex& index, int label, int row, int& cursor, int& end) {
+__device__ __forceinline__ void partner_range(const SideIndex& index, int label, int row, int& cursor, int& end,
+                                              int begin = 0, int limit = 0x7fffffff) {
     const int bucket = bucket_of(label);
     const int lo = __ldg(index.starts + bucket), hi = __ldg(index.starts + bucket + 1);
-    // positions ascend inside a bucket: keys up to the row, queries from the row on
-    cursor = QUERY_MAJOR ? lo : lower_bound_position(index.entries, lo, hi, row);
-    end = QUERY_MAJOR ? lower_bound_position(index.entries, lo, hi, row + 1) : hi;
+    // positions ascend inside a bucket: keys from the document start up to the row, queries from
+    // the row to the document end
+    if (QUERY_MAJOR) {
+        cursor = begin > 0 ? lower_bound_position(index.entries, lo, hi, begin) : lo;
+        end = lower_bound_position(index.entries, cursor, hi, row + 1);
+    } else {
+        cursor = lower_bound_position(index.entries, lo, hi, row);
+        end = limit < 0x7fffffff ? lower_bound_position(index.entries, cursor, hi, limit) : hi;
+    }
 }
 
 // ---- gather ring -------------------------------------------------------------------------------
@@ -211,7 +219,9 @@ struct RowsArgs {
     const int *iq, *ik, *boundary;
     const uint8_t* hard;
     const float *lut, *dlut, *lse2;
-    SideIndex index;  // position index of the partner side
+    SideIndex index;        // position index of the partner side
+    const int2* documents;  // packed layout: (begin, end) of the document of every 256-row block, or null
+    int hard_rows;          // rows of the hard-flag matrix (the batch size unless packed)
     __nv_bfloat16 *out, *dsk, *dv;
     float *lse2_out, *dsq, *dtau_rows;
     int batch, heads, n, lut_stride, tasks;
@@ -252,13 +262,15 @@ cudaError_t launch_log_weights(const float* tau, int heads, int n, float* lut, c
 size_t hard_forward_workspace_bytes(int batch, int heads, int n);
 cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,
                                 const __nv_bfloat16* v, const int* iq, const int* ik, const uint8_t* hard,
-                                const int* boundary, const float* lut, int lut_stride, int ctas,
-                                __nv_bfloat16* out, float* lse2, void* workspace, cudaStream_t stream);
+                                const int* boundary, const int2* documents, int hard_rows, const float* lut,
+                                int lut_stride, int ctas, __nv_bfloat16* out, float* lse2, void* workspace,
+                                cudaStream_t stream);
 size_t hard_backward_workspace_bytes(int batch, int heads, int n, int lut_stride);
 cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,
                                  const __nv_bfloat16* v, const __nv_bfloat16* dout, const int* iq, const int* ik,
-                                 const uint8_t* hard, const int* boundary, const float* lut, int lut_stride,
-                                 const float* lse2, int ctas, float* dsq, __nv_bfloat16* dsk, __nv_bfloat16* dv,
-                                 float* dtau, void* workspace, cudaStream_t stream);
+                                 const uint8_t* hard, const int* boundary, const int2* documents, int hard_rows,
+                                 const float* lut, int lut_stride, const float* lse2, int ctas, float* dsq,
+                                 __nv_bfloat16* dsk, __nv_bfloat16* dv, float* dtau, void* workspace,
+                                 cudaStream_t stream);
 
 }  // namespace dism

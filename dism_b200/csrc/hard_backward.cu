@@ -52,7 +52,7 @@ struct QueryBackwardPolicy {
             if (has_r) load_bf16<8>(a.sq + at * R + part * 8, query);
             load_bf16<VPL>(a.dout + at * DV + part * VPL, derivative);
             norm = __ldg(ctx.lse2 + row);
-            center = __ldg(ctx.dlut + row + 1);
+            center = __ldg(ctx.dlut + row - ctx.begin + 1);  // document-local position
         }
     }
     __device__ __forceinline__ void pair(bool live, float x, float extra, const float (&key)[8], const float (&value)[VPL]) {
@@ -171,9 +171,10 @@ size_t hard_backward_workspace_bytes(int batch, int heads, int n, int lut_stride
 
 cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,
                                  const __nv_bfloat16* v, const __nv_bfloat16* dout, const int* iq, const int* ik,
-                                 const uint8_t* hard, const int* boundary, const float* lut, int lut_stride,
-                                 const float* lse2, int ctas, float* dsq, __nv_bfloat16* dsk, __nv_bfloat16* dv,
-                                 float* dtau, void* workspace, cudaStream_t stream) {
+                                 const uint8_t* hard, const int* boundary, const int2* documents, int hard_rows,
+                                 const float* lut, int lut_stride, const float* lse2, int ctas, float* dsq,
+                                 __nv_bfloat16* dsk, __nv_bfloat16* dv, float* dtau, void* workspace,
+                                 cudaStream_t stream) {
     const int batch_heads = shape.batch * shape.heads;
     cudaError_t status = launch_build_index(ik, batch_heads, shape.n, workspace, 0, 2, stream);
     if (status != cudaSuccess) return status;
@@ -188,6 +189,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     RowsArgs args{};
     args.sq = sq; args.sk = sk; args.v = v; args.dout = dout;
     args.iq = iq; args.ik = ik; args.boundary = boundary; args.hard = hard;
+    args.documents = documents; args.hard_rows = hard_rows;
     args.lut = lut; args.dlut = dlut; args.lse2 = lse2;
     args.dsq = dsq; args.dtau_rows = rows; args.dsk = dsk; args.dv = dv;
     args.batch = shape.batch; args.heads = shape.heads; args.n = shape.n; args.lut_stride = lut_stride;

@@ -99,14 +99,16 @@ size_t hard_forward_workspace_bytes(int batch, int heads, int n) { return index_
 
 cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,
                                 const __nv_bfloat16* v, const int* iq, const int* ik, const uint8_t* hard,
-                                const int* boundary, const float* lut, int lut_stride, int ctas,
-                                __nv_bfloat16* out, float* lse2, void* workspace, cudaStream_t stream) {
+                                const int* boundary, const int2* documents, int hard_rows, const float* lut,
+                                int lut_stride, int ctas, __nv_bfloat16* out, float* lse2, void* workspace,
+                                cudaStream_t stream) {
     const int batch_heads = shape.batch * shape.heads;
     cudaError_t status = launch_build_index(ik, batch_heads, shape.n, workspace, 0, 1, stream);
     if (status != cudaSuccess) return status;
     RowsArgs args{};
     args.sq = sq; args.sk = sk; args.v = v;
     args.iq = iq; args.ik = ik; args.boundary = boundary; args.hard = hard;
+    args.documents = documents; args.hard_rows = hard_rows;
     args.lut = lut;
     args.index = side_index(workspace, batch_heads, shape.n, 0, 1);
     args.out = out; args.lse2_out = lse2;

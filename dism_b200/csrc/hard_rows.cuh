@@ -21,6 +21,7 @@ struct RowContext {  // what a task's rows share
     SideIndex index;  // position index of the partner side
     int64_t vec0;     // (b, 0, h) in units of one vector
     int n, heads, bh;
+    int begin, end;   // the document of the task's rows: [begin, end) within the sequence
 };
 
 struct RowsShared {
@@ -107,7 +108,7 @@ __device__ __forceinline__ void finish_partners(PartnerQueues<EXTRA>* queue, con
         const int position = queue->position[group][slot];
         const int neighbour = position > 0 ? __ldg(other_side + position - 1) : 0;
         const float shift = shift_by_position ? __ldg(shift_by_position + position) : 0.f;
-        if (position > 0 && mine.row > 0 && neighbour == mine.previous) longer |= 1ull << slot;
+        if (position > ctx.begin && mine.row > ctx.begin && neighbour == mine.previous) longer |= 1ull << slot;
         queue->weight[group][slot] = weight_one - shift;
         if (EXTRA) queue->extra[group][slot] = extra_one;
     }
@@ -122,7 +123,7 @@ __device__ __forceinline__ void finish_partners(PartnerQueues<EXTRA>* queue, con
         position = __shfl_sync(FULL, position, owner);
         const int row = __shfl_sync(FULL, mine.row, owner);
         const int i = QUERY_MAJOR ? row : position, j = QUERY_MAJOR ? position : row;
-        const int length = run_length(ctx.iq, ctx.ik, ctx.boundary, ctx.n, i, j, lane);
+        const int length = run_length(ctx.iq, ctx.ik, ctx.boundary, ctx.n, i, j, lane, ctx.begin);
         if (lane == owner) {
             const float shift = shift_by_position ? __ldg(shift_by_position + position) : 0.f;
             queue->weight[group][slot] = __ldg(ctx.lut + length) - shift;
@@ -155,8 +156,17 @@ __global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(cons
         // (batch, head) the blocks with the most causal partners go first.
         const int bh = task / blocks, rank = task % blocks, block = QM ? blocks - 1 - rank : rank;
         const int b = bh / a.heads, h = bh % a.heads;
-        const bool active = a.hard[bh];
         RowContext ctx;
+        ctx.begin = 0;
+        ctx.end = a.n;
+        int hard_row = b;
+        if (a.documents) {  // packed: one batch row, documents and hard training rows are 256-aligned spans
+            const int2 document = __ldg(a.documents + block);
+            ctx.begin = document.x;
+            ctx.end = document.y;
+            hard_row = (block * TASK_ROWS) / (a.n / a.hard_rows);
+        }
+        const bool active = a.hard[hard_row * a.heads + h];
         ctx.iq = a.iq + int64_t(bh) * a.n;
         ctx.ik = a.ik + int64_t(bh) * a.n;
         ctx.boundary = a.boundary ? a.boundary + int64_t(bh) * ((a.n - 1) / 32) * a.n : nullptr;
@@ -182,9 +192,9 @@ __global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(cons
             // the lane groups start from there instead of from a chain of dependent global loads
             const int label = __ldg(own_labels + my_row);
             int first, last;
-            partner_range<QM>(ctx.index, label, my_row, first, last);
+            partner_range<QM>(ctx.index, label, my_row, first, last, ctx.begin, ctx.end < a.n ? ctx.end : 0x7fffffff);
             shared.rows.label[threadIdx.x] = label;
-            shared.rows.previous[threadIdx.x] = my_row ? __ldg(own_labels + my_row - 1) : 0;
+            shared.rows.previous[threadIdx.x] = my_row > ctx.begin ? __ldg(own_labels + my_row - 1) : 0;
             shared.rows.first[threadIdx.x] = first;
             shared.rows.last[threadIdx.x] = last;
             // the causal range is, up to bucket collisions, the row's partner count: exact bins for

@@ -7,10 +7,11 @@ forwards plain pointers to the C ABI of libdism_b200.so on the current CUDA stre
 compute of its own and has no fallback: without the library, importing it fails.
 
 Differences a caller can see: `hard_readout` and `hard_backward` accept `boundary=None` (run
-lengths are then derived from the labels inside the kernel, nothing quadratic is stored); the
-packed (`table`) layout and the soft path (`core_forward`, `core_backward`) are not built and
-raise NotImplementedError; the `choice` device word of the reference's CUDA-graph router is
-accepted only as None.
+lengths are then derived from the labels inside the kernel, nothing quadratic is stored) and, with
+a packed `table`, only `boundary=None`; the packed `hard_summary` / `hard_chunk` run document by
+document through the fixed-length kernels; the soft path (`core_forward`, `core_backward`) is not
+built and raises NotImplementedError; the `choice` device word of the reference's CUDA-graph
+router is accepted only as None.
 """
 import torch
 
@@ -42,9 +43,87 @@ def _stream(tensor):
 
 def _no_table(table, choice):
     if table is not None:
-        raise NotImplementedError('packed (varlen) layouts are not built yet')
+        raise NotImplementedError('this entry takes fixed-length input only')
     if choice is not None:
         raise NotImplementedError('the CUDA-graph route word is not supported')
+
+
+# ---- packed (varlen) layouts -------------------------------------------------------------------
+# The reference describes a pack by a CPU int64 table [documents, 7] with the columns Begin, Length,
+# PaddedBegin, PaddedLength, ForwardOffset, VerticalOffset, BackwardOffset
+# (dism_v3/include/varlen/layout.cuh:17-20, built in dism_v3/src/frontend.cpp:259-280).
+def make_varlen_layout(cu_seqlens, total):
+    """cu_seqlens int32 [documents+1] -> (table, lengths, tokens, padded, forward, vertical, backward)."""
+    if not (torch.is_tensor(cu_seqlens) and cu_seqlens.dim() == 1 and cu_seqlens.dtype == torch.int32
+            and cu_seqlens.is_contiguous() and cu_seqlens.numel() > 0):
+        _fail('cu_seqlens must be contiguous int32 [sequences+1]')
+    offsets = cu_seqlens.cpu().tolist()
+    if total < 0 or offsets[0] != 0 or offsets[-1] != total:
+        _fail('invalid cu_seqlens endpoints')
+    rows, lengths, forward, vertical, backward = [], [], 0, 0, 0
+    for begin, end in zip(offsets, offsets[1:]):
+        if begin < 0 or begin % 256 or end % 256:
+            _fail('all varlen boundaries must be256-token aligned')
+        n = end - begin
+        if n < 0:
+            _fail('cu_seqlens must be monotonic with supported lengths')
+        rows.append([begin, n, begin, n, forward, vertical, backward])
+        forward += ((n - 1) // 32 if n else 0) * n
+        vertical += ((n - 1) // 16 if n else 0) * n
+        backward += (n + 31) // 32 * n
+        lengths.append(n)
+    table = torch.tensor(rows, dtype=torch.int64).reshape(len(rows), 7)
+    return table, lengths, total, total, forward, vertical, backward
+
+
+def _documents(table, n, rows):
+    """(begin, length) of the non-empty documents of a layout table, validated against N and the hard rows."""
+    if not (torch.is_tensor(table) and table.device.type == 'cpu' and table.dtype == torch.int64 and table.dim() == 2
+            and table.size(1) == 7 and table.is_contiguous()):
+        _fail('layout must be CPU int64 [sequences,7]')
+    spans, tokens = [], 0
+    for begin, length, *_ in table.tolist():
+        if length < 0 or length % 256 or begin != tokens:
+            _fail('varlen boundaries including T must be256-token aligned; no input padding')
+        tokens += length
+        if length:
+            spans.append((begin, length))
+    if tokens != n:
+        _fail('packed labels/layout length mismatch')
+    if n % rows or (n // rows) % 256:
+        _fail('packed hard rows must evenly divide tokens into 256-aligned training rows')
+    row_tokens = n // rows
+    for begin, length in spans:
+        if begin // row_tokens != (begin + length - 1) // row_tokens:
+            _fail('document cannot cross a hard training-row boundary')
+    return spans
+
+
+_document_tables = {}
+
+
+def _document_table(spans, n, device):
+    """Device int32 [N/256, 2]: for every 256-position block the [begin, end) of its document.
+    Uploaded once per distinct pack and device (the reference caches its task tables the same way,
+    dism_v3/include/host/metadata_upload.h:15-48)."""
+    key = (tuple(spans), n, str(device))
+    cached = _document_tables.get(key)
+    if cached is None:
+        if len(_document_tables) >= 32:
+            _document_tables.pop(next(iter(_document_tables)))
+        blocks = torch.zeros((n // 256, 2), dtype=torch.int32)
+        for begin, length in spans:
+            blocks[begin // 256:(begin + length) // 256, 0] = begin
+            blocks[begin // 256:(begin + length) // 256, 1] = begin + length
+        cached = _document_tables[key] = blocks.to(device)
+    return cached
+
+
+def _packed_hard(hard, device, heads):
+    if not (torch.is_tensor(hard) and hard.device == device and hard.dtype == torch.bool and hard.dim() == 2
+            and hard.size(0) > 0 and hard.size(1) == heads and hard.is_contiguous()):
+        _fail('hard must be contiguous bool [training_rows,H]; token-level masks are unsupported '
+              '(sequence hard flags only)')
 
 
 def _check(tensor, dtype, shape, name):
@@ -63,7 +142,20 @@ def _check_hard(hard, device, batch, heads, what='hard'):
 
 
 def hard_summary(query, key, hard, table=None, ctas=0, choice=None):
-    """int32 labels [B,H,N] -> strip summaries int32 [B,H,(N-1)//32,N]."""
+    """int32 labels [B,H,N] -> strip summaries int32 [B,H,(N-1)//32,N]; packed: the documents'
+    [H,(length-1)//32,length] regions one after the other, flattened."""
+    if table is not None:
+        _no_table(None, choice)
+        if not (torch.is_tensor(query) and query.dim() == 3 and query.size(0) == 1):
+            _fail('packed labels/layout length mismatch')
+        h, n = query.size(1), query.size(2)
+        _packed_hard(hard, query.device, h)
+        spans = _documents(table, n, hard.size(0))
+        row_tokens = n // hard.size(0)
+        pieces = [hard_summary(query[:, :, a:a + m].contiguous(), key[:, :, a:a + m].contiguous(),
+                               hard[a // row_tokens:a // row_tokens + 1].contiguous(), None, ctas).flatten()
+                  for a, m in spans]
+        return torch.cat(pieces) if pieces else torch.empty(0, dtype=torch.int32, device=query.device)
     _no_table(table, choice)
     if not (torch.is_tensor(query) and query.is_cuda and query.dtype == torch.int32 and query.dim() == 3
             and query.is_contiguous()):
@@ -88,8 +180,21 @@ def hard_chunk(summary, table=None, heads=0, choice=None, inplace=False):
     """Compose strip summaries into inclusive boundaries (same shape; aliases the input if inplace)."""
     if not (torch.is_tensor(summary) and summary.is_cuda and summary.dtype == torch.int32 and summary.is_contiguous()):
         _fail('hard summary must be contiguous CUDA int32')
-    if table is not None and summary.dim() != 1:
-        _fail('invalid packed hard summary/heads')
+    if table is not None:
+        _no_table(None, choice)
+        lengths = [m for _, m, *_ in table.tolist() if m]
+        expected = sum(heads * ((m - 1) // 32) * m for m in lengths)
+        if heads <= 0 or summary.dim() != 1 or summary.numel() != expected:
+            _fail('invalid packed hard summary/heads')
+        out = summary if inplace else torch.empty_like(summary)
+        at = 0
+        for m in lengths:
+            size = heads * ((m - 1) // 32) * m
+            if size:
+                region = summary[at:at + size].view(1, heads, (m - 1) // 32, m)
+                out[at:at + size] = hard_chunk(region, None, heads, None, inplace).flatten()
+            at += size
+        return out
     _no_table(table, choice)
     if summary.dim() != 4:
         _fail('fixed hard summary must be [B,H,C,N]')
@@ -147,9 +252,26 @@ def _check_lut(lut, h, n, device):
         _fail('hard log-weight table is too short')
 
 
+def _layout_arguments(table, hard, boundary, lut, b, h, n, device):
+    """Validates hard flags and LUT for the fixed or the packed layout; returns the document-table
+    pointer (0 = fixed) and the number of hard rows."""
+    if table is None:
+        _check_hard(hard, device, b, h)
+        _check_lut(lut, h, n, device)
+        return 0, b
+    _packed_hard(hard, device, h)
+    if b != 1:
+        _fail('packed labels/layout length mismatch')
+    spans = _documents(table, n, hard.size(0))
+    if boundary is not None:
+        raise NotImplementedError('packed layouts take boundary=None (run lengths come from the labels)')
+    _check_lut(lut, h, max([m for _, m in spans], default=0), device)
+    return _document_table(spans, n, device).data_ptr(), hard.size(0)
+
+
 def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
     """x = (sq, sk, v, query labels, key labels, hard) -> (bf16 [B,N,H,DV], FP32 log2 normaliser [B,H,N])."""
-    _no_table(table, choice)
+    _no_table(None, choice)
     b, n, h, r = _vectors(x, 6, ('SQ', 'SK', 'V', 'query labels', 'key labels', 'hard flags'))
     sq, sk, v, iq, ik, hard = x
     _check(sq, torch.bfloat16, (b, n, h, r), 'SQ')
@@ -160,8 +282,7 @@ def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
     dv = v.size(3)
     _check(iq, torch.int32, (b, h, n), 'query labels')
     _check(ik, torch.int32, (b, h, n), 'key labels')
-    _check_hard(hard, sq.device, b, h)
-    _check_lut(lut, h, n, sq.device)
+    documents_ptr, rows = _layout_arguments(table, hard, boundary, lut, b, h, n, sq.device)
     if ctas < 0:
         _fail('invalid CTA count')
     boundary_ptr = _check_boundary(boundary, b, h, n, sq.device)
@@ -171,15 +292,15 @@ def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
         size = _abi.dism_hard_readout_workspace(b, h, n)
         workspace = torch.empty((size,), dtype=torch.uint8, device=sq.device)
         _lib.check(_abi.dism_hard_readout(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), iq.data_ptr(), ik.data_ptr(),
-                                          hard.data_ptr(), boundary_ptr, lut.data_ptr(), lut.size(1), b, n, h, r, dv,
-                                          int(ctas), out.data_ptr(), norm.data_ptr(), workspace.data_ptr(), size,
-                                          _stream(sq)))
+                                          hard.data_ptr(), boundary_ptr, documents_ptr, rows, lut.data_ptr(),
+                                          lut.size(1), b, n, h, r, dv, int(ctas), out.data_ptr(), norm.data_ptr(),
+                                          workspace.data_ptr(), size, _stream(sq)))
     return out, norm
 
 
 def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None):
     """x = (sq, sk, v, dO, query labels, key labels, hard) -> [dSQ f32, dSK bf16, dV bf16, dtau f32[H]]."""
-    _no_table(table, choice)
+    _no_table(None, choice)
     b, n, h, r = _vectors(x, 7, ('SQ', 'SK', 'V', 'dO', 'query labels', 'key labels', 'hard'))
     sq, sk, v, dout, iq, ik, hard = x
     _check(sq, torch.bfloat16, (b, n, h, r), 'SQ')
@@ -192,10 +313,10 @@ def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None)
     _check(iq, torch.int32, (b, h, n), 'query labels')
     _check(ik, torch.int32, (b, h, n), 'key labels')
     _check(normalizer, torch.float32, (b, h, n), 'log2 normalizer')
-    if not (torch.is_tensor(hard) and hard.dtype == torch.bool and tuple(hard.shape) == (b, h)
-            and hard.is_contiguous() and hard.device == sq.device):
+    if table is None and not (torch.is_tensor(hard) and hard.dtype == torch.bool and tuple(hard.shape) == (b, h)
+                              and hard.is_contiguous() and hard.device == sq.device):
         _fail('sequence hard flags: invalid device, dtype, shape or stride')
-    _check_lut(lut, h, n, sq.device)
+    documents_ptr, rows = _layout_arguments(table, hard, boundary, lut, b, h, n, sq.device)
     if ctas < 0:
         _fail('invalid CTA count')
     boundary_ptr = _check_boundary(boundary, b, h, n, sq.device)
@@ -207,7 +328,8 @@ def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None)
         workspace = torch.empty((size,), dtype=torch.uint8, device=sq.device)
         _lib.check(_abi.dism_hard_backward(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), dout.data_ptr(),
                                            iq.data_ptr(), ik.data_ptr(), hard.data_ptr(), boundary_ptr,
-                                           lut.data_ptr(), lut.size(1), normalizer.data_ptr(), b, n, h, r, dv,
+                                           documents_ptr, rows, lut.data_ptr(), lut.size(1), normalizer.data_ptr(),
+                                           b, n, h, r, dv,
                                            int(ctas), dsq.data_ptr(), dsk.data_ptr(), dv_out.data_ptr(),
                                            dtau.data_ptr(), workspace.data_ptr(), size, _stream(sq)))
     return [dsq, dsk, dv_out, dtau]

@@ -6,3 +6,4 @@ so callers and tests written against the reference import unchanged.
 from .summary import summarize_hard, hard_chunk_scan
 from .hard_forward import forward_hard, hard_readout, hard_log_weights
 from .hard_backward import backward_hard, backward_hard_recompute
+from .varlen import VarlenLayout

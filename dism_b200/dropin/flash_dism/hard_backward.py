@@ -18,6 +18,14 @@ def backward_hard(sq, sk, v, dout, idx_q, idx_k, hard, normalizer, state, *, lay
 def backward_hard_recompute(sq, sk, v, dout, iq, ik, hard, tau, *, layout=None, ctas=0, _graph_choice=None):
     """Backward without retained state: the forward is run again for the normaliser, nothing
     quadratic is materialised.  Returns a dict keyed sq_vec, sk_vec, v, rtau."""
+    if layout is not None:
+        n = sq.shape[1]
+        if sq.shape[0] != 1 or hard.ndim != 2 or n % hard.shape[0] or layout.tokens != n:
+            raise ValueError('invalid packed fallback rows')
+        row_tokens = n // hard.shape[0]
+        if any(length and begin // row_tokens != (begin + length - 1) // row_tokens
+               for begin, length, *_ in layout.table.tolist()):
+            raise ValueError('document crosses original hard row')
     sq, sk, v, dout = (t.contiguous() for t in (sq, sk, v, dout))
     iq, ik = (t.to(torch.int32).contiguous() for t in (iq, ik))
     hard, tau = hard.contiguous(), tau.contiguous()

@@ -51,15 +51,20 @@ int dism_hard_log_weights(const float *tau, int heads, int n, float *lut, void *
 size_t dism_hard_readout_workspace(int batch, int heads, int n);
 
 /* Fused hard readout.  `boundary` is the rectangle of dism_hard_chunk or NULL (the kernel then
- * derives run lengths from the labels alone); lut has row stride lut_stride > N.
+ * derives run lengths from the labels alone); lut has row stride lut_stride > N (packed: > the
+ * longest document).  Packed layout (the reference's `table` argument, dism_v3/src/host/hard_forward.cpp:
+ * 56-85): batch 1, `documents` is a device int32 [N/256, 2] table giving, for every 256-position
+ * block, the [begin, end) of the 256-aligned document that contains it, and `hard` is
+ * [hard_rows, H] over equal training rows of N / hard_rows positions; fixed layout: documents NULL,
+ * hard_rows = batch.
  * out bf16 [B,N,H,DV], lse2 float [B,H,N]; soft (batch, head) rows are written as zeros.
  * R in {16,32}, DV in {32,64,128}; vectors 16-byte aligned.  `workspace` is caller-owned scratch of
  * dism_hard_readout_workspace bytes, 256-byte aligned; its contents are dead after the call.
  * Stands in for cu_flash_dism.hard_readout (dism_v3/src/host/hard_forward.cpp:25-113). */
 int dism_hard_readout(const void *sq, const void *sk, const void *v, const int32_t *iq, const int32_t *ik,
-                      const uint8_t *hard, const int32_t *boundary, const float *lut, int lut_stride,
-                      int batch, int n, int heads, int r, int dv, int ctas, void *out, float *lse2,
-                      void *workspace, size_t workspace_bytes, void *stream);
+                      const uint8_t *hard, const int32_t *boundary, const int32_t *documents, int hard_rows,
+                      const float *lut, int lut_stride, int batch, int n, int heads, int r, int dv, int ctas,
+                      void *out, float *lse2, void *workspace, size_t workspace_bytes, void *stream);
 
 /* The same readout for callers that cannot supply scratch memory (an operator hook that only gets its
  * input and output buffers, a server whose memory pool already holds the whole GPU: cudaMalloc there
@@ -82,13 +87,14 @@ size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride)
 
 /* Hard backward: dsq float [B,N,H,R], dsk bf16 [B,N,H,R], dv bf16 [B,N,H,DV], dtau float [H]
  * (gradient of the natural-log coefficient).  lse2 is the normaliser the forward returned;
- * `boundary` may be NULL; `workspace` is caller-owned scratch of dism_hard_backward_workspace bytes.
+ * `boundary` may be NULL; `documents`/`hard_rows` as in dism_hard_readout; `workspace` is caller-owned scratch of dism_hard_backward_workspace bytes.
  * Stands in for cu_flash_dism.hard_backward (dism_v3/src/host/hard_backward.cpp:13-141). */
 int dism_hard_backward(const void *sq, const void *sk, const void *v, const void *dout, const int32_t *iq,
-                       const int32_t *ik, const uint8_t *hard, const int32_t *boundary, const float *lut,
-                       int lut_stride, const float *lse2, int batch, int n, int heads, int r, int dv,
-                       int ctas, float *dsq, void *dsk, void *dv_out, float *dtau, void *workspace,
-                       size_t workspace_bytes, void *stream);
+                       const int32_t *ik, const uint8_t *hard, const int32_t *boundary,
+                       const int32_t *documents, int hard_rows, const float *lut, int lut_stride,
+                       const float *lse2, int batch, int n, int heads, int r, int dv, int ctas, float *dsq,
+                       void *dsk, void *dv_out, float *dtau, void *workspace, size_t workspace_bytes,
+                       void *stream);
 
 /* Single longest earlier match of symbol streams int32 [B,N] (labels of queries and keys are
  * the same stream): for every i the most recent j < i with the longest run L(i,j), its length,

@@ -311,3 +311,66 @@ def test_validation_errors(api):
         api['bwd'].backward_hard(*x[:3], x[2], *x[3:5], x[5][:, :, None].expand_as(x[3]).contiguous(), norm, state)
     with pytest.raises(RuntimeError, match='head'):
         api['summary'].hard_chunk_scan(state['summary'], heads=5)
+
+
+# ---- packed documents ----------------------------------------------------------------------------------
+def packed_case(api, pattern):
+    from flash_dism.varlen import VarlenLayout
+    n = 2048
+    q, k = reference_labels(n, pattern, b=1, h=2)
+    sq, sk, v, dout = vectors(77, 1, n, 2, 32, 64)
+    x = [sq.cuda(), sk.cuda(), v.cuda(), dev(q), dev(k), torch.tensor([[True, False], [False, True]], device='cuda'),
+         torch.tensor([.5, -.25], device='cuda')]
+    offsets = [0, 0, 256, 512, 1024, 1024, 2048]
+    layout = VarlenLayout.from_cu_seqlens(torch.tensor(offsets, dtype=torch.int32), n)
+    return x, dout.cuda(), layout, [(a, z) for a, z in zip(offsets, offsets[1:]) if z > a]
+
+
+def document(x, dout, start, end):
+    return ([t[:, start:end].contiguous() for t in x[:3]] + [t[:, :, start:end].contiguous() for t in x[3:5]] +
+            [x[5][start // 1024:start // 1024 + 1].contiguous(), x[6]], dout[:, start:end].contiguous())
+
+
+@pytest.mark.parametrize('pattern', ['random', 'equal', 'periodic', 'boundary'])
+def test_packed_documents_match_fixed_length(api, oracle, pattern):
+    x, dout, layout, spans = packed_case(api, pattern)
+    out, norm = api['fwd'].forward_hard(*x, layout=layout, ctas=1)
+    grads = api['bwd'].backward_hard_recompute(*x[:3], dout, *x[3:], layout=layout)
+    dtau = torch.zeros(2, device='cuda')
+    for start, end in spans:
+        local, local_dout = document(x, dout, start, end)
+        want, want_norm = api['fwd'].forward_hard(*local)
+        assert torch.equal(out[:, start:end], want) and torch.equal(norm[:, :, start:end], want_norm)
+        local_grads = api['bwd'].backward_hard_recompute(*local[:3], local_dout, *local[3:])
+        for name in ('sq_vec', 'sk_vec', 'v'):
+            assert torch.equal(grads[name][:, start:end], local_grads[name])
+        dtau += local_grads['rtau']
+        f = lambda t: t.float().cpu().numpy()
+        expected, _ = oracle.forward(f(local[0]), f(local[1]), f(local[2]), local[3].cpu().numpy(), local[4].cpu().numpy(),
+                                     local[5].cpu().numpy(), f(local[6]))
+        assert_vectors(want, expected)
+    torch.testing.assert_close(grads['rtau'], dtau, atol=2e-3, rtol=1e-4)  # same terms, different summation tree
+    # a change inside the first document leaves the later ones untouched
+    x[2][:, :256] += 5
+    changed, changed_norm = api['fwd'].forward_hard(*x, layout=layout)
+    assert torch.equal(changed[:, 256:], out[:, 256:]) and torch.equal(changed_norm, norm)
+
+
+def test_packed_summary_chunk_and_errors(api, oracle):
+    x, dout, layout, spans = packed_case(api, 'boundary')
+    summary = api['summary'].summarize_hard(x[3], x[4], x[5], layout=layout)
+    boundary = api['summary'].hard_chunk_scan(summary, layout=layout, heads=2)
+    expected = []
+    for start, end in spans:
+        flags = x[5][start // 1024:start // 1024 + 1].cpu().numpy()
+        expected.append(oracle.boundary_numpy(x[3][:, :, start:end].cpu().numpy(), x[4][:, :, start:end].cpu().numpy(),
+                                              flags).ravel())
+    assert np.array_equal(boundary.cpu().numpy(), np.concatenate(expected))
+    from flash_dism.varlen import VarlenLayout
+    whole = VarlenLayout.from_cu_seqlens(torch.tensor([0, 2048], dtype=torch.int32), 2048)
+    with pytest.raises(RuntimeError, match='cross a hard training-row'):
+        api['fwd'].forward_hard(*x, layout=whole)
+    with pytest.raises(RuntimeError, match='aligned'):
+        VarlenLayout.from_cu_seqlens(torch.tensor([0, 100, 2048], dtype=torch.int32), 2048)
+    empty = VarlenLayout.from_cu_seqlens(torch.tensor([0, 0, 0], dtype=torch.int32), 0)
+    assert api['summary'].hard_chunk_scan(torch.empty(0, device='cuda', dtype=torch.int32), layout=empty, heads=2).numel() == 0

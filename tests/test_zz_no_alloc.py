@@ -40,7 +40,7 @@ def test_static_readout_matches_workspace_readout_twice():
         size = lib.dism_hard_readout_workspace(b, h, n)
         workspace = torch.empty(size, dtype=torch.uint8, device='cuda')
         _lib.check(lib.dism_hard_readout(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), iq.data_ptr(), ik.data_ptr(),
-                                         hard.data_ptr(), None, lut.data_ptr(), n + 1, b, n, h, r, dv, 0,
+                                         hard.data_ptr(), None, None, b, lut.data_ptr(), n + 1, b, n, h, r, dv, 0,
                                          want.data_ptr(), want_norm.data_ptr(), workspace.data_ptr(), size, stream))
         got, got_norm = torch.full_like(want, float('nan')), torch.full_like(want_norm, float('nan'))
         status = lib.dism_hard_readout_static(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), iq.data_ptr(), ik.data_ptr(),
