@@ -37,7 +37,7 @@ KERNEL_BYTES = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at the full shape, from the ncu captures
 # summarised under profiles/ (captured at batch 2 and scaled by 4: traffic grows with the rows).
-TRAFFIC = {}
+TRAFFIC = {'labels': 138.5e6, 'hard_forward': 301e6, 'hard_backward_query': 466e6, 'hard_backward_key': 494e6}
 STEP_BYTES = 2 * 132 + 396 + 716  # whole path: two label launches, forward, backward (inputs counted once)
 
 
