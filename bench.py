@@ -185,33 +185,60 @@ def run_ours(args):
                                   'stage_ms': dict(zip(('labels', 'forward', 'backward'), map(float, stage_ms))),
                                   'kernel_ms': kernel_ms}))
             return
-        # end to end: pinned host inputs in, results out, every step
+        # end to end: every step copies its inputs from pinned host memory and all of its results back.
+        # Steps are pipelined over three streams (copy in, compute, copy out) with two buffer sets, as a
+        # training loop that prefetches its next batch would do; the timed region covers all of it.
         copy_names = ('q', 'k', 'sq', 'sk', 'v', 'dout')
         h2d = sum(host[k].numel() * host[k].element_size() for k in copy_names)
-        result_host = None
+        copy_in, compute, copy_out = (torch.cuda.Stream(device) for _ in range(3))
+        staged = [{k: torch.empty_like(resident[k]) for k in copy_names} for _ in range(2)]
+        results = [None, None]
+        result_host = [None, None]
+        ready_in = [torch.cuda.Event() for _ in range(2)]
+        done_compute = [torch.cuda.Event() for _ in range(2)]
+        done_out = [torch.cuda.Event() for _ in range(2)]
+        d2h = [0]
 
-        def e2e_step():
-            nonlocal result_host
-            x = {k: host[k].to(device, non_blocking=True) for k in copy_names}
-            out, norm, grads = step(x)
-            outputs = [out, norm, *grads]
-            if result_host is None:
-                result_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outputs]
-            for dst, src in zip(result_host, outputs):
-                dst.copy_(src, non_blocking=True)
-            return outputs
+        def e2e_step(index):
+            slot = index % 2
+            with torch.cuda.stream(copy_in):
+                copy_in.wait_event(done_compute[slot])  # the previous user of this input buffer has finished
+                for k in copy_names:
+                    staged[slot][k].copy_(host[k], non_blocking=True)
+                ready_in[slot].record(copy_in)
+            with torch.cuda.stream(compute):
+                compute.wait_event(ready_in[slot])
+                compute.wait_event(done_out[slot])  # the previous results of this slot have left the device
+                out, norm, grads = step(staged[slot])
+                results[slot] = [out, norm, *grads]
+                done_compute[slot].record(compute)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(done_compute[slot])
+                if result_host[slot] is None:
+                    result_host[slot] = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in results[slot]]
+                for dst, src in zip(result_host[slot], results[slot]):
+                    dst.copy_(src, non_blocking=True)
+                    src.record_stream(copy_out)
+                done_out[slot].record(copy_out)
+            d2h[0] = sum(o.numel() * o.element_size() for o in results[slot])
 
-        for _ in range(min(args.warmup, 3)):
-            e2e_step()
+        for index in range(4):
+            e2e_step(index)
         barrier()
-        e2e_steps = max(2, min(args.steps, 5))
-        e2e_start = _event()
-        for _ in range(e2e_steps):
-            outputs = e2e_step()
-        e2e_stop = _event()
+        e2e_steps = max(4, args.steps)
+        e2e_start = torch.cuda.Event(enable_timing=True)
+        e2e_stop = torch.cuda.Event(enable_timing=True)
+        e2e_start.record(torch.cuda.current_stream())
+        for stream in (copy_in, compute, copy_out):
+            stream.wait_event(e2e_start)
+        for index in range(e2e_steps):
+            e2e_step(index)
+        for stream in (copy_in, compute, copy_out):
+            torch.cuda.current_stream().wait_stream(stream)
+        e2e_stop.record(torch.cuda.current_stream())
         barrier()
         e2e_ms = e2e_start.elapsed_time(e2e_stop)
-        d2h = sum(o.numel() * o.element_size() for o in outputs)
+        d2h = d2h[0]
 
     times = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
     if world > 1:
