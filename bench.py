@@ -356,6 +356,78 @@ def run_reference(args):
         'e2e': {'value': value, 'unit': 'positions/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
 
 
+def run_other_workload(args):
+    """The two side workloads: forward only on the long-context shape (one GPU's share: 4 heads of
+    N = 131072 with planted 1024-long runs), and the single-longest-match reduction on symbol streams."""
+    import dism_b200
+    dism_b200.install_dropin()
+    import cu_flash_dism as cu
+    from flash_dism.hard_forward import forward_hard
+    torch.cuda.set_device(0)
+    g = torch.Generator(device='cuda').manual_seed(0)
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / args.steps
+
+    if args.workload == 'long_context':
+        b, h, n, d, r, dv, vocab = 1, 4, 131072, 64, 32, 64, 512
+        k = torch.randn(b, n, h, d, generator=g, device='cuda').bfloat16()
+        q = torch.randn(b, n, h, d, generator=g, device='cuda').bfloat16()
+        rng = np.random.default_rng(0)
+        for start in range(4096, n, 4096):  # queries of a window repeat the keys of an earlier window
+            target = start + int(rng.integers(0, 3072))
+            source = int(rng.integers(0, target - 1024))
+            q[:, target:target + 1024] = k[:, source:source + 1024]
+        codebook = torch.nn.functional.silu(torch.randn(h, vocab, d, generator=g, device='cuda')).bfloat16()
+        sq, sk = [(torch.nn.functional.silu(torch.randn(b, n, h, r, generator=g, device='cuda')) * .4).bfloat16()
+                  for _ in range(2)]
+        v = torch.randn(b, n, h, dv, generator=g, device='cuda').bfloat16()
+        hard, tau = torch.ones(b, h, dtype=torch.bool, device='cuda'), torch.full((h,), .05, device='cuda')
+        iq, ik = cu.labels(q, codebook), cu.labels(k, codebook)  # one shared codebook, so copied rows match
+        ms_labels = timed(lambda: (cu.labels(q, codebook), cu.labels(k, codebook)))
+        ms_forward = timed(lambda: forward_hard(sq, sk, v, iq, ik, hard, tau))
+        from dism_b200 import _lib
+        _lib.load().dism_profile_enable(1)
+        _, norm = forward_hard(sq, sk, v, iq, ik, hard, tau)
+        torch.cuda.synchronize()
+        kernel_ms = dict(_lib.kernel_timings())
+        _lib.load().dism_profile_enable(0)
+        print(json.dumps({'workload': 'long context forward, B1 H4 N131072 (one GPU of eight), planted 1024-long runs',
+                          'metric': 'query positions/s', 'value': b * h * n / ((ms_labels + ms_forward) * 1e-3),
+                          'ms_labels': ms_labels, 'ms_forward': ms_forward, 'kernel_ms': kernel_ms,
+                          'max_log2_normaliser': float(norm.max()),
+                          'steps': args.steps, 'warmup': args.warmup}))
+    else:
+        batch, n = 4, 4096
+        rng = np.random.default_rng(0)
+        streams = np.empty((batch, n), np.int32)
+        for row in range(batch):
+            s = list(rng.integers(0, 256, 512))
+            while len(s) < n:
+                length = int(rng.integers(16, 513))
+                if rng.random() < .5:
+                    at = int(rng.integers(0, len(s)))
+                    for t in range(length):
+                        s.append(s[at + t])
+                else:
+                    s.extend(rng.integers(0, 256, length))
+            streams[row] = s[:n]
+        device = torch.from_numpy(streams).cuda()
+        ms = timed(lambda: cu.longest_match(device))
+        print(json.dumps({'workload': 'symbol streams [4, 4096] over 256 symbols, single longest earlier match',
+                          'metric': 'positions/s', 'value': batch * n / (ms * 1e-3), 'ms': ms,
+                          'steps': args.steps, 'warmup': args.warmup}))
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument('--gpus', type=int, default=1)
@@ -365,9 +437,13 @@ def main():
     # profiling aids (ncu captures want a small case and no host-side work); not for reported numbers
     parser.add_argument('--batch', type=int, default=SHAPE['batch'])
     parser.add_argument('--kernels-only', action='store_true', help='skip the end-to-end and CPU-baseline legs')
+    parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams'],
+                        help='side workloads print their own line; the benchmark contract is the training shape')
     args = parser.parse_args()
     SHAPE['batch'] = args.batch
-    if args.impl == 'reference':
+    if args.workload != 'training':
+        run_other_workload(args)
+    elif args.impl == 'reference':
         run_reference(args)
     else:
         run_ours(args)
