@@ -41,7 +41,8 @@ struct QueryBackwardPolicy {
 
     float query[8], derivative[VPL], dsq[8], u, v, w, z, norm, center;
 
-    __device__ __forceinline__ void begin(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active) {
+    __device__ __forceinline__ void begin(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active,
+                                          bool) {
         u = v = w = z = norm = center = 0.f;
 #pragma unroll
         for (int c = 0; c < 8; ++c) { query[c] = 0.f; dsq[c] = 0.f; }
@@ -75,6 +76,18 @@ struct QueryBackwardPolicy {
             for (int c = 0; c < 8; ++c) dsq[c] = fmaf(pe, key[c], dsq[c]);
         }
     }
+    // Adds up the eight lane groups' partial sums of one row (same tree on every lane).
+    __device__ __forceinline__ void merge_groups() {
+#pragma unroll
+        for (int step = 4; step < 32; step <<= 1) {
+            u += __shfl_xor_sync(FULL, u, step);
+            v += __shfl_xor_sync(FULL, v, step);
+            w += __shfl_xor_sync(FULL, w, step);
+            z += __shfl_xor_sync(FULL, z, step);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) dsq[c] += __shfl_xor_sync(FULL, dsq[c], step);
+        }
+    }
     __device__ __forceinline__ void finish(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active) {
         float term = 0.f;
         if (active) {
@@ -104,7 +117,8 @@ struct KeyBackwardPolicy {
 
     float key[8], value[VPL], dv[VPL], dsk[8];
 
-    __device__ __forceinline__ void begin(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active) {
+    __device__ __forceinline__ void begin(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active,
+                                          bool) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) { key[c] = 0.f; dsk[c] = 0.f; }
 #pragma unroll
@@ -131,6 +145,15 @@ struct KeyBackwardPolicy {
             for (int c = 0; c < VPL; ++c) dv[c] = fmaf(ps, derivative[c], dv[c]);
 #pragma unroll
             for (int c = 0; c < 8; ++c) dsk[c] = fmaf(pe, query[c], dsk[c]);
+        }
+    }
+    __device__ __forceinline__ void merge_groups() {
+#pragma unroll
+        for (int step = 4; step < 32; step <<= 1) {
+#pragma unroll
+            for (int c = 0; c < VPL; ++c) dv[c] += __shfl_xor_sync(FULL, dv[c], step);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) dsk[c] += __shfl_xor_sync(FULL, dsk[c], step);
         }
     }
     __device__ __forceinline__ void finish(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool) {

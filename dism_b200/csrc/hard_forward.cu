@@ -44,9 +44,12 @@ struct ForwardPolicy {
 
     float query[8], acc[VPL], maximum, denominator;
 
-    __device__ __forceinline__ void begin(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active) {
+    // `leading` is false for the lane groups that reduce a later part of a shared row: the unit
+    // fallback of the normaliser is counted once, by the leading group.
+    __device__ __forceinline__ void begin(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active,
+                                          bool leading) {
         maximum = 0.f;
-        denominator = 1.f;
+        denominator = leading ? 1.f : 0.f;
 #pragma unroll
         for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
 #pragma unroll
@@ -73,6 +76,20 @@ struct ForwardPolicy {
             const float weight = p * s;
 #pragma unroll
             for (int c = 0; c < VPL; ++c) acc[c] = fmaf(weight, value[c], acc[c]);
+        }
+    }
+    // Combines the eight lane groups' partial results of one row (same tree on every lane).
+    __device__ __forceinline__ void merge_groups() {
+#pragma unroll
+        for (int step = 4; step < 32; step <<= 1) {
+            const float other_maximum = __shfl_xor_sync(FULL, maximum, step);
+            const float other_denominator = __shfl_xor_sync(FULL, denominator, step);
+            const float merged = fmaxf(maximum, other_maximum);
+            const float mine = ex2(maximum - merged), theirs = ex2(other_maximum - merged);
+            denominator = denominator * mine + other_denominator * theirs;
+#pragma unroll
+            for (int c = 0; c < VPL; ++c) acc[c] = acc[c] * mine + __shfl_xor_sync(FULL, acc[c], step) * theirs;
+            maximum = merged;
         }
     }
     __device__ __forceinline__ void finish(const Args& a, const RowContext& ctx, int row, int part, bool, bool active) {

@@ -1,6 +1,11 @@
 // Skeleton shared by the three row-owned kernels of the hard path (forward, query-major backward,
 // key-major backward).
 //
+// A row with very many partners (a popular label in a long sequence) would keep one lane group
+// busy long after everything else has finished, so such rows are taken out of the groups: a whole
+// warp handles one of them, its eight lane groups each reduce one contiguous eighth of the
+// partner range, and the eight partial results are merged in a fixed shuffle tree.
+//
 // A CTA takes 256 consecutive rows of one (batch, head).  Rows differ a lot in how many partners
 // they have (a popular label has a big bucket), so the CTA first orders its rows by an estimate
 // of that load and its warps then pull groups of eight similar rows from the ordered list: the
@@ -14,6 +19,7 @@ namespace dism {
 
 constexpr int TASK_ROWS = 256;  // rows per CTA task (sequence lengths are multiples of 256)
 constexpr int LOAD_BINS = 64;
+constexpr int HEAVY_ROW = 256;  // rows with at least this many partners are shared by a whole warp
 
 struct RowContext {  // what a task's rows share
     const int *iq, *ik, *boundary;
@@ -30,6 +36,8 @@ struct RowsShared {
     int first[TASK_ROWS], last[TASK_ROWS];      // the row's bucket range in the partner index
     int bin_count[LOAD_BINS], bin_start[LOAD_BINS];
     int next_group;
+    int heavy[TASK_ROWS];  // local numbers of the rows handled one per warp
+    int heavy_count;
 };
 
 // Search state of one owned row, replicated in the four lanes of its group.
@@ -183,7 +191,7 @@ __global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(cons
         // ---- order the task's rows by estimated load, heaviest first -------------------------------
         __syncthreads();
         if (threadIdx.x < LOAD_BINS) shared.rows.bin_count[threadIdx.x] = 0;
-        if (threadIdx.x == 0) shared.rows.next_group = 0;
+        if (threadIdx.x == 0) shared.rows.next_group = shared.rows.heavy_count = 0;
         __syncthreads();
         const int my_row = block * TASK_ROWS + threadIdx.x;
         int bin = 0;
@@ -201,6 +209,11 @@ __global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(cons
             // small counts, steps of 16 above
             const int count = last - first;
             bin = count < 48 ? count : min(LOAD_BINS - 1, 48 + (count - 48) / 16);
+            if (count >= HEAVY_ROW) {  // handled by a whole warp later: an empty row as far as the groups go
+                shared.rows.heavy[atomicAdd(&shared.rows.heavy_count, 1)] = threadIdx.x;
+                shared.rows.first[threadIdx.x] = -1 - first;  // marks the row; the range is recovered from it
+                bin = 0;
+            }
         }
         const int rank_in_bin = atomicAdd(&shared.rows.bin_count[bin], 1);
         __syncthreads();
@@ -221,23 +234,35 @@ __global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(cons
         shared.rows.order[shared.rows.bin_start[bin] + rank_in_bin] = threadIdx.x;
         __syncthreads();
 
-        // ---- warps pull groups of eight rows ----------------------------------------------------------
+        // ---- warps pull work items: first the groups of eight rows, then the heavy rows ---------------------
         for (;;) {
             int chosen = 0;
             if (lane == 0) chosen = atomicAdd(&shared.rows.next_group, 1);
             chosen = __shfl_sync(FULL, chosen, 0);
-            if (chosen >= TASK_ROWS / OWN) break;
-            const int local = shared.rows.order[chosen * OWN + group];
-            const int row = block * TASK_ROWS + local;  // the row this lane group owns
+            const int shared_item = chosen - TASK_ROWS / OWN;  // >= 0: one heavy row for the whole warp
+            if (shared_item >= shared.rows.heavy_count) break;
+            const bool whole_warp = shared_item >= 0;
+            const int local = whole_warp ? shared.rows.heavy[shared_item] : shared.rows.order[chosen * OWN + group];
+            const int row = block * TASK_ROWS + local;  // the row this lane group works on
+            const int first = shared.rows.first[local], last = shared.rows.last[local];
+            // a heavy row (marked by a negative start) is skipped by its group and done by a whole warp later
+            const bool mine_to_do = active && (whole_warp || first >= 0);
             Policy state;
-            state.begin(a, ctx, row, part, has_r, active);
+            state.begin(a, ctx, row, part, has_r, mine_to_do, !whole_warp || group == 0);
             if (active) {
                 SearchRow search;
                 search.row = row;
                 search.label = shared.rows.label[local];
                 search.previous = shared.rows.previous[local];
-                search.cursor = shared.rows.first[local];
-                search.end = shared.rows.last[local];
+                search.cursor = search.end = 0;
+                if (whole_warp) {  // an eighth of the partner range per lane group
+                    const int from = -1 - first, share = (last - from + OWN - 1) / OWN;
+                    search.cursor = min(from + group * share, last);
+                    search.end = min(search.cursor + share, last);
+                } else if (first >= 0) {
+                    search.cursor = first;
+                    search.end = last;
+                }
                 search.queued = 0;
                 for (;;) {
                     // scan while some group can take 32 more; otherwise weigh and drain every queue
@@ -263,8 +288,9 @@ __global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(cons
                     search.queued = 0;
                     __syncwarp();
                 }
+                if (whole_warp) state.merge_groups();
             }
-            state.finish(a, ctx, row, part, has_r, active);
+            if (whole_warp ? group == 0 : (!active || first >= 0)) state.finish(a, ctx, row, part, has_r, active);
         }
     }
 }
