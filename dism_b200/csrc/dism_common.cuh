@@ -108,6 +108,7 @@ __device__ __forceinline__ int run_length(const int* __restrict__ q, const int* 
 struct SideIndex {
     const int2* entries;
     const int* starts;
+    const int* previous;  // parallel to entries: the same side's label one position earlier (0 at position 0)
 };
 
 // First entry of bucket range [lo, hi) whose position is >= bound (positions ascend).

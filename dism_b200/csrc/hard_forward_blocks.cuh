@@ -1,0 +1,368 @@
+// Hard forward as label-block tensor-core tiles.
+//
+// Two positions can only interact when their labels are equal, so after both sides are sorted by
+// (label bucket, position) the whole causal pair set is a union of small dense blocks: the
+// queries of a bucket against the keys of the same bucket.  A warp takes sixteen queries of one
+// bucket (one m16 tile), walks the bucket's keys sixteen at a time, and does what a fused
+// attention kernel does on such a tile with bf16 mma.sync: scores = SQ.SK^T, a mask (same label,
+// same document, key not after the query), weights, then acc += P.V.  The rows of SQ are
+// gathered once per tile and the rows of SK and V once per (tile, key step) instead of once per
+// pair.
+//
+// Weights.  Almost every matching pair has run length 1 and therefore the same table entry
+// lut[1]; its weight relative to the row's running maximum is one constant per row and key step
+// and is folded into the score before the bf16 rounding.  A pair whose diagonal predecessor
+// matches as well (run length >= 2) is rare in sparse data; those pairs are left out of the
+// tiles and added one by one by the whole warp, in ascending key order, which walks the diagonal
+// for the run length.  The running maximum and denominator follow the reference's online
+// normalisation (maximum starts at 0, denominator at 1).  Each row is reduced by one warp in a
+// fixed order: results do not depend on the grid.
+#pragma once
+#include "dism_common.cuh"
+
+namespace dism {
+
+constexpr int QT = 16;  // queries per tile (the m of m16n8k16)
+constexpr int KT = 16;  // keys per step: two n8 score tiles, one k16 step of the value product
+constexpr int BLOCK_WARPS = 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(unsigned& b0, unsigned& b1, const void* row) {
+    const unsigned address = static_cast<unsigned>(__cvta_generic_to_shared(row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(address));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&pair);
+}
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+    for (int s = 16; s; s >>= 1) x += __shfl_xor_sync(FULL, x, s);
+    return x;
+}
+
+template <int R, int DV>
+struct alignas(16) KeyStage {
+    __nv_bfloat16 sk[KT][R + 8];  // padded rows: fragment loads and ldmatrix rows fall in distinct banks
+    __nv_bfloat16 v[KT][DV + 8];
+    int position[KT], label[KT], previous[KT];
+};
+
+template <int R, int DV>
+struct alignas(16) BlockWarpShared {
+    KeyStage<R, DV> stage[2];
+    int position[QT], label[QT], previous[QT], begin[QT], active[QT];
+};
+
+struct BlockArgs {
+    const __nv_bfloat16 *sq, *sk, *v;
+    const int *iq, *ik, *boundary;
+    const uint8_t* hard;
+    const float* lut;
+    SideIndex keys, queries;
+    const int* tile_starts;  // [BH, BUCKETS + 1]: first query tile of every bucket
+    const int4* tiles;       // [BH, tile capacity]: (first query entry, queries, first key entry, end of key entries)
+    int tile_capacity;
+    const int2* documents;
+    __nv_bfloat16* out;
+    float* lse2;
+    int batch, heads, n, lut_stride, hard_rows;
+};
+
+// Number of 16-query tiles a (batch, head) can have at most: every bucket may end with a partial tile.
+__host__ __device__ inline int tile_capacity_for(int n) { return n / QT + BUCKETS; }
+
+// tile_starts[b] = number of 16-query tiles in the buckets before b, and one descriptor per tile.
+__global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int* __restrict__ query_starts,
+                                                                const int* __restrict__ key_starts,
+                                                                int* __restrict__ tile_starts, int4* __restrict__ tiles,
+                                                                int tile_capacity) {
+    constexpr int PER = BUCKETS / 1024;
+    __shared__ int warp_total[32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    query_starts += int64_t(blockIdx.x) * (BUCKETS + 1);
+    key_starts += int64_t(blockIdx.x) * (BUCKETS + 1);
+    tile_starts += int64_t(blockIdx.x) * (BUCKETS + 1);
+    tiles += int64_t(blockIdx.x) * tile_capacity;
+    int local[PER], sum = 0;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        local[e] = sum;
+        sum += (query_starts[tid * PER + e + 1] - query_starts[tid * PER + e] + QT - 1) / QT;
+    }
+    int prefix = sum;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+        const int other = __shfl_up_sync(FULL, prefix, s);
+        if (lane >= s) prefix += other;
+    }
+    if (lane == 31) warp_total[warp] = prefix;
+    __syncthreads();
+    if (warp == 0) {
+        const int mine = warp_total[lane];
+        int scan = mine;
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+            const int other = __shfl_up_sync(FULL, scan, s);
+            if (lane >= s) scan += other;
+        }
+        warp_total[lane] = scan - mine;
+    }
+    __syncthreads();
+    const int before = warp_total[warp] + prefix - sum;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int bucket = tid * PER + e, first = before + local[e];
+        tile_starts[bucket] = first;
+        const int q0 = query_starts[bucket], q1 = query_starts[bucket + 1];
+        const int k0 = key_starts[bucket], k1 = key_starts[bucket + 1];
+        for (int q = q0, tile = first; q < q1; q += QT, ++tile) tiles[tile] = make_int4(q, min(QT, q1 - q), k0, k1);
+    }
+    if (tid == 1023) tile_starts[BUCKETS] = before + sum;
+}
+
+template <int R, int DV>
+__global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(const BlockArgs a) {
+    constexpr int KSTEPS = R / 16, VTILES = DV / 8;
+    extern __shared__ __align__(16) unsigned char storage[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    auto& mine = reinterpret_cast<BlockWarpShared<R, DV>*>(storage)[warp];
+    const int bh = blockIdx.y, b = bh / a.heads, h = bh % a.heads;
+    const int64_t vec0 = int64_t(b) * a.n * a.heads + h;
+    const int* iq = a.iq + int64_t(bh) * a.n;
+    const int* ik = a.ik + int64_t(bh) * a.n;
+    const int* boundary = a.boundary ? a.boundary + int64_t(bh) * ((a.n - 1) / 32) * a.n : nullptr;
+    const float* lut = a.lut + int64_t(h) * a.lut_stride;
+    const int2* key_entries = a.keys.entries + int64_t(bh) * a.n;
+    const int* key_previous = a.keys.previous + int64_t(bh) * a.n;
+    const int2* query_entries = a.queries.entries + int64_t(bh) * a.n;
+    const int* query_previous = a.queries.previous + int64_t(bh) * a.n;
+    const int4* tiles = a.tiles + int64_t(bh) * a.tile_capacity;
+    const int tile_count = __ldg(a.tile_starts + int64_t(bh) * (BUCKETS + 1) + BUCKETS);
+    const float weight_one = __ldg(lut + 1);
+
+    for (int tile = blockIdx.x * BLOCK_WARPS + warp; tile < tile_count; tile += gridDim.x * BLOCK_WARPS) {
+        const int4 plan = __ldg(tiles + tile);
+        const int q0 = plan.x, queries = plan.y;
+        __syncwarp();
+        if (lane < QT) {
+            int2 entry = make_int2(-1, 0);
+            int previous = 0, begin = 0, active = 0;
+            if (lane < queries) {
+                entry = __ldg(query_entries + q0 + lane);
+                previous = __ldg(query_previous + q0 + lane);
+                int hard_row = b;
+                if (a.documents) {
+                    begin = __ldg(a.documents + entry.x / 256).x;
+                    hard_row = entry.x / (a.n / a.hard_rows);
+                }
+                active = a.hard[hard_row * a.heads + h];
+            }
+            mine.position[lane] = entry.x;
+            mine.label[lane] = entry.y;
+            mine.previous[lane] = previous;
+            mine.begin[lane] = begin;
+            mine.active[lane] = active;
+        }
+        __syncwarp();
+        int position[2], label[2], previous[2], begin[2];
+        bool active[2];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            const int r = g + 8 * s;
+            position[s] = mine.position[r];
+            label[s] = mine.label[r];
+            previous[s] = mine.previous[r];
+            begin[s] = mine.begin[r];
+            active[s] = mine.active[r] != 0;
+        }
+        const int last_query = mine.position[queries - 1];
+        int key_begin = plan.z;
+        const int key_end = plan.w;
+        if (a.documents) {  // packed: the bucket also holds keys of earlier documents
+            int first_begin = mine.begin[0];
+            for (int r = 1; r < queries; ++r) first_begin = min(first_begin, mine.begin[r]);
+            key_begin = lower_bound_position(key_entries, key_begin, key_end, first_begin);
+        }
+
+        unsigned query[KSTEPS][4];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            const unsigned* source = reinterpret_cast<const unsigned*>(a.sq + (vec0 + int64_t(max(position[s], 0)) * a.heads) * R);
+#pragma unroll
+            for (int k = 0; k < KSTEPS; ++k) {
+                query[k][s] = active[s] ? __ldg(source + k * 8 + t) : 0u;
+                query[k][s + 2] = active[s] ? __ldg(source + k * 8 + 4 + t) : 0u;
+            }
+        }
+        float acc[VTILES][4], maximum[2] = {0.f, 0.f}, denominator[2] = {1.f, 1.f};
+#pragma unroll
+        for (int c = 0; c < VTILES; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+
+        // The kind of one score element: 1 = ordinary pair (run length 1), 2 = longer run, 0 = no pair.
+        auto classify = [&](const KeyStage<R, DV>& keys, int s, int column) {
+            const int key_position = keys.position[column];
+            const bool pair = active[s] && keys.label[column] == label[s] && key_position <= position[s] && key_position >= begin[s];
+            const bool longer = pair && key_position > begin[s] && position[s] > begin[s] && keys.previous[column] == previous[s];
+            return pair ? (longer ? 2 : 1) : 0;
+        };
+        // Labels of a key step and its sk / v rows (cp.async); rows beyond the range are zero-filled.
+        auto stage_keys = [&](KeyStage<R, DV>& keys, int k0) {
+            int key_position = 0x7fffffff;
+            if (lane < KT) {
+                int2 entry = make_int2(0x7fffffff, 0);
+                int before = 0;
+                if (k0 + lane < key_end) {
+                    entry = __ldg(key_entries + k0 + lane);
+                    before = __ldg(key_previous + k0 + lane);
+                }
+                key_position = entry.x;
+                keys.position[lane] = entry.x;
+                keys.label[lane] = entry.y;
+                keys.previous[lane] = before;
+            }
+            constexpr int SK_PIECES = KT * R / 8, V_PIECES = KT * DV / 8;
+#pragma unroll
+            for (int piece = lane; piece < SK_PIECES; piece += 32) {
+                const int key = piece / (R / 8), c = piece % (R / 8);
+                const int at = __shfl_sync(FULL, key_position, key);
+                if (at != 0x7fffffff) cp_async16(&keys.sk[key][c * 8], a.sk + (vec0 + int64_t(at) * a.heads) * R + c * 8);
+                else *reinterpret_cast<uint4*>(&keys.sk[key][c * 8]) = make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int piece = lane; piece < V_PIECES; piece += 32) {
+                const int key = piece / (DV / 8), c = piece % (DV / 8);
+                const int at = __shfl_sync(FULL, key_position, key);
+                if (at != 0x7fffffff) cp_async16(&keys.v[key][c * 8], a.v + (vec0 + int64_t(at) * a.heads) * DV + c * 8);
+                else *reinterpret_cast<uint4*>(&keys.v[key][c * 8]) = make_uint4(0, 0, 0, 0);
+            }
+            cp_async_commit();
+        };
+        // Multiplies a row's running state when its maximum rises to x.
+        auto raise = [&](int s, float x) {
+            const float alpha = ex2(maximum[s] - x);
+            denominator[s] *= alpha;
+#pragma unroll
+            for (int c = 0; c < VTILES; ++c) { acc[c][2 * s] *= alpha; acc[c][2 * s + 1] *= alpha; }
+            maximum[s] = x;
+        };
+
+        if (key_begin < key_end) stage_keys(mine.stage[0], key_begin);
+        int buffer = 0;
+        for (int k0 = key_begin; k0 < key_end; k0 += KT, buffer ^= 1) {
+            const bool more = k0 + KT < key_end;
+            if (more) stage_keys(mine.stage[buffer ^ 1], k0 + KT);
+            if (more) cp_async_wait<1>();
+            else cp_async_wait<0>();
+            __syncwarp();
+            const KeyStage<R, DV>& keys = mine.stage[buffer];
+            if (keys.position[0] > last_query) break;  // keys ascend: nothing causal from here on
+
+            float score[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                score[j][0] = score[j][1] = score[j][2] = score[j][3] = 0.f;
+#pragma unroll
+                for (int k = 0; k < KSTEPS; ++k) {
+                    const unsigned* source = reinterpret_cast<const unsigned*>(&keys.sk[j * 8 + g][k * 16]);
+                    mma_bf16_16816(score[j], query[k], source[t], source[4 + t]);
+                }
+            }
+            // one bit per score element of this lane, at s * 4 + j * 2 + e
+            unsigned ordinary_bits = 0, longer_bits = 0;
+#pragma unroll
+            for (int s = 0; s < 2; ++s)
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int kind = classify(keys, s, j * 8 + 2 * t + e);
+                        ordinary_bits |= unsigned(kind == 1) << (s * 4 + j * 2 + e);
+                        longer_bits |= unsigned(kind == 2) << (s * 4 + j * 2 + e);
+                    }
+            int ordinary[2] = {__popc(ordinary_bits & 15u), __popc(ordinary_bits >> 4)};
+            // pairs with longer runs: one at a time, keys ascending, so a row always sees them in the same order
+            if (__ballot_sync(FULL, longer_bits != 0)) {
+#pragma unroll 1
+                for (int column = 0; column < KT; ++column) {
+                    const int j = column >> 3, e = column & 1;
+                    const bool holder = t == ((column & 7) >> 1);
+#pragma unroll
+                    for (int s = 0; s < 2; ++s) {
+                        unsigned waiting = __ballot_sync(FULL, holder && ((longer_bits >> (s * 4 + j * 2 + e)) & 1u));  // lanes = rows g + 8 s, ascending
+                        for (; waiting; waiting &= waiting - 1) {
+                            const int row = ((__ffs(waiting) - 1) >> 2) + 8 * s;
+                            const int qi = mine.position[row], kj = keys.position[column];
+                            const int length = run_length(iq, ik, boundary, a.n, qi, kj, lane, mine.begin[row]);
+                            const float x = __ldg(lut + length);
+                            float product = 0.f;
+                            if (lane < R) product = bf2f(a.sq[(vec0 + int64_t(qi) * a.heads) * R + lane]) * bf2f(keys.sk[column][lane]);
+                            const float value_score = warp_sum(product);
+                            if (g == (row & 7)) {  // the four lanes that hold this row
+                                if (x > maximum[s]) raise(s, x);
+                                const float p = ex2(x - maximum[s]);
+                                denominator[s] += p;
+                                const float weight = p * value_score;
+#pragma unroll
+                                for (int c = 0; c < VTILES; ++c) {
+                                    const float2 pair = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&keys.v[column][c * 8 + 2 * t]));
+                                    acc[c][2 * s] = fmaf(weight, pair.x, acc[c][2 * s]);
+                                    acc[c][2 * s + 1] = fmaf(weight, pair.y, acc[c][2 * s + 1]);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            // ordinary pairs: one weight per row, folded into the score, then the value product on tensor cores
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                ordinary[s] += __shfl_xor_sync(FULL, ordinary[s], 1);
+                ordinary[s] += __shfl_xor_sync(FULL, ordinary[s], 2);
+            }
+            if (__ballot_sync(FULL, ordinary[0] + ordinary[1] > 0)) {
+                float common[2];
+#pragma unroll
+                for (int s = 0; s < 2; ++s) {
+                    if (ordinary[s] > 0 && weight_one > maximum[s]) raise(s, weight_one);
+                    common[s] = ordinary[s] > 0 ? ex2(weight_one - maximum[s]) : 0.f;
+                    denominator[s] = fmaf(common[s], float(ordinary[s]), denominator[s]);
+                }
+                unsigned weights[4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int s = 0; s < 2; ++s)
+                        weights[2 * j + s] = pack_bf16(
+                            (ordinary_bits >> (s * 4 + j * 2)) & 1u ? common[s] * score[j][2 * s] : 0.f,
+                            (ordinary_bits >> (s * 4 + j * 2 + 1)) & 1u ? common[s] * score[j][2 * s + 1] : 0.f);
+#pragma unroll
+                for (int c = 0; c < VTILES; ++c) {
+                    unsigned b0, b1;
+                    ldmatrix_x2_trans(b0, b1, &keys.v[lane & 15][c * 8]);
+                    mma_bf16_16816(acc[c], weights, b0, b1);
+                }
+            }
+            __syncwarp();
+        }
+        cp_async_wait<0>();
+
+        // ---- write the tile's rows --------------------------------------------------------------------------
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            if (g + 8 * s >= queries) continue;
+            const float inverse = active[s] ? 1.f / denominator[s] : 0.f;
+            __nv_bfloat16* out = a.out + (vec0 + int64_t(position[s]) * a.heads) * DV + 2 * t;
+#pragma unroll
+            for (int c = 0; c < VTILES; ++c)
+                *reinterpret_cast<__nv_bfloat162*>(out + c * 8) = __floats2bfloat162_rn(acc[c][2 * s] * inverse, acc[c][2 * s + 1] * inverse);
+            if (t == 0) a.lse2[int64_t(bh) * a.n + position[s]] = active[s] ? maximum[s] + log2f(denominator[s]) : 0.f;
+        }
+    }
+}
+
+}  // namespace dism

@@ -15,8 +15,8 @@ static_assert(PASS_BINS * PASS_BINS == BUCKETS, "two passes cover the bucket num
 // sorts by the high six bits.
 template <bool FIRST>
 __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, const int2* __restrict__ source,
-                                              int2* __restrict__ target, int n, int* base, int* total,
-                                              unsigned short (*counts)[PASS_BINS]) {
+                                              int2* __restrict__ target, int* __restrict__ previous, int n, int* base,
+                                              int* total, unsigned short (*counts)[PASS_BINS]) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid < PASS_BINS) total[tid] = 0;
     __syncthreads();
@@ -61,7 +61,11 @@ __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, co
             total[tid] = running;
         }
         __syncthreads();
-        if (valid) target[base[bin] + counts[warp][bin] + rank] = item;
+        if (valid) {
+            const int to = base[bin] + counts[warp][bin] + rank;
+            target[to] = item;
+            if (!FIRST) previous[to] = item.x > 0 ? labels[item.x - 1] : 0;
+        }
         __syncthreads();
         if (tid < PASS_BINS) base[tid] += total[tid];
         __syncthreads();
@@ -71,6 +75,7 @@ __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, co
 __global__ __launch_bounds__(INDEX_THREADS) void build_index_kernel(const int* __restrict__ labels, int n,
                                                                     int2* __restrict__ entries,
                                                                     int2* __restrict__ scratch,
+                                                                    int* __restrict__ previous,
                                                                     int* __restrict__ starts) {
     __shared__ int base[PASS_BINS], total[PASS_BINS];
     __shared__ unsigned short counts[INDEX_THREADS / 32][PASS_BINS];
@@ -80,6 +85,7 @@ __global__ __launch_bounds__(INDEX_THREADS) void build_index_kernel(const int* _
     labels += int64_t(blockIdx.x) * n;
     entries += int64_t(blockIdx.x) * n;
     scratch += int64_t(blockIdx.x) * n;
+    previous += int64_t(blockIdx.x) * n;
     starts += int64_t(blockIdx.x) * (BUCKETS + 1);
     // bucket starts: histogram of all 4096 buckets and its exclusive scan (four buckets per thread)
     for (int e = tid; e < BUCKETS; e += INDEX_THREADS) histogram[e] = 0;
@@ -116,14 +122,14 @@ __global__ __launch_bounds__(INDEX_THREADS) void build_index_kernel(const int* _
         if (tid == INDEX_THREADS - 1) starts[BUCKETS] = n;
     }
     __syncthreads();
-    counting_pass<true>(labels, nullptr, scratch, n, base, total, counts);
+    counting_pass<true>(labels, nullptr, scratch, nullptr, n, base, total, counts);
     __syncthreads();
-    counting_pass<false>(nullptr, scratch, entries, n, base, total, counts);
+    counting_pass<false>(labels, scratch, entries, previous, n, base, total, counts);
 }
 
-// Per side: entries int2 [BH, N], sort scratch int2 [BH, N], starts int [BH, BUCKETS + 1].
+// Per side: entries int2 [BH, N], sort scratch int2 [BH, N], previous int [BH, N], starts int [BH, BUCKETS + 1].
 size_t index_bytes(int batch_heads, int n, int sides) {
-    size_t one = 2 * size_t(batch_heads) * n * sizeof(int2) + size_t(batch_heads) * (BUCKETS + 1) * sizeof(int);
+    size_t one = size_t(batch_heads) * n * (2 * sizeof(int2) + sizeof(int)) + size_t(batch_heads) * (BUCKETS + 1) * sizeof(int);
     one = (one + 255) & ~size_t(255);
     return one * sides;
 }
@@ -132,8 +138,9 @@ SideIndex side_index(void* workspace, int batch_heads, int n, int side, int side
     const size_t one = index_bytes(batch_heads, n, 1);
     char* p = static_cast<char*>(workspace) + one * side;
     (void)sides;
-    return SideIndex{reinterpret_cast<const int2*>(p),
-                     reinterpret_cast<const int*>(p + 2 * size_t(batch_heads) * n * sizeof(int2))};
+    const size_t items = size_t(batch_heads) * n;
+    return SideIndex{reinterpret_cast<const int2*>(p), reinterpret_cast<const int*>(p + items * (2 * sizeof(int2) + sizeof(int))),
+                     reinterpret_cast<const int*>(p + items * 2 * sizeof(int2))};
 }
 
 cudaError_t launch_build_index(const int* labels, int batch_heads, int n, void* workspace, int side, int sides,
@@ -142,6 +149,7 @@ cudaError_t launch_build_index(const int* labels, int batch_heads, int n, void* 
     int2* entries = const_cast<int2*>(index.entries);
     KernelTimer timer("build_index", stream);
     build_index_kernel<<<batch_heads, INDEX_THREADS, 0, stream>>>(labels, n, entries, entries + size_t(batch_heads) * n,
+                                                                  const_cast<int*>(index.previous),
                                                                   const_cast<int*>(index.starts));
     return cudaGetLastError();
 }

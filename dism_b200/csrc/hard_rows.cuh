@@ -181,7 +181,7 @@ __global__ __launch_bounds__(WARPS * 32, Policy::MIN_CTAS) void rows_kernel(cons
         ctx.lut = a.lut + int64_t(h) * a.lut_stride;
         ctx.dlut = a.dlut ? a.dlut + int64_t(h) * a.lut_stride : nullptr;
         ctx.lse2 = a.lse2 ? a.lse2 + int64_t(bh) * a.n : nullptr;
-        ctx.index = SideIndex{a.index.entries + int64_t(bh) * a.n, a.index.starts + int64_t(bh) * (BUCKETS + 1)};
+        ctx.index = SideIndex{a.index.entries + int64_t(bh) * a.n, a.index.starts + int64_t(bh) * (BUCKETS + 1), nullptr};
         ctx.vec0 = int64_t(b) * a.n * a.heads + h;
         ctx.n = a.n;
         ctx.heads = a.heads;

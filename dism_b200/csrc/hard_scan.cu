@@ -90,7 +90,7 @@ __global__ __launch_bounds__(WARPS * 32) void longest_match_kernel(const int* __
          task += int64_t(gridDim.x) * WARPS) {
         const int b = int(task / groups), row0 = int(task % groups) * OWN;
         const int* s = streams + int64_t(b) * n;
-        const SideIndex mine{index.entries + int64_t(b) * n, index.starts + int64_t(b) * (BUCKETS + 1)};
+        const SideIndex mine{index.entries + int64_t(b) * n, index.starts + int64_t(b) * (BUCKETS + 1), nullptr};
         for (int r = 0; r < OWN; ++r) {
             const int i = row0 + r, label = __ldg(s + i);
             int from, to;
