@@ -5,8 +5,8 @@
 // an inference server whose memory was handed to the server's own pool at start-up, or a plugin
 // hook whose contract forbids device allocation because cudaMalloc serialises the whole device
 // and can fail once that pool holds everything.  Such a caller has no workspace to pass to
-// dism_hard_readout.  This entry point keeps the one piece of scratch the readout needs, the
-// key-side position index, in a fixed array that is part of the library image, so the call
+// dism_hard_readout.  This entry point keeps the scratch the readout needs (the position indices
+// of both sides and the tile plan) in a fixed array that is part of the library image, so the call
 // allocates nothing: no cudaMalloc, no cudaFree, no allocating library routine.
 //
 // The price is a fixed ceiling and shared state.  Every GPU that loads the library holds the
@@ -47,7 +47,7 @@ int dism_hard_readout_static(const void* sq, const void* sk, const void* v, cons
     const size_t needed = dism_hard_readout_workspace(batch, heads, n);
     if (needed > size_t(DISM_READOUT_STATIC_BYTES)) {
         snprintf(static_error, sizeof(static_error),
-                 "shape needs %zu bytes of index but the built-in scratch holds %zu (B*H*N*16 + B*H*16388 bytes must fit); "
+                 "shape needs %zu bytes of scratch but the built-in scratch holds %zu; "
                  "use dism_hard_readout with a caller-owned workspace",
                  needed, size_t(DISM_READOUT_STATIC_BYTES));
         return DISM_EINVAL;

