@@ -40,12 +40,12 @@ int device_sm_count() {
     return sms;
 }
 
-// Workspace: both position indices, the tile descriptors [BH, N/16 + BUCKETS] (16-byte records) and
-// the first-tile table [BH, BUCKETS + 1].
+// Workspace: both position indices, the tile descriptors [BH, N/16 + BUCKETS] (16-byte records), the
+// first-tile table [BH, BUCKETS + 1] and one tile counter per (batch, head).
 size_t hard_forward_workspace_bytes(int batch, int heads, int n) {
     const size_t batch_heads = size_t(batch) * heads;
     return index_bytes(batch * heads, n, 2) + batch_heads * tile_capacity_for(n) * sizeof(int4) +
-           batch_heads * (BUCKETS + 1) * sizeof(int);
+           batch_heads * (BUCKETS + 2) * sizeof(int);
 }
 
 template <int R, int DV>
@@ -55,8 +55,9 @@ static cudaError_t launch_blocks_variant(const BlockArgs& args, int ctas, cudaSt
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
     if (status != cudaSuccess) return status;
     const int batch_heads = args.batch * args.heads;
-    // enough CTAs per (batch, head) for every warp to get a few tiles; `ctas` caps the whole grid
-    int per_head = (args.n / QT + BUCKETS) / (BLOCK_WARPS * 4) + 1;
+    // about eight full tiles per warp (partial tiles of small buckets come on top); `ctas` caps the whole grid
+    int per_head = args.n / (QT * BLOCK_WARPS * 8);
+    if (per_head < 1) per_head = 1;
     if (ctas) per_head = ctas / batch_heads > 0 ? ctas / batch_heads : 1;
     KernelTimer timer("hard_forward", stream);
     kernel<<<dim3(per_head, batch_heads), BLOCK_WARPS * 32, shared, stream>>>(args);
@@ -85,12 +86,13 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
     int* tile_starts = reinterpret_cast<int*>(tiles + size_t(batch_heads) * args.tile_capacity);
     args.tiles = tiles;
     args.tile_starts = tile_starts;
+    args.next_tile = tile_starts + size_t(batch_heads) * (BUCKETS + 1);
     args.out = out; args.lse2 = lse2;
     args.batch = shape.batch; args.heads = shape.heads; args.n = shape.n; args.lut_stride = lut_stride;
     {
         KernelTimer timer("plan_query_tiles", stream);
         plan_query_tiles_kernel<<<batch_heads, 1024, 0, stream>>>(args.queries.starts, args.keys.starts, tile_starts, tiles,
-                                                                  args.tile_capacity);
+                                                                  args.next_tile, args.tile_capacity);
     }
 #define DISM_CASE(RR, VV) \
     if (shape.r == RR && shape.dv == VV) return launch_blocks_variant<RR, VV>(args, ctas, stream);

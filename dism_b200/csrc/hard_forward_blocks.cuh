@@ -66,6 +66,7 @@ struct BlockArgs {
     SideIndex keys, queries;
     const int* tile_starts;  // [BH, BUCKETS + 1]: first query tile of every bucket
     const int4* tiles;       // [BH, tile capacity]: (first query entry, queries, first key entry, end of key entries)
+    int* next_tile;          // [BH]: the next tile to hand out (zeroed by the plan kernel)
     int tile_capacity;
     const int2* documents;
     __nv_bfloat16* out;
@@ -80,7 +81,7 @@ __host__ __device__ inline int tile_capacity_for(int n) { return n / QT + BUCKET
 __global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int* __restrict__ query_starts,
                                                                 const int* __restrict__ key_starts,
                                                                 int* __restrict__ tile_starts, int4* __restrict__ tiles,
-                                                                int tile_capacity) {
+                                                                int* __restrict__ next_tile, int tile_capacity) {
     constexpr int PER = BUCKETS / 1024;
     __shared__ int warp_total[32];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -122,7 +123,10 @@ __global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int* __res
         const int k0 = key_starts[bucket], k1 = key_starts[bucket + 1];
         for (int q = q0, tile = first; q < q1; q += QT, ++tile) tiles[tile] = make_int4(q, min(QT, q1 - q), k0, k1);
     }
-    if (tid == 1023) tile_starts[BUCKETS] = before + sum;
+    if (tid == 1023) {
+        tile_starts[BUCKETS] = before + sum;
+        next_tile[blockIdx.x] = 0;
+    }
 }
 
 template <int R, int DV>
@@ -145,7 +149,12 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
     const int tile_count = __ldg(a.tile_starts + int64_t(bh) * (BUCKETS + 1) + BUCKETS);
     const float weight_one = __ldg(lut + 1);
 
-    for (int tile = blockIdx.x * BLOCK_WARPS + warp; tile < tile_count; tile += gridDim.x * BLOCK_WARPS) {
+    // Tiles differ a lot in their number of key steps, so warps take them one at a time from a counter.
+    for (;;) {
+        int tile = 0;
+        if (lane == 0) tile = atomicAdd(a.next_tile + bh, 1);
+        tile = __shfl_sync(FULL, tile, 0);
+        if (tile >= tile_count) break;
         const int4 plan = __ldg(tiles + tile);
         const int q0 = plan.x, queries = plan.y;
         __syncwarp();
