@@ -9,7 +9,7 @@
 // accumulated by exactly one lane group in ascending partner order, with no atomics, no
 // zero-filled accumulators and bit-identical results for any grid size.  Pair coefficients stay
 // in FP32 (the reference rounds them to BF16 to feed its tensor-core tiles).
-#include "hard_rows.cuh"
+#include "hard_backward_blocks.cuh"
 
 namespace dism {
 
@@ -28,140 +28,6 @@ __global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __rest
     }
     out[int64_t(head) * stride + l] = g;
 }
-
-// ---- query-major pass: dSQ and the per-row tau term ----------------------------------------------
-template <int R_, int DV>
-struct QueryBackwardPolicy {
-    static constexpr bool QUERY_MAJOR = true, EXTRA = true;
-    static constexpr int R = R_, VPL = DV / 4, MIN_CTAS = 2;
-    using Args = RowsArgs;
-    static const char* name() { return "hard_backward_query"; }
-    static __device__ __forceinline__ const __nv_bfloat16* gather_a(const Args& a) { return a.sk; }
-    static __device__ __forceinline__ const __nv_bfloat16* gather_b(const Args& a) { return a.v; }
-
-    float query[8], derivative[VPL], dsq[8], u, v, w, z, norm, center;
-
-    __device__ __forceinline__ void begin(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active,
-                                          bool) {
-        u = v = w = z = norm = center = 0.f;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) { query[c] = 0.f; dsq[c] = 0.f; }
-#pragma unroll
-        for (int c = 0; c < VPL; ++c) derivative[c] = 0.f;
-        if (active) {
-            const int64_t at = ctx.vec0 + int64_t(row) * ctx.heads;
-            if (has_r) load_bf16<8>(a.sq + at * R + part * 8, query);
-            load_bf16<VPL>(a.dout + at * DV + part * VPL, derivative);
-            norm = __ldg(ctx.lse2 + row);
-            center = __ldg(ctx.dlut + row - ctx.begin + 1);  // document-local position
-        }
-    }
-    __device__ __forceinline__ void pair(bool live, float x, float extra, const float (&key)[8], const float (&value)[VPL]) {
-        float partial_s = 0.f, partial_e = 0.f;
-        if (live) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) partial_s = fmaf(query[c], key[c], partial_s);
-#pragma unroll
-            for (int c = 0; c < VPL; ++c) partial_e = fmaf(derivative[c], value[c], partial_e);
-        }
-        const float s = group_sum(partial_s), e = group_sum(partial_e);
-        if (live) {
-            const float p = ex2(x - norm), g = extra - center;
-            const float pse = p * s * e, pe = p * e;
-            u += pse;
-            v = fmaf(p, g, v);
-            w = fmaf(pse, g, w);
-            z += p;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) dsq[c] = fmaf(pe, key[c], dsq[c]);
-        }
-    }
-    // Adds up the eight lane groups' partial sums of one row (same tree on every lane).
-    __device__ __forceinline__ void merge_groups() {
-#pragma unroll
-        for (int step = 4; step < 32; step <<= 1) {
-            u += __shfl_xor_sync(FULL, u, step);
-            v += __shfl_xor_sync(FULL, v, step);
-            w += __shfl_xor_sync(FULL, w, step);
-            z += __shfl_xor_sync(FULL, z, step);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) dsq[c] += __shfl_xor_sync(FULL, dsq[c], step);
-        }
-    }
-    __device__ __forceinline__ void finish(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active) {
-        float term = 0.f;
-        if (active) {
-            // Centred four-moment form: the fallback has unit weight and zero derivative.
-            const float fallback = ex2(-norm), inverse = __fdividef(1.f, z + fallback);
-            const float mean = fmaf(-fallback, center, v) * inverse;
-            term = fmaf(-u, mean, w) * inverse;
-        }
-        if (has_r) {
-            float* out = a.dsq + (ctx.vec0 + int64_t(row) * ctx.heads) * R + part * 8;
-            *reinterpret_cast<float4*>(out) = make_float4(dsq[0], dsq[1], dsq[2], dsq[3]);
-            *reinterpret_cast<float4*>(out + 4) = make_float4(dsq[4], dsq[5], dsq[6], dsq[7]);
-        }
-        if (part == 0) a.dtau_rows[int64_t(ctx.bh) * ctx.n + row] = term;
-    }
-};
-
-// ---- key-major pass: dV and dSK ---------------------------------------------------------------------
-template <int R_, int DV>
-struct KeyBackwardPolicy {
-    static constexpr bool QUERY_MAJOR = false, EXTRA = false;
-    static constexpr int R = R_, VPL = DV / 4, MIN_CTAS = 2;
-    using Args = RowsArgs;
-    static const char* name() { return "hard_backward_key"; }
-    static __device__ __forceinline__ const __nv_bfloat16* gather_a(const Args& a) { return a.sq; }
-    static __device__ __forceinline__ const __nv_bfloat16* gather_b(const Args& a) { return a.dout; }
-
-    float key[8], value[VPL], dv[VPL], dsk[8];
-
-    __device__ __forceinline__ void begin(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool active,
-                                          bool) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) { key[c] = 0.f; dsk[c] = 0.f; }
-#pragma unroll
-        for (int c = 0; c < VPL; ++c) { value[c] = 0.f; dv[c] = 0.f; }
-        if (active) {
-            const int64_t at = ctx.vec0 + int64_t(row) * ctx.heads;
-            if (has_r) load_bf16<8>(a.sk + at * R + part * 8, key);
-            load_bf16<VPL>(a.v + at * DV + part * VPL, value);
-        }
-    }
-    // x is the table entry minus the partner query's log2 normaliser
-    __device__ __forceinline__ void pair(bool live, float x, float, const float (&query)[8], const float (&derivative)[VPL]) {
-        float partial_s = 0.f, partial_e = 0.f;
-        if (live) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) partial_s = fmaf(query[c], key[c], partial_s);
-#pragma unroll
-            for (int c = 0; c < VPL; ++c) partial_e = fmaf(derivative[c], value[c], partial_e);
-        }
-        const float s = group_sum(partial_s), e = group_sum(partial_e);
-        if (live) {
-            const float p = ex2(x), ps = p * s, pe = p * e;
-#pragma unroll
-            for (int c = 0; c < VPL; ++c) dv[c] = fmaf(ps, derivative[c], dv[c]);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) dsk[c] = fmaf(pe, query[c], dsk[c]);
-        }
-    }
-    __device__ __forceinline__ void merge_groups() {
-#pragma unroll
-        for (int step = 4; step < 32; step <<= 1) {
-#pragma unroll
-            for (int c = 0; c < VPL; ++c) dv[c] += __shfl_xor_sync(FULL, dv[c], step);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) dsk[c] += __shfl_xor_sync(FULL, dsk[c], step);
-        }
-    }
-    __device__ __forceinline__ void finish(const Args& a, const RowContext& ctx, int row, int part, bool has_r, bool) {
-        const int64_t at = ctx.vec0 + int64_t(row) * ctx.heads;
-        store_bf16<VPL>(a.dv + at * DV + part * VPL, dv);
-        if (has_r) store_bf16<8>(a.dsk + at * R + part * 8, dsk);
-    }
-};
 
 // dtau[h] = sum over batch and rows of the per-row terms, in a fixed order (thread-strided partial
 // sums, then a tree), so the result is the same for every launch.
@@ -186,10 +52,32 @@ __global__ __launch_bounds__(1024) void tau_reduce_kernel(const float* __restric
     if (threadIdx.x == 0) dtau[head] = partial[0];
 }
 
-// Workspace: both position indices, then the per-row tau terms [B, H, N] (read back as float4, so
-// they come first and stay 16-byte aligned) and the dlog table [H, lut_stride], all FP32.
+// Workspace: both position indices, a tile plan (descriptors, first-tile table, counter) for each of
+// the two passes, then the per-row tau terms [B, H, N] (read back as float4, so 16-byte aligned) and the
+// dlog table [H, lut_stride], FP32.
+static size_t plan_bytes(int batch_heads, int n) {
+    size_t bytes = size_t(batch_heads) * tile_capacity_for(n) * sizeof(int4) + size_t(batch_heads) * (BUCKETS + 2) * sizeof(int);
+    return (bytes + 255) & ~size_t(255);
+}
+
 size_t hard_backward_workspace_bytes(int batch, int heads, int n, int lut_stride) {
-    return index_bytes(batch * heads, n, 2) + sizeof(float) * (size_t(heads) * lut_stride + size_t(batch) * heads * n);
+    return index_bytes(batch * heads, n, 2) + 2 * plan_bytes(batch * heads, n) +
+           sizeof(float) * (size_t(heads) * lut_stride + size_t(batch) * heads * n);
+}
+
+template <bool QUERY_MAJOR, int R, int DV>
+static cudaError_t launch_backward_blocks(const BackwardBlockArgs& args, int ctas, cudaStream_t stream) {
+    auto kernel = hard_backward_blocks_kernel<QUERY_MAJOR, R, DV>;
+    const int shared = sizeof(BackwardWarpShared<R, DV>) * BLOCK_WARPS;
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+    if (status != cudaSuccess) return status;
+    const int batch_heads = args.batch * args.heads;
+    int per_head = args.n / (QT * BLOCK_WARPS * 8);
+    if (per_head < 1) per_head = 1;
+    if (ctas) per_head = ctas / batch_heads > 0 ? ctas / batch_heads : 1;
+    KernelTimer timer(QUERY_MAJOR ? "hard_backward_query" : "hard_backward_key", stream);
+    kernel<<<dim3(per_head, batch_heads), BLOCK_WARPS * 32, shared, stream>>>(args);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,
@@ -203,28 +91,49 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     if (status != cudaSuccess) return status;
     status = launch_build_index(iq, batch_heads, shape.n, workspace, 1, 2, stream);
     if (status != cudaSuccess) return status;
-    float* rows = reinterpret_cast<float*>(static_cast<char*>(workspace) + index_bytes(batch_heads, shape.n, 2));
+    const SideIndex keys = side_index(workspace, batch_heads, shape.n, 0, 2), queries = side_index(workspace, batch_heads, shape.n, 1, 2);
+    char* cursor = static_cast<char*>(workspace) + index_bytes(batch_heads, shape.n, 2);
+    const int capacity = tile_capacity_for(shape.n);
+    int4* tiles[2];
+    int* tile_starts[2];
+    for (int pass = 0; pass < 2; ++pass) {
+        tiles[pass] = reinterpret_cast<int4*>(cursor);
+        tile_starts[pass] = reinterpret_cast<int*>(tiles[pass] + size_t(batch_heads) * capacity);
+        cursor += plan_bytes(batch_heads, shape.n);
+    }
+    float* rows = reinterpret_cast<float*>(cursor);
     float* dlut = rows + size_t(batch_heads) * shape.n;
     {
         KernelTimer timer("dlog_weights", stream);
         dlog_weights_kernel<<<dim3((lut_stride + 255) / 256, shape.heads), 256, 0, stream>>>(lut, dlut, lut_stride);
     }
-    RowsArgs args{};
+    {
+        KernelTimer timer("plan_tiles", stream);
+        plan_query_tiles_kernel<<<batch_heads, 1024, 0, stream>>>(queries.starts, keys.starts, tile_starts[0], tiles[0],
+                                                                  tile_starts[0] + size_t(batch_heads) * (BUCKETS + 1), capacity);
+        plan_query_tiles_kernel<<<batch_heads, 1024, 0, stream>>>(keys.starts, queries.starts, tile_starts[1], tiles[1],
+                                                                  tile_starts[1] + size_t(batch_heads) * (BUCKETS + 1), capacity);
+    }
+    BackwardBlockArgs args{};
     args.sq = sq; args.sk = sk; args.v = v; args.dout = dout;
     args.iq = iq; args.ik = ik; args.boundary = boundary; args.hard = hard;
     args.documents = documents; args.hard_rows = hard_rows;
     args.lut = lut; args.dlut = dlut; args.lse2 = lse2;
     args.dsq = dsq; args.dtau_rows = rows; args.dsk = dsk; args.dv = dv;
     args.batch = shape.batch; args.heads = shape.heads; args.n = shape.n; args.lut_stride = lut_stride;
-    args.tasks = batch_heads * (shape.n / TASK_ROWS);
-    RowsArgs by_query = args, by_key = args;
-    by_query.index = side_index(workspace, batch_heads, shape.n, 0, 2);  // queries look up keys
-    by_key.index = side_index(workspace, batch_heads, shape.n, 1, 2);    // keys look up queries
+    args.tile_capacity = capacity;
+    BackwardBlockArgs by_query = args, by_key = args;
+    by_query.owners = queries; by_query.partners = keys;
+    by_query.tiles = tiles[0]; by_query.tile_starts = tile_starts[0];
+    by_query.next_tile = tile_starts[0] + size_t(batch_heads) * (BUCKETS + 1);
+    by_key.owners = keys; by_key.partners = queries;
+    by_key.tiles = tiles[1]; by_key.tile_starts = tile_starts[1];
+    by_key.next_tile = tile_starts[1] + size_t(batch_heads) * (BUCKETS + 1);
     status = cudaErrorInvalidValue;
 #define DISM_CASE(RR, VV)                                                                         \
     if (shape.r == RR && shape.dv == VV) {                                                        \
-        status = launch_rows_kernel<QueryBackwardPolicy<RR, VV>>(by_query, ctas, stream);         \
-        if (status == cudaSuccess) status = launch_rows_kernel<KeyBackwardPolicy<RR, VV>>(by_key, ctas, stream); \
+        status = launch_backward_blocks<true, RR, VV>(by_query, ctas, stream);                    \
+        if (status == cudaSuccess) status = launch_backward_blocks<false, RR, VV>(by_key, ctas, stream); \
     }
     DISM_CASE(16, 32) DISM_CASE(16, 64) DISM_CASE(16, 128)
     DISM_CASE(32, 32) DISM_CASE(32, 64) DISM_CASE(32, 128)

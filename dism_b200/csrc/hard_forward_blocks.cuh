@@ -78,7 +78,7 @@ struct BlockArgs {
 __host__ __device__ inline int tile_capacity_for(int n) { return n / QT + BUCKETS; }
 
 // tile_starts[b] = number of 16-query tiles in the buckets before b, and one descriptor per tile.
-__global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int* __restrict__ query_starts,
+static __global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int* __restrict__ query_starts,
                                                                 const int* __restrict__ key_starts,
                                                                 int* __restrict__ tile_starts, int4* __restrict__ tiles,
                                                                 int* __restrict__ next_tile, int tile_capacity) {
