@@ -58,7 +58,7 @@ __device__ __forceinline__ void split_bf16(float x, float y, unsigned& high, uns
 }
 
 template <bool QUERY_MAJOR, int R, int DV>
-__global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_backward_blocks_kernel(const BackwardBlockArgs a) {
+__global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kernel(const BackwardBlockArgs a) {
     constexpr int KSTEPS = R / 16, VSTEPS = DV / 16, RTILES = R / 8, VTILES = DV / 8;
     extern __shared__ __align__(16) unsigned char storage[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
