@@ -7,7 +7,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 OUT = os.path.join(HERE, 'libdism_b200.so')
-SOURCES = ['abi.cu', 'labels.cu', 'hard_index.cu', 'hard_scan.cu', 'hard_forward.cu', 'hard_forward_static.cu',
+SOURCES = ['abi.cu', 'labels.cu', 'labels_tcgen05.cu', 'hard_index.cu', 'hard_scan.cu', 'hard_forward.cu', 'hard_forward_static.cu',
            'hard_backward.cu']
 FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
          '-Xcompiler', '-fPIC', '-Xptxas', '-v']

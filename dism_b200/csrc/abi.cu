@@ -85,7 +85,7 @@ int dism_profile_read(int index, char* name, int capacity, float* milliseconds) 
 }
 
 const char* dism_last_error(void) { return last_error; }
-int dism_abi_version(void) { return 3; }
+int dism_abi_version(void) { return 4; }
 
 int dism_labels(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t* labels, void* stream) {
@@ -97,6 +97,11 @@ int dism_labels(const void* x, const void* codebook, int batch, int n, int heads
     return cuda_status(dism::launch_labels(static_cast<const __nv_bfloat16*>(x),
                                            static_cast<const __nv_bfloat16*>(codebook), batch, n, heads, d, vocab,
                                            labels, static_cast<cudaStream_t>(stream)), "labels");
+}
+
+int dism_labels_fault(int* code) {
+    if (!code) return fail(DISM_EINVAL, "null pointer");
+    return cuda_status(dism::read_labels_fault(code), "labels fault code");
 }
 
 int dism_hard_summary(const int32_t* iq, const int32_t* ik, const uint8_t* hard, int batch, int heads, int n,

@@ -215,6 +215,8 @@ __global__ __launch_bounds__(LABEL_ROWS) void labels_kernel(const __nv_bfloat16*
 
 cudaError_t launch_labels(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int batch, int n, int heads,
                           int d, int vocab, int* labels, cudaStream_t stream) {
+    if (labels_tcgen05_covers(x, codebook, batch, n, heads, d, vocab))
+        return launch_labels_tcgen05(x, codebook, batch, n, heads, d, vocab, labels, stream);
     dim3 grid((n + LABEL_ROWS - 1) / LABEL_ROWS, batch * heads);
     KernelTimer timer("labels", stream);
     if (d == 32) labels_kernel<32><<<grid, LABEL_ROWS, 0, stream>>>(x, codebook, n, heads, vocab, labels);

@@ -1,0 +1,506 @@
+// Discretiser on the fifth-generation tensor cores: arg-max symbol of x . E^T per head.
+//
+// Same contract as the general kernel in labels.cu (reference: dism_v3/python/flash_dism/emb_kernel.py:88-108,
+// kernels/interp_true.py:25-33) for the shapes the tensor-memory pipeline covers: D of 64 or 128,
+// a codebook of a multiple of 128 codes that fits in 128 KiB, N a multiple of 128.
+//
+// One persistent CTA per SM walks a contiguous range of (head, 128-row tile) pairs:
+//   producer warp   TMA: the head's whole codebook once (128-byte swizzled, K-major), then one
+//                   128 x D tile of x per step into a two-stage ring;
+//   MMA warp        one thread issues tcgen05.mma (M=128, N=128, K=16) for each 128-code slice of the
+//                   codebook into a ring of FP32 accumulators in tensor memory;
+//   eight epilogue  read the accumulators with tcgen05.ld (row = tensor-memory lane = thread), keep the
+//   warps           best and second-best logit per row, and write the label.
+// The epilogue is the ALU bound of the kernel, so a logit costs 3.5 instructions: the column index
+// inside a 32-column chunk replaces the five low mantissa bits (one LOP3), pairs of logits are
+// folded into the running top two with two- and three-input min/max, and the chunk that last
+// raised the maximum is noted once per chunk.
+//
+// Labels are defined by the pinned FP32 order (d ascending, one rounding per add).  A row whose
+// top-two margin is inside a rigorous bound on |tensor-core logit - pinned logit| (plus the
+// mantissa bits given to the index) is recomputed in the pinned order by a whole warp after the
+// CTA's last tile; all other rows provably have the same arg-max in both orders.
+//
+// Every wait on an mbarrier is bounded: when one runs out the CTA records a fault code, all roles
+// leave their loops, tensor memory is freed and the kernel returns.
+#include <cuda.h>
+
+#include "dism_common.cuh"
+
+namespace dism {
+namespace {
+
+constexpr int TILE_ROWS = 128;   // rows of x per tile: the 128 lanes of tensor memory
+constexpr int TILE_CODES = 128;  // codes per accumulator: 128 FP32 columns
+constexpr int KBLOCK = 64;       // elements in one 128-byte swizzled row
+constexpr int BLOCK_BYTES = TILE_ROWS * 128;
+constexpr int A_STAGES = 2, ACC_STAGES = 2;
+constexpr int EPILOGUE_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, THREADS = 320;
+constexpr int FLAG_CAPACITY = 256;  // per finishing warp
+constexpr unsigned WAIT_LIMIT = 1u << 20, SETTLE_LIMIT = 1u << 14;
+constexpr int MAX_CODE_BYTES = 128 * 1024;
+
+struct Exchange {
+    float first, second;
+    int arg;
+    float norm2;
+};
+
+struct Control {
+    uint64_t code_full, code_empty, drain, list_ready;
+    uint64_t a_full[A_STAGES], a_empty[A_STAGES];
+    uint64_t acc_full[ACC_STAGES], acc_empty[ACC_STAGES];
+    uint64_t exchange_full[2], exchange_empty[2];
+    Exchange exchange[2][TILE_ROWS];
+    int flagged[4][FLAG_CAPACITY];
+    int flagged_count[4];
+    uint32_t tensor_memory;
+    int abort;
+};
+
+__device__ int labels_fault_code;  // first bounded wait that ran out (0: none)
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void barrier_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(shared_address(bar)), "r"(count));
+}
+__device__ __forceinline__ void barrier_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(shared_address(bar)) : "memory");
+}
+__device__ __forceinline__ void barrier_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool barrier_test(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{.reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p;}"
+                 : "=r"(done) : "r"(shared_address(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait.  False: this wait ran out (fault `code` recorded) or another role already gave up.
+__device__ __noinline__ bool barrier_wait_slow(uint64_t* bar, uint32_t parity, Control& control, int code) {
+    for (unsigned tries = 0; tries < WAIT_LIMIT; ++tries) {
+        if (barrier_test(bar, parity)) return true;
+        if (*reinterpret_cast<volatile int*>(&control.abort)) return false;
+    }
+    *reinterpret_cast<volatile int*>(&control.abort) = 1;
+    atomicCAS(&labels_fault_code, 0, code);
+    return false;
+}
+__device__ __forceinline__ bool barrier_wait(uint64_t* bar, uint32_t parity, Control& control, int code) {
+    return barrier_test(bar, parity) || barrier_wait_slow(bar, parity, control, code);
+}
+// After a fault: give copies or products in flight a bounded time to land before the CTA leaves.
+__device__ __noinline__ void barrier_settle(uint64_t* bar, uint32_t parity) {
+    for (unsigned tries = 0; tries < SETTLE_LIMIT; ++tries)
+        if (barrier_test(bar, parity)) return;
+}
+
+__device__ __forceinline__ void tma_load(void* destination, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(shared_address(destination)), "l"(map), "r"(x), "r"(y), "r"(shared_address(bar)) : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, eight-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t operand_descriptor(uint32_t address) {
+    return uint64_t((address & 0x3ffff) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+           (uint64_t(2) << 61);
+}
+// bf16 x bf16 -> f32, both operands K-major, M = 128, N = 128
+constexpr uint32_t INSTRUCTION = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(TILE_CODES >> 3) << 17) | (uint32_t(TILE_ROWS >> 4) << 24);
+
+__device__ __forceinline__ void mma(uint32_t accumulator, uint64_t a, uint64_t b, uint32_t accumulate) {
+    asm volatile("{.reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;}"
+                 ::"r"(accumulator), "l"(a), "l"(b), "r"(INSTRUCTION), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(shared_address(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void load_columns(uint32_t (&r)[32], uint32_t address) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(address));
+}
+__device__ __forceinline__ void wait_columns() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// Running best and second-best key of a row.  A key is a logit whose five low mantissa bits hold
+// the column inside the current 32-column chunk.
+struct TopTwo {
+    float first, second, seen;  // seen: first at the end of the previous chunk
+    int chunk;                  // chunk that last raised first
+    __device__ __forceinline__ void offer(uint32_t r0, uint32_t r1, int column) {
+        const float k0 = __uint_as_float((r0 & ~31u) | unsigned(column)), k1 = __uint_as_float((r1 & ~31u) | unsigned(column + 1));
+        const float high = fmaxf(k0, k1), low = fminf(k0, k1);
+        second = max3(second, low, fminf(first, high));
+        first = fmaxf(first, high);
+    }
+    __device__ __forceinline__ void close_chunk(int index) {
+        chunk = first != seen ? index : chunk;
+        seen = first;
+    }
+    __device__ __forceinline__ int arg() const { return chunk * 32 + int(__float_as_uint(first) & 31u); }
+};
+
+__device__ __forceinline__ float squares(uint4 raw, float sum) {
+    const unsigned word[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const float low = __uint_as_float(word[w] << 16), high = __uint_as_float(word[w] & 0xffff0000u);
+        sum = fmaf(low, low, fmaf(high, high, sum));
+    }
+    return sum;
+}
+
+// Pinned-order arg-max of one row by a whole warp; every lane returns the label.  A lane works on
+// four codes at a time, because the additions of one code form a serial chain.
+template <int D>
+__device__ int pinned_label(const __nv_bfloat16* __restrict__ row, const __nv_bfloat16* __restrict__ codes, int vocab, int lane) {
+    float top = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int v0 = lane; v0 < vocab; v0 += 128) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+            const uint4 packed = __ldg(reinterpret_cast<const uint4*>(row) + c);
+            const unsigned xs[4] = {packed.x, packed.y, packed.z, packed.w};
+            unsigned es[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint4 e = __ldg(reinterpret_cast<const uint4*>(codes + int64_t(min(v0 + 32 * u, vocab - 1)) * D) + c);
+                es[u][0] = e.x, es[u][1] = e.y, es[u][2] = e.z, es[u][3] = e.w;
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    acc[u] = __fadd_rn(acc[u], __fmul_rn(__uint_as_float(xs[w] << 16), __uint_as_float(es[u][w] << 16)));
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    acc[u] = __fadd_rn(acc[u], __fmul_rn(__uint_as_float(xs[w] & 0xffff0000u), __uint_as_float(es[u][w] & 0xffff0000u)));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)  // ascending v per lane: the first maximum is kept
+            if (v0 + 32 * u < vocab && acc[u] > top) { top = acc[u]; arg = v0 + 32 * u; }
+    }
+#pragma unroll
+    for (int s = 16; s; s >>= 1) {
+        const float other = __shfl_xor_sync(FULL, top, s);
+        const int other_arg = __shfl_xor_sync(FULL, arg, s);
+        if (other > top || (other == top && other_arg < arg)) { top = other; arg = other_arg; }
+    }
+    return arg;
+}
+
+template <int D>
+__global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map,
+                                                                    const __grid_constant__ CUtensorMap code_map,
+                                                                    const __nv_bfloat16* __restrict__ x,
+                                                                    const __nv_bfloat16* __restrict__ codebook, int n, int heads,
+                                                                    int vocab, int tiles_per_head, int total_tiles,
+                                                                    int* __restrict__ labels) {
+    constexpr int KBLOCKS = D / KBLOCK, A_BYTES = KBLOCKS * BLOCK_BYTES;
+    extern __shared__ unsigned char raw[];
+    unsigned char* base = raw + ((1024u - (shared_address(raw) & 1023u)) & 1023u);  // swizzled tiles: 1024-byte aligned
+    const int code_tiles = vocab / TILE_CODES;
+    unsigned char* codes = base;
+    unsigned char* a_ring = codes + code_tiles * KBLOCKS * BLOCK_BYTES;
+    Control& control = *reinterpret_cast<Control*>(a_ring + A_STAGES * A_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int first_tile = int(int64_t(blockIdx.x) * total_tiles / gridDim.x);
+    const int last_tile = int(int64_t(blockIdx.x + 1) * total_tiles / gridDim.x);
+
+    if (threadIdx.x == 0) {
+        barrier_init(&control.code_full, 1);
+        barrier_init(&control.code_empty, 1);
+        barrier_init(&control.drain, 1);
+        barrier_init(&control.list_ready, 4);
+        for (int s = 0; s < A_STAGES; ++s) { barrier_init(&control.a_full[s], 1); barrier_init(&control.a_empty[s], 1); }
+        for (int s = 0; s < ACC_STAGES; ++s) { barrier_init(&control.acc_full[s], 1); barrier_init(&control.acc_empty[s], EPILOGUE_WARPS); }
+        for (int s = 0; s < 2; ++s) { barrier_init(&control.exchange_full[s], 4); barrier_init(&control.exchange_empty[s], 4); }
+        for (int s = 0; s < 4; ++s) control.flagged_count[s] = 0;
+        control.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(shared_address(&control.tensor_memory)),
+                     "r"(ACC_STAGES * TILE_CODES) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tensor_memory = *reinterpret_cast<volatile uint32_t*>(&control.tensor_memory);
+
+    if (warp == PRODUCER_WARP) {
+        if (lane == 0) {
+            int loaded_head = -1, code_loads = 0, step = 0;
+            bool ok = true;
+            for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
+                const int head = tile / tiles_per_head, row = (tile % tiles_per_head) * TILE_ROWS;
+                if (head != loaded_head) {
+                    // the tensor core must have finished with the previous head's codes
+                    if (code_loads > 0 && !barrier_wait(&control.code_empty, (code_loads - 1) & 1, control, 1)) break;
+                    barrier_expect(&control.code_full, uint32_t(code_tiles * KBLOCKS * BLOCK_BYTES));
+                    for (int j = 0; j < code_tiles; ++j)
+                        for (int kb = 0; kb < KBLOCKS; ++kb)
+                            tma_load(codes + (j * KBLOCKS + kb) * BLOCK_BYTES, &code_map, kb * KBLOCK, head * vocab + j * TILE_CODES,
+                                     &control.code_full);
+                    loaded_head = head;
+                    ++code_loads;
+                }
+                const int stage = step % A_STAGES;
+                ok = barrier_wait(&control.a_empty[stage], ((step / A_STAGES) & 1) ^ 1, control, 2);
+                if (!ok) break;
+                barrier_expect(&control.a_full[stage], uint32_t(A_BYTES));
+                for (int kb = 0; kb < KBLOCKS; ++kb)
+                    tma_load(a_ring + stage * A_BYTES + kb * BLOCK_BYTES, &x_map, head * D + kb * KBLOCK, row, &control.a_full[stage]);
+            }
+            if (*reinterpret_cast<volatile int*>(&control.abort)) {  // let the copies in flight land
+                if (code_loads > 0) barrier_settle(&control.code_full, (code_loads - 1) & 1);
+                for (int back = 1; back <= A_STAGES && back <= step; ++back)
+                    barrier_settle(&control.a_full[(step - back) % A_STAGES], ((step - back) / A_STAGES) & 1);
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            int loaded_head = -1, code_uses = 0, step = 0, product = 0;
+            bool ok = true;
+            for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
+                const int head = tile / tiles_per_head;
+                if (head != loaded_head) {
+                    if (!barrier_wait(&control.code_full, code_uses & 1, control, 3)) break;
+                    ++code_uses;
+                    loaded_head = head;
+                }
+                const int stage = step % A_STAGES;
+                if (!barrier_wait(&control.a_full[stage], (step / A_STAGES) & 1, control, 4)) break;
+                fence_after_sync();
+                const uint32_t a_address = shared_address(a_ring + stage * A_BYTES);
+                for (int j = 0; j < code_tiles; ++j, ++product) {
+                    const int slot = product % ACC_STAGES;
+                    ok = barrier_wait(&control.acc_empty[slot], ((product / ACC_STAGES) & 1) ^ 1, control, 5);
+                    if (!ok) break;
+                    fence_after_sync();
+                    const uint32_t b_address = shared_address(codes + j * KBLOCKS * BLOCK_BYTES);
+#pragma unroll
+                    for (int kb = 0; kb < KBLOCKS; ++kb)
+#pragma unroll
+                        for (int ks = 0; ks < KBLOCK / 16; ++ks)
+                            mma(tensor_memory + slot * TILE_CODES, operand_descriptor(a_address + kb * BLOCK_BYTES + ks * 32),
+                                operand_descriptor(b_address + kb * BLOCK_BYTES + ks * 32), (kb | ks) != 0);
+                    mma_commit(&control.acc_full[slot]);
+                }
+                if (!ok) break;
+                mma_commit(&control.a_empty[stage]);
+                if (tile + 1 < last_tile && (tile + 1) / tiles_per_head != head) mma_commit(&control.code_empty);
+            }
+            // every product issued above has completed once this commit arrives
+            mma_commit(&control.drain);
+            barrier_settle(&control.drain, 0);
+        }
+    } else {
+        const int quarter = warp & 3, group = warp >> 2, row_in_tile = quarter * 32 + lane;
+        const uint32_t lanes = tensor_memory + (uint32_t(quarter * 32) << 16) + group * (TILE_CODES / 2);
+        int loaded_head = -1, step = 0, product = 0;
+        float code_max = 0.f;
+        bool ok = true;
+        for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
+            const int head = tile / tiles_per_head, row = (tile % tiles_per_head) * TILE_ROWS + row_in_tile;  // row in [B*N]
+            float norm2 = 0.f;
+            if (group == 1) {  // this half also measures the row
+                const uint4* source = reinterpret_cast<const uint4*>(x + (int64_t(row) * heads + head) * D);
+#pragma unroll
+                for (int c = 0; c < D / 8; ++c) norm2 = squares(__ldg(source + c), norm2);
+            } else if (head != loaded_head) {  // largest squared code norm of the head, per warp
+                const __nv_bfloat16* head_codes = codebook + int64_t(head) * vocab * D;
+                code_max = 0.f;
+                for (int v = lane; v < vocab; v += 32) {
+                    const uint4* code = reinterpret_cast<const uint4*>(head_codes + int64_t(v) * D);
+                    float sum = 0.f;
+#pragma unroll
+                    for (int c = 0; c < D / 8; ++c) sum = squares(__ldg(code + c), sum);
+                    code_max = fmaxf(code_max, sum);
+                }
+#pragma unroll
+                for (int s = 16; s; s >>= 1) code_max = fmaxf(code_max, __shfl_xor_sync(FULL, code_max, s));
+                loaded_head = head;
+            }
+            TopTwo even{-INFINITY, -INFINITY, -INFINITY, 0}, odd{-INFINITY, -INFINITY, -INFINITY, 0};
+            for (int j = 0; j < code_tiles; ++j, ++product) {
+                const int slot = product % ACC_STAGES;
+                ok = barrier_wait(&control.acc_full[slot], (product / ACC_STAGES) & 1, control, 6);
+                if (!ok) break;
+                fence_after_sync();
+                uint32_t r0[32], r1[32];
+                load_columns(r0, lanes + slot * TILE_CODES);
+                load_columns(r1, lanes + slot * TILE_CODES + 32);
+                wait_columns();
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) barrier_arrive(&control.acc_empty[slot]);  // the logits are in registers
+                const int chunk = j * (TILE_CODES / 32) + group * 2;
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    even.offer(r0[i], r0[i + 1], i);
+                    odd.offer(r0[i + 2], r0[i + 3], i + 2);
+                }
+                even.close_chunk(chunk);
+                odd.close_chunk(chunk);
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    even.offer(r1[i], r1[i + 1], i);
+                    odd.offer(r1[i + 2], r1[i + 3], i + 2);
+                }
+                even.close_chunk(chunk + 1);
+                odd.close_chunk(chunk + 1);
+            }
+            if (!ok) break;
+            float first = fmaxf(even.first, odd.first);
+            float second = max3(even.second, odd.second, fminf(even.first, odd.first));
+            int arg = even.first >= odd.first ? even.arg() : odd.arg();
+            const int side = step & 1;
+            if (group == 1) {
+                ok = barrier_wait(&control.exchange_empty[side], ((step >> 1) & 1) ^ 1, control, 7);
+                if (!ok) break;
+                control.exchange[side][row_in_tile] = Exchange{first, second, arg, norm2};
+                __syncwarp();
+                if (lane == 0) barrier_arrive(&control.exchange_full[side]);
+            } else {
+                ok = barrier_wait(&control.exchange_full[side], (step >> 1) & 1, control, 8);
+                if (!ok) break;
+                const Exchange other = control.exchange[side][row_in_tile];
+                __syncwarp();
+                if (lane == 0) barrier_arrive(&control.exchange_empty[side]);
+                second = max3(second, other.second, fminf(first, other.first));
+                arg = first >= other.first ? arg : other.arg;
+                first = fmaxf(first, other.first);
+                // |tensor-core logit - exact| <= 4 D u sum|x e| (sixteen-term blocks whose addends may be truncated),
+                // |pinned logit - exact| <= D u sum|x e|, u = 2^-24, sum|x e| <= |x|_2 |e|_2; the index bits move a
+                // key by less than 2^-18 of its size, or by less than 2^-144 near zero.
+                const float tolerance = (float(5 * D) * 5.9604645e-8f + 3.8146973e-6f) * sqrtf(other.norm2 * code_max) * 1.01f + 1e-37f;
+                const bool flagged = !(first - second > 2.f * tolerance);
+                const int batch = row / n, position = row % n;
+                if (!flagged) labels[(int64_t(batch) * heads + head) * n + position] = arg;
+                const unsigned mask = __ballot_sync(FULL, flagged);
+                if (mask) {
+                    const int count = control.flagged_count[quarter], more = __popc(mask);
+                    if (count + more <= FLAG_CAPACITY) {
+                        if (flagged) control.flagged[quarter][count + __popc(mask & ((1u << lane) - 1))] = tile * TILE_ROWS + row_in_tile;
+                        __syncwarp();
+                        if (lane == 0) control.flagged_count[quarter] = count + more;
+                        __syncwarp();
+                    } else {  // list full: recompute here
+                        for (unsigned rest = mask; rest; rest &= rest - 1) {
+                            const int r = (tile % tiles_per_head) * TILE_ROWS + quarter * 32 + __ffs(rest) - 1;
+                            const int label = pinned_label<D>(x + (int64_t(r) * heads + head) * D, codebook + int64_t(head) * vocab * D, vocab, lane);
+                            if (lane == 0) labels[(int64_t(r / n) * heads + head) * n + r % n] = label;
+                        }
+                    }
+                }
+            }
+        }
+        // Rows on the lists: pinned order, one warp per row, all eight warps.
+        if (ok && group == 0) {
+            __syncwarp();
+            if (lane == 0) barrier_arrive(&control.list_ready);
+        }
+        if (ok && barrier_wait(&control.list_ready, 0, control, 9)) {
+            int turn = 0;
+            for (int list = 0; list < 4; ++list) {
+                const int count = *reinterpret_cast<volatile int*>(&control.flagged_count[list]);
+                for (int entry = 0; entry < count; ++entry, ++turn) {
+                    if (turn % EPILOGUE_WARPS != warp) continue;
+                    const int id = control.flagged[list][entry], tile = id / TILE_ROWS;
+                    const int head = tile / tiles_per_head, r = (tile % tiles_per_head) * TILE_ROWS + id % TILE_ROWS;
+                    const int label = pinned_label<D>(x + (int64_t(r) * heads + head) * D, codebook + int64_t(head) * vocab * D, vocab, lane);
+                    if (lane == 0) labels[(int64_t(r / n) * heads + head) * n + r % n] = label;
+                }
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tensor_memory), "r"(ACC_STAGES * TILE_CODES) : "memory");
+    }
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled entry = [] {
+        void* address = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &address, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            address = nullptr;
+        return reinterpret_cast<EncodeTiled>(address);
+    }();
+    return entry;
+}
+
+// bf16 matrix [rows, columns] (row stride in elements) read in boxes of 64 columns by 128 rows, 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* data, uint64_t rows, uint64_t columns, uint64_t row_stride) {
+    const EncodeTiled encode = encode_tiled();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {columns, rows}, strides[1] = {row_stride * 2};
+    const cuuint32_t box[2] = {KBLOCK, TILE_ROWS}, element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(data), dims, strides, box, element_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D>
+cudaError_t launch(const CUtensorMap& x_map, const CUtensorMap& code_map, const __nv_bfloat16* x, const __nv_bfloat16* codebook,
+                   int n, int heads, int vocab, int tiles_per_head, int total_tiles, int* labels, cudaStream_t stream) {
+    const int bytes = vocab * D * 2 + A_STAGES * (D / KBLOCK) * BLOCK_BYTES + int(sizeof(Control)) + 1024;
+    const cudaError_t status = cudaFuncSetAttribute(labels_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (status != cudaSuccess) return status;
+    const int grid = total_tiles < device_sm_count() ? total_tiles : device_sm_count();
+    labels_tcgen05_kernel<D><<<grid, THREADS, bytes, stream>>>(x_map, code_map, x, codebook, n, heads, vocab, tiles_per_head, total_tiles, labels);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool labels_tcgen05_covers(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab) {
+    return (d == 64 || d == 128) && vocab % TILE_CODES == 0 && int64_t(vocab) * d * 2 <= MAX_CODE_BYTES && n % TILE_ROWS == 0 &&
+           int64_t(batch) * n * heads < (int64_t(1) << 31) && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+           reinterpret_cast<uintptr_t>(codebook) % 16 == 0 && encode_tiled() != nullptr;
+}
+
+cudaError_t launch_labels_tcgen05(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int batch, int n, int heads, int d,
+                                  int vocab, int* labels, cudaStream_t stream) {
+    CUtensorMap x_map, code_map;
+    if (!make_map(&x_map, x, uint64_t(batch) * n, uint64_t(heads) * d, uint64_t(heads) * d) ||
+        !make_map(&code_map, codebook, uint64_t(heads) * vocab, uint64_t(d), uint64_t(d)))
+        return cudaErrorInvalidValue;
+    const int tiles_per_head = int(int64_t(batch) * n / TILE_ROWS), total_tiles = tiles_per_head * heads;
+    KernelTimer timer("labels", stream);
+    if (d == 64) return launch<64>(x_map, code_map, x, codebook, n, heads, vocab, tiles_per_head, total_tiles, labels, stream);
+    return launch<128>(x_map, code_map, x, codebook, n, heads, vocab, tiles_per_head, total_tiles, labels, stream);
+}
+
+// First bounded wait that ran out in any earlier launch on this device (0: none).  Synchronises the device.
+cudaError_t read_labels_fault(int* code) { return cudaMemcpyFromSymbol(code, labels_fault_code, sizeof(int)); }
+
+}  // namespace dism

@@ -32,6 +32,10 @@ int dism_abi_version(void);
  * 155-189) and of kernels/interp_true.py:8-65. */
 int dism_labels(const void *x, const void *codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t *labels, void *stream);
+/* The discretiser's tensor-memory pipeline bounds every wait of its roles on one another; *code is
+ * the first wait that ran out in any earlier dism_labels launch on the current device (0: none, the
+ * only value a correct run produces).  Synchronises the device.  No counterpart in the reference. */
+int dism_labels_fault(int *code);
 
 /* Strip summaries: summary int32 [B,H,(N-1)/32,N]; non-causal and soft entries are -1.
  * Stands in for cu_flash_dism.hard_summary (dism_v3/src/frontend.cpp:309-312,

@@ -262,6 +262,48 @@ def test_labels_bit_exact_and_ties(api, oracle):
     assert not zero.count_nonzero()
 
 
+def labels_fault():
+    import ctypes
+    from dism_b200 import _lib
+    code = ctypes.c_int(-1)
+    _lib.check(_lib.load().dism_labels_fault(ctypes.byref(code)))
+    return code.value
+
+
+@pytest.mark.parametrize('shape', [(2, 1024, 4, 64, 512), (1, 256, 2, 128, 256), (3, 128, 5, 64, 128),
+                                   (1, 2048, 3, 64, 1024), (2, 640, 16, 128, 512), (1, 27 * 128, 7, 64, 384)])
+def test_labels_tensor_memory_pipeline(api, oracle, shape):
+    """Shapes the tcgen05 pipeline covers (D 64/128, V a multiple of 128, N a multiple of 128): bit-exact
+    labels, including duplicated codes (exact ties: the lowest index), near ties and zero rows."""
+    b, n, h, d, v = shape
+    g = torch.Generator().manual_seed(b * 1000 + n + v)
+    x = torch.randn(b, n, h, d, generator=g).bfloat16()
+    e = torch.nn.functional.silu(torch.randn(h, v, d, generator=g)).bfloat16()
+    e[:, v // 2] = e[:, 3]          # exact duplicates
+    e[:, v - 1] = e[:, 0]
+    x[0, 5] = 0                     # all logits equal
+    x[-1, n - 1, h - 1] = 0
+    x[0, 7] = e[:, 3] * 4           # rows aligned with a duplicated code
+    got = api['cu'].labels(x.cuda(), e.cuda())
+    assert labels_fault() == 0
+    assert np.array_equal(got.cpu().numpy(), oracle.labels(x.float().numpy(), e.float().numpy()))
+    again = api['cu'].labels(x.cuda(), e.cuda())
+    assert torch.equal(got, again)
+
+
+def test_labels_tensor_memory_pipeline_all_ties(api):
+    """Every row inside the margin bound: the per-warp lists overflow and rows are recomputed in place."""
+    x = torch.zeros(1, 4096, 2, 64).bfloat16()
+    e = torch.randn(2, 128, 64, generator=torch.Generator().manual_seed(5)).bfloat16()
+    got = api['cu'].labels(x.cuda(), e.cuda())
+    assert labels_fault() == 0 and not got.count_nonzero()
+    # a scaled code as the row: the arg-max is that code or an earlier duplicate
+    x = (e[:, :64].transpose(0, 1).reshape(1, 64, 2, 64) * 2).repeat(1, 2, 1, 1).contiguous()
+    got = api['cu'].labels(x.cuda(), e.cuda()).cpu()
+    reference = torch.argmax(torch.einsum('bnhd,hvd->bnhv', x.float(), e.float()), -1).transpose(1, 2)
+    assert (got != reference).float().mean() < .02
+
+
 # ---- symbol streams: single longest earlier match -----------------------------------------------------
 def symbol_streams(batch, n, vocab, seed):
     rng = np.random.default_rng(seed)
