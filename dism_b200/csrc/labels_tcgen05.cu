@@ -11,15 +11,15 @@
 //                   codebook into a ring of FP32 accumulators in tensor memory;
 //   eight epilogue  read the accumulators with tcgen05.ld (row = tensor-memory lane = thread), keep the
 //   warps           best and second-best logit per row, and write the label.
-// The epilogue is the ALU bound of the kernel, so a logit costs 3.5 instructions: the column index
-// inside a 32-column chunk replaces the five low mantissa bits (one LOP3), pairs of logits are
-// folded into the running top two with two- and three-input min/max, and the chunk that last
-// raised the maximum is noted once per chunk.
+// The epilogue is the instruction bound of the kernel, and min/max/logic instructions issue at half
+// the FMA rate.  So the half-rate pipe only finds the maximum of each 32-column chunk (three-input
+// max: half an instruction per logit), and the full-rate pipe does the rest with saturating FMAs:
+// it counts the logits within the safety margin of the leader and sums their column numbers.
 //
 // Labels are defined by the pinned FP32 order (d ascending, one rounding per add).  A row whose
-// top-two margin is inside a rigorous bound on |tensor-core logit - pinned logit| (plus the
-// mantissa bits given to the index) is recomputed in the pinned order by a whole warp after the
-// CTA's last tile; all other rows provably have the same arg-max in both orders.
+// best logit has another one within a rigorous bound on |tensor-core logit - pinned logit| is
+// recomputed in the pinned order by a whole warp after the CTA's last tile; all other rows
+// provably have the same arg-max in both orders.
 //
 // Every wait on an mbarrier is bounded: when one runs out the CTA records a fault code, all roles
 // leave their loops, tensor memory is freed and the kernel returns.
@@ -34,21 +34,21 @@ constexpr int TILE_ROWS = 128;   // rows of x per tile: the 128 lanes of tensor 
 constexpr int TILE_CODES = 128;  // codes per accumulator: 128 FP32 columns
 constexpr int KBLOCK = 64;       // elements in one 128-byte swizzled row
 constexpr int BLOCK_BYTES = TILE_ROWS * 128;
-constexpr int A_STAGES = 2, ACC_STAGES = 2;
+constexpr int ACC_STAGES = 4;  // all 512 columns of tensor memory
+constexpr int MAX_A_STAGES = 4;
 constexpr int EPILOGUE_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, THREADS = 320;
 constexpr int FLAG_CAPACITY = 256;  // per finishing warp
 constexpr unsigned WAIT_LIMIT = 1u << 20, SETTLE_LIMIT = 1u << 14;
 constexpr int MAX_CODE_BYTES = 128 * 1024;
 
 struct Exchange {
-    float first, second;
-    int arg;
-    float norm2;
+    float first;
+    int arg, clean, pad;
 };
 
 struct Control {
     uint64_t code_full, code_empty, drain, list_ready;
-    uint64_t a_full[A_STAGES], a_empty[A_STAGES];
+    uint64_t a_full[MAX_A_STAGES], a_empty[MAX_A_STAGES];
     uint64_t acc_full[ACC_STAGES], acc_empty[ACC_STAGES];
     uint64_t exchange_full[2], exchange_empty[2];
     Exchange exchange[2][TILE_ROWS];
@@ -81,7 +81,7 @@ __device__ __forceinline__ bool barrier_test(uint64_t* bar, uint32_t parity) {
 __device__ __noinline__ bool barrier_wait_slow(uint64_t* bar, uint32_t parity, Control& control, int code) {
     for (unsigned tries = 0; tries < WAIT_LIMIT; ++tries) {
         if (barrier_test(bar, parity)) return true;
-        if (*reinterpret_cast<volatile int*>(&control.abort)) return false;
+        if ((tries & 63) == 63 && *reinterpret_cast<volatile int*>(&control.abort)) return false;
     }
     *reinterpret_cast<volatile int*>(&control.abort) = 1;
     atomicCAS(&labels_fault_code, 0, code);
@@ -137,23 +137,56 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-// Running best and second-best key of a row.  A key is a logit whose five low mantissa bits hold
-// the column inside the current 32-column chunk.
-struct TopTwo {
-    float first, second, seen;  // seen: first at the end of the previous chunk
-    int chunk;                  // chunk that last raised first
-    __device__ __forceinline__ void offer(uint32_t r0, uint32_t r1, int column) {
-        const float k0 = __uint_as_float((r0 & ~31u) | unsigned(column)), k1 = __uint_as_float((r1 & ~31u) | unsigned(column + 1));
-        const float high = fmaxf(k0, k1), low = fminf(k0, k1);
-        second = max3(second, low, fminf(first, high));
-        first = fmaxf(first, high);
-    }
-    __device__ __forceinline__ void close_chunk(int index) {
-        chunk = first != seen ? index : chunk;
-        seen = first;
-    }
-    __device__ __forceinline__ int arg() const { return chunk * 32 + int(__float_as_uint(first) & 31u); }
+__device__ __forceinline__ float fma_saturate(float a, float b, float c) {
+    float d;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// What a row knows after some of its logits: the largest one, its column, and whether every other
+// logit seen so far is more than `delta` below it (clean).
+struct Leader {
+    float first;
+    int arg;
+    bool clean;
 };
+
+// Per-row constants of the margin test.
+struct Margin {
+    float delta;  // a logit this far below the leader cannot overtake it in the pinned order
+    float gain;   // power of two that turns "above the threshold" into a saturated 1
+    bool sharp;   // delta * gain >= 1: the chunk maximum itself saturates
+};
+
+// Folds 32 logits (one chunk of columns) into the leader.  The min/max pipe runs at half rate, so
+// it only finds the chunk maximum (three-input max, half an instruction per logit); counting the
+// logits within delta of the leader, and summing their columns, is done with saturating FMAs on
+// the full-rate pipe: g = sat((s - t) * gain) is 1 above the threshold t, 0 at or below it.  A
+// fractional g (a logit within 1/gain of t) makes the count differ from 1 and the row not clean.
+__device__ __forceinline__ void fold_chunk(Leader& leader, const uint32_t (&r)[32], int chunk, const Margin margin) {
+    float m0 = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+    float m1 = max3(__uint_as_float(r[3]), __uint_as_float(r[4]), __uint_as_float(r[5]));
+#pragma unroll
+    for (int i = 6; i < 30; i += 4) {
+        m0 = max3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+        m1 = max3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+    }
+    const float top = fmaxf(max3(m0, __uint_as_float(r[30]), __uint_as_float(r[31])), m1);
+    const float best = fmaxf(leader.first, top);
+    const float offset = -(best - margin.delta) * margin.gain;
+    float count[2] = {0.f, 0.f}, columns[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const float g = fma_saturate(__uint_as_float(r[i]), margin.gain, offset);
+        count[i & 1] += g;
+        columns[i & 1] = fmaf(g, float(i), columns[i & 1]);
+    }
+    const bool clear = top > leader.first + margin.delta;                 // a new leader, the old one out of reach
+    const bool close = !clear && top >= leader.first - margin.delta;      // within reach of the old leader
+    leader.clean = clear ? (margin.sharp && count[0] + count[1] == 1.f) : (leader.clean && !close);
+    leader.arg = clear ? chunk * 32 + int(columns[0] + columns[1]) : leader.arg;
+    leader.first = best;
+}
 
 __device__ __forceinline__ float squares(uint4 raw, float sum) {
     const unsigned word[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -162,6 +195,20 @@ __device__ __forceinline__ float squares(uint4 raw, float sum) {
         const float low = __uint_as_float(word[w] << 16), high = __uint_as_float(word[w] & 0xffff0000u);
         sum = fmaf(low, low, fmaf(high, high, sum));
     }
+    return sum;
+}
+
+// Squared norm of one 128-byte-swizzled operand row in shared memory (the swizzle permutes the
+// 16-byte pieces inside the row, which a sum of squares does not see).  Lanes start at different
+// pieces so that a warp reading 32 consecutive rows meets no bank conflict.
+template <int D>
+__device__ __forceinline__ float shared_row_squares(const unsigned char* tile, int row, int lane) {
+    float sum = 0.f;
+#pragma unroll
+    for (int kb = 0; kb < D / KBLOCK; ++kb)
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            sum = squares(*reinterpret_cast<const uint4*>(tile + kb * BLOCK_BYTES + row * 128 + ((c + lane) & 7) * 16), sum);
     return sum;
 }
 
@@ -213,7 +260,7 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                                                                     const __nv_bfloat16* __restrict__ codebook, int n, int heads,
                                                                     int vocab, int tiles_per_head, int total_tiles,
                                                                     int* __restrict__ labels) {
-    constexpr int KBLOCKS = D / KBLOCK, A_BYTES = KBLOCKS * BLOCK_BYTES;
+    constexpr int KBLOCKS = D / KBLOCK, A_BYTES = KBLOCKS * BLOCK_BYTES, A_STAGES = D == 64 ? 4 : 2;
     extern __shared__ unsigned char raw[];
     unsigned char* base = raw + ((1024u - (shared_address(raw) & 1023u)) & 1023u);  // swizzled tiles: 1024-byte aligned
     const int code_tiles = vocab / TILE_CODES;
@@ -226,10 +273,10 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
 
     if (threadIdx.x == 0) {
         barrier_init(&control.code_full, 1);
-        barrier_init(&control.code_empty, 1);
+        barrier_init(&control.code_empty, 1 + EPILOGUE_WARPS);  // the tensor core and the warps that measure the codes
         barrier_init(&control.drain, 1);
         barrier_init(&control.list_ready, 4);
-        for (int s = 0; s < A_STAGES; ++s) { barrier_init(&control.a_full[s], 1); barrier_init(&control.a_empty[s], 1); }
+        for (int s = 0; s < A_STAGES; ++s) { barrier_init(&control.a_full[s], 1); barrier_init(&control.a_empty[s], 1 + EPILOGUE_WARPS); }
         for (int s = 0; s < ACC_STAGES; ++s) { barrier_init(&control.acc_full[s], 1); barrier_init(&control.acc_empty[s], EPILOGUE_WARPS); }
         for (int s = 0; s < 2; ++s) { barrier_init(&control.exchange_full[s], 4); barrier_init(&control.exchange_empty[s], 4); }
         for (int s = 0; s < 4; ++s) control.flagged_count[s] = 0;
@@ -317,31 +364,42 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
     } else {
         const int quarter = warp & 3, group = warp >> 2, row_in_tile = quarter * 32 + lane;
         const uint32_t lanes = tensor_memory + (uint32_t(quarter * 32) << 16) + group * (TILE_CODES / 2);
-        int loaded_head = -1, step = 0, product = 0;
+        int loaded_head = -1, step = 0, product = 0, code_uses = 0;
         float code_max = 0.f;
         bool ok = true;
         for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
             const int head = tile / tiles_per_head, row = (tile % tiles_per_head) * TILE_ROWS + row_in_tile;  // row in [B*N]
-            float norm2 = 0.f;
-            if (group == 1) {  // this half also measures the row
-                const uint4* source = reinterpret_cast<const uint4*>(x + (int64_t(row) * heads + head) * D);
-#pragma unroll
-                for (int c = 0; c < D / 8; ++c) norm2 = squares(__ldg(source + c), norm2);
-            } else if (head != loaded_head) {  // largest squared code norm of the head, per warp
-                const __nv_bfloat16* head_codes = codebook + int64_t(head) * vocab * D;
+            const int stage = step % A_STAGES;
+            if (head != loaded_head) {  // largest squared code norm of the head, per warp
+                ok = barrier_wait(&control.code_full, code_uses & 1, control, 11);
+                if (!ok) break;
+                ++code_uses;
                 code_max = 0.f;
-                for (int v = lane; v < vocab; v += 32) {
-                    const uint4* code = reinterpret_cast<const uint4*>(head_codes + int64_t(v) * D);
-                    float sum = 0.f;
-#pragma unroll
-                    for (int c = 0; c < D / 8; ++c) sum = squares(__ldg(code + c), sum);
-                    code_max = fmaxf(code_max, sum);
-                }
+                for (int v = lane; v < vocab; v += 32)
+                    code_max = fmaxf(code_max, shared_row_squares<D>(codes + (v / TILE_CODES) * KBLOCKS * BLOCK_BYTES, v % TILE_CODES, lane));
 #pragma unroll
                 for (int s = 16; s; s >>= 1) code_max = fmaxf(code_max, __shfl_xor_sync(FULL, code_max, s));
+                __syncwarp();
+                if (lane == 0) barrier_arrive(&control.code_empty);
                 loaded_head = head;
             }
-            TopTwo even{-INFINITY, -INFINITY, -INFINITY, 0}, odd{-INFINITY, -INFINITY, -INFINITY, 0};
+            // the row's squared norm, from the tile the TMA brought
+            ok = barrier_wait(&control.a_full[stage], (step / A_STAGES) & 1, control, 10);
+            if (!ok) break;
+            const float norm2 = shared_row_squares<D>(a_ring + stage * A_BYTES, row_in_tile, lane);
+            __syncwarp();
+            if (lane == 0) barrier_arrive(&control.a_empty[stage]);
+            // |tensor-core logit - exact| <= 4 D u sum|x e| (sixteen-term blocks whose addends may be truncated),
+            // |pinned logit - exact| <= D u sum|x e|, u = 2^-24, and sum|x e| <= |x|_2 |e|_2 =: bound.  Two logits
+            // further apart than delta = 2 * (5 D u bound), with a little slack, keep their order.
+            const float bound = sqrtf(norm2 * code_max) * 1.01f;
+            Margin margin;
+            margin.delta = 2.f * float(5 * D) * 5.9604645e-8f * bound * 1.001f + 1e-37f;
+            // gain = 2^100 / (power of two above the bound): threshold * gain stays finite
+            const unsigned exponent = max(__float_as_uint(bound) >> 23, 107u);
+            margin.gain = __uint_as_float((353u - exponent) << 23);
+            margin.sharp = margin.delta * margin.gain >= 1.f;
+            Leader leader{-INFINITY, 0, false};
             for (int j = 0; j < code_tiles; ++j, ++product) {
                 const int slot = product % ACC_STAGES;
                 ok = barrier_wait(&control.acc_full[slot], (product / ACC_STAGES) & 1, control, 6);
@@ -355,30 +413,15 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 __syncwarp();
                 if (lane == 0) barrier_arrive(&control.acc_empty[slot]);  // the logits are in registers
                 const int chunk = j * (TILE_CODES / 32) + group * 2;
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    even.offer(r0[i], r0[i + 1], i);
-                    odd.offer(r0[i + 2], r0[i + 3], i + 2);
-                }
-                even.close_chunk(chunk);
-                odd.close_chunk(chunk);
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    even.offer(r1[i], r1[i + 1], i);
-                    odd.offer(r1[i + 2], r1[i + 3], i + 2);
-                }
-                even.close_chunk(chunk + 1);
-                odd.close_chunk(chunk + 1);
+                fold_chunk(leader, r0, chunk, margin);
+                fold_chunk(leader, r1, chunk + 1, margin);
             }
             if (!ok) break;
-            float first = fmaxf(even.first, odd.first);
-            float second = max3(even.second, odd.second, fminf(even.first, odd.first));
-            int arg = even.first >= odd.first ? even.arg() : odd.arg();
             const int side = step & 1;
             if (group == 1) {
                 ok = barrier_wait(&control.exchange_empty[side], ((step >> 1) & 1) ^ 1, control, 7);
                 if (!ok) break;
-                control.exchange[side][row_in_tile] = Exchange{first, second, arg, norm2};
+                control.exchange[side][row_in_tile] = Exchange{leader.first, leader.arg, leader.clean, 0};
                 __syncwarp();
                 if (lane == 0) barrier_arrive(&control.exchange_full[side]);
             } else {
@@ -387,14 +430,10 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 const Exchange other = control.exchange[side][row_in_tile];
                 __syncwarp();
                 if (lane == 0) barrier_arrive(&control.exchange_empty[side]);
-                second = max3(second, other.second, fminf(first, other.first));
-                arg = first >= other.first ? arg : other.arg;
-                first = fmaxf(first, other.first);
-                // |tensor-core logit - exact| <= 4 D u sum|x e| (sixteen-term blocks whose addends may be truncated),
-                // |pinned logit - exact| <= D u sum|x e|, u = 2^-24, sum|x e| <= |x|_2 |e|_2; the index bits move a
-                // key by less than 2^-18 of its size, or by less than 2^-144 near zero.
-                const float tolerance = (float(5 * D) * 5.9604645e-8f + 3.8146973e-6f) * sqrtf(other.norm2 * code_max) * 1.01f + 1e-37f;
-                const bool flagged = !(first - second > 2.f * tolerance);
+                const bool mine = leader.first >= other.first;
+                const bool apart = fabsf(leader.first - other.first) > margin.delta;  // false for NaN and for two -inf
+                const bool flagged = !(apart && (mine ? leader.clean : other.clean != 0));
+                const int arg = mine ? leader.arg : other.arg;
                 const int batch = row / n, position = row % n;
                 if (!flagged) labels[(int64_t(batch) * heads + head) * n + position] = arg;
                 const unsigned mask = __ballot_sync(FULL, flagged);
@@ -472,7 +511,7 @@ bool make_map(CUtensorMap* map, const void* data, uint64_t rows, uint64_t column
 template <int D>
 cudaError_t launch(const CUtensorMap& x_map, const CUtensorMap& code_map, const __nv_bfloat16* x, const __nv_bfloat16* codebook,
                    int n, int heads, int vocab, int tiles_per_head, int total_tiles, int* labels, cudaStream_t stream) {
-    const int bytes = vocab * D * 2 + A_STAGES * (D / KBLOCK) * BLOCK_BYTES + int(sizeof(Control)) + 1024;
+    const int bytes = vocab * D * 2 + (D == 64 ? 4 : 2) * (D / KBLOCK) * BLOCK_BYTES + int(sizeof(Control)) + 1024;
     const cudaError_t status = cudaFuncSetAttribute(labels_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (status != cudaSuccess) return status;
     const int grid = total_tiles < device_sm_count() ? total_tiles : device_sm_count();
