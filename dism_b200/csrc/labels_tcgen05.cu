@@ -6,20 +6,25 @@
 //
 // One persistent CTA per SM walks a contiguous range of (head, 128-row tile) pairs:
 //   producer warp   TMA: the head's whole codebook once (128-byte swizzled, K-major), then one
-//                   128 x D tile of x per step into a two-stage ring;
+//                   128 x D tile of x per step into a ring;
 //   MMA warp        one thread issues tcgen05.mma (M=128, N=128, K=16) for each 128-code slice of the
-//                   codebook into a ring of FP32 accumulators in tensor memory;
-//   eight epilogue  read the accumulators with tcgen05.ld (row = tensor-memory lane = thread), keep the
-//   warps           best and second-best logit per row, and write the label.
+//                   codebook into a ring of four FP32 accumulators: all of tensor memory;
+//   norm warp       squared norms of the tile's rows (the margin below scales with them);
+//   sixteen         read the accumulators with tcgen05.ld (row = tensor-memory lane = thread; a warp
+//   epilogue warps  owns 32 rows and half the columns of every other accumulator) and keep, per row,
+//                   the largest logit and the columns of all logits within a safety margin of it.
+//
 // The epilogue is the instruction bound of the kernel, and min/max/logic instructions issue at half
 // the FMA rate.  So the half-rate pipe only finds the maximum of each 32-column chunk (three-input
-// max: half an instruction per logit), and the full-rate pipe does the rest with saturating FMAs:
-// it counts the logits within the safety margin of the leader and sums their column numbers.
+// max: half an instruction per logit); the full-rate pipe marks the logits above the threshold with
+// a saturating FMA, g = sat((s - t) * gain), and a second FMA adds g * 2^column into a bit mask.
+// gain is a power of two chosen from the exponent of t so that g is exactly 0 or 1 for every float s.
 //
-// Labels are defined by the pinned FP32 order (d ascending, one rounding per add).  A row whose
-// best logit has another one within a rigorous bound on |tensor-core logit - pinned logit| is
-// recomputed in the pinned order by a whole warp after the CTA's last tile; all other rows
-// provably have the same arg-max in both orders.
+// Labels are defined by the pinned FP32 order (d ascending, one rounding per add).  delta is a
+// rigorous bound on how far the tensor-core order can move the difference of two logits, so only
+// columns within delta of the row's largest logit can win in the pinned order.  One such column:
+// it is the label.  Two (a near tie): the two pinned logits are computed by one thread after the
+// CTA's last tile.  More: a whole warp recomputes the row in the pinned order.
 //
 // Every wait on an mbarrier is bounded: when one runs out the CTA records a fault code, all roles
 // leave their loops, tensor memory is freed and the kernel returns.
@@ -34,26 +39,29 @@ constexpr int TILE_ROWS = 128;   // rows of x per tile: the 128 lanes of tensor 
 constexpr int TILE_CODES = 128;  // codes per accumulator: 128 FP32 columns
 constexpr int KBLOCK = 64;       // elements in one 128-byte swizzled row
 constexpr int BLOCK_BYTES = TILE_ROWS * 128;
-constexpr int ACC_STAGES = 4;  // all 512 columns of tensor memory
+constexpr int ACC_STAGES = 4;    // all 512 columns of tensor memory
 constexpr int MAX_A_STAGES = 4;
-constexpr int EPILOGUE_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, THREADS = 320;
-constexpr int FLAG_CAPACITY = 256;  // per finishing warp
+constexpr int EPILOGUE_WARPS = 16, PRODUCER_WARP = 16, MMA_WARP = 17, NORM_WARP = 18, THREADS = 19 * 32;
+constexpr int LIST_CAPACITY = 256;  // per finishing warp and list
 constexpr unsigned WAIT_LIMIT = 1u << 20, SETTLE_LIMIT = 1u << 14;
 constexpr int MAX_CODE_BYTES = 128 * 1024;
 
-struct Exchange {
-    float first;
-    int arg, clean, pad;
+// Columns that can still win a row: none yet (count 0), a, a and b, or too many to list (count 3).
+struct Candidates {
+    float first;  // largest logit seen
+    int a, b, count;
 };
 
 struct Control {
     uint64_t code_full, code_empty, drain, list_ready;
-    uint64_t a_full[MAX_A_STAGES], a_empty[MAX_A_STAGES];
+    uint64_t a_full[MAX_A_STAGES], a_empty[MAX_A_STAGES], norm_full[MAX_A_STAGES];
     uint64_t acc_full[ACC_STAGES], acc_empty[ACC_STAGES];
     uint64_t exchange_full[2], exchange_empty[2];
-    Exchange exchange[2][TILE_ROWS];
-    int flagged[4][FLAG_CAPACITY];
-    int flagged_count[4];
+    Candidates exchange[2][3][TILE_ROWS];
+    float norm2[MAX_A_STAGES][TILE_ROWS];
+    int pairs[4][LIST_CAPACITY][3];  // near ties: row id and the two columns
+    int crowded[4][LIST_CAPACITY];   // rows with more than two columns in reach
+    int pair_count[4], crowded_count[4];
     uint32_t tensor_memory;
     int abort;
 };
@@ -143,27 +151,13 @@ __device__ __forceinline__ float fma_saturate(float a, float b, float c) {
     return d;
 }
 
-// What a row knows after some of its logits: the largest one, its column, and whether every other
-// logit seen so far is more than `delta` below it (clean).
-struct Leader {
-    float first;
-    int arg;
-    bool clean;
-};
-
-// Per-row constants of the margin test.
-struct Margin {
-    float delta;  // a logit this far below the leader cannot overtake it in the pinned order
-    float gain;   // power of two that turns "above the threshold" into a saturated 1
-    bool sharp;   // delta * gain >= 1: the chunk maximum itself saturates
-};
-
-// Folds 32 logits (one chunk of columns) into the leader.  The min/max pipe runs at half rate, so
-// it only finds the chunk maximum (three-input max, half an instruction per logit); counting the
-// logits within delta of the leader, and summing their columns, is done with saturating FMAs on
-// the full-rate pipe: g = sat((s - t) * gain) is 1 above the threshold t, 0 at or below it.  A
-// fractional g (a logit within 1/gain of t) makes the count differ from 1 and the row not clean.
-__device__ __forceinline__ void fold_chunk(Leader& leader, const uint32_t (&r)[32], int chunk, const Margin margin) {
+// Folds 32 logits (columns base .. base+31) into the row's candidates.
+//   t = max(first, chunk maximum) - delta; a logit at or below t cannot win the row.
+//   gain = 2^(27 - exponent of t), so (s - t) * gain is at least 8 for every float s > t (two
+//   distinct floats near t differ by at least 2^-24 |t|) and saturates to exactly 1; it is at most
+//   0 for s <= t and saturates to exactly 0.  The mask sums are therefore exact integers.
+// A chunk maximum more than delta above the old leader puts every earlier column out of reach.
+__device__ __forceinline__ void fold_chunk(Candidates& row, const uint32_t (&r)[32], int base, float delta) {
     float m0 = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
     float m1 = max3(__uint_as_float(r[3]), __uint_as_float(r[4]), __uint_as_float(r[5]));
 #pragma unroll
@@ -172,20 +166,34 @@ __device__ __forceinline__ void fold_chunk(Leader& leader, const uint32_t (&r)[3
         m1 = max3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
     }
     const float top = fmaxf(max3(m0, __uint_as_float(r[30]), __uint_as_float(r[31])), m1);
-    const float best = fmaxf(leader.first, top);
-    const float offset = -(best - margin.delta) * margin.gain;
-    float count[2] = {0.f, 0.f}, columns[2] = {0.f, 0.f};
+    const float best = fmaxf(row.first, top);
+    const float threshold = best - delta;
+    const unsigned exponent = (__float_as_uint(threshold) >> 23) & 0xffu;
+    const bool scaled = exponent >= 27u && exponent < 255u;  // |t| in [2^-100, inf): the gain is a finite float
+    const float gain = __uint_as_float((281u - max(exponent, 27u)) << 23);
+    const float offset = -threshold * gain;
+    float low = 0.f, high = 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const float g = fma_saturate(__uint_as_float(r[i]), margin.gain, offset);
-        count[i & 1] += g;
-        columns[i & 1] = fmaf(g, float(i), columns[i & 1]);
+    for (int i = 0; i < 16; ++i) {
+        low = fmaf(fma_saturate(__uint_as_float(r[i]), gain, offset), float(1 << i), low);
+        high = fmaf(fma_saturate(__uint_as_float(r[16 + i]), gain, offset), float(1 << i), high);
     }
-    const bool clear = top > leader.first + margin.delta;                 // a new leader, the old one out of reach
-    const bool close = !clear && top >= leader.first - margin.delta;      // within reach of the old leader
-    leader.clean = clear ? (margin.sharp && count[0] + count[1] == 1.f) : (leader.clean && !close);
-    leader.arg = clear ? chunk * 32 + int(columns[0] + columns[1]) : leader.arg;
-    leader.first = best;
+    const unsigned mask = unsigned(low) | (unsigned(high) << 16);
+    const int inside = __popc(mask), lowest = base + __ffs(mask) - 1, highest = base + 31 - __clz(mask);
+    const int kept = top > row.first + delta ? 0 : row.count;  // a clear new leader drops the earlier columns
+    row.b = (inside >= 1 && kept == 1) ? lowest : ((inside == 2 && kept == 0) ? highest : row.b);
+    row.a = (inside >= 1 && kept == 0) ? lowest : row.a;
+    row.count = scaled ? min(kept + inside, 3) : 3;
+    row.first = best;
+}
+
+// Adds the candidates of another column range of the same row.
+__device__ __forceinline__ void merge_candidates(Candidates& row, const Candidates other, float best, float delta) {
+    if (!(other.first >= best - delta) || other.count == 0) return;  // everything there is out of reach
+    if (other.count == 3 || row.count + other.count > 2) { row.count = 3; return; }
+    if (row.count == 0) row.a = other.a; else row.b = other.a;
+    if (other.count == 2) row.b = other.b;
+    row.count += other.count;
 }
 
 __device__ __forceinline__ float squares(uint4 raw, float sum) {
@@ -253,6 +261,23 @@ __device__ int pinned_label(const __nv_bfloat16* __restrict__ row, const __nv_bf
     return arg;
 }
 
+// Pinned-order logit of one row against one code, by one thread.
+template <int D>
+__device__ float pinned_logit(const __nv_bfloat16* __restrict__ row, const __nv_bfloat16* __restrict__ code) {
+    float acc = 0.f;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+        const uint4 xs = __ldg(reinterpret_cast<const uint4*>(row) + c), es = __ldg(reinterpret_cast<const uint4*>(code) + c);
+        const unsigned xw[4] = {xs.x, xs.y, xs.z, xs.w}, ew[4] = {es.x, es.y, es.z, es.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            acc = __fadd_rn(acc, __fmul_rn(__uint_as_float(xw[w] << 16), __uint_as_float(ew[w] << 16)));
+            acc = __fadd_rn(acc, __fmul_rn(__uint_as_float(xw[w] & 0xffff0000u), __uint_as_float(ew[w] & 0xffff0000u)));
+        }
+    }
+    return acc;
+}
+
 template <int D>
 __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map,
                                                                     const __grid_constant__ CUtensorMap code_map,
@@ -276,10 +301,20 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
         barrier_init(&control.code_empty, 1 + EPILOGUE_WARPS);  // the tensor core and the warps that measure the codes
         barrier_init(&control.drain, 1);
         barrier_init(&control.list_ready, 4);
-        for (int s = 0; s < A_STAGES; ++s) { barrier_init(&control.a_full[s], 1); barrier_init(&control.a_empty[s], 1 + EPILOGUE_WARPS); }
-        for (int s = 0; s < ACC_STAGES; ++s) { barrier_init(&control.acc_full[s], 1); barrier_init(&control.acc_empty[s], EPILOGUE_WARPS); }
-        for (int s = 0; s < 2; ++s) { barrier_init(&control.exchange_full[s], 4); barrier_init(&control.exchange_empty[s], 4); }
-        for (int s = 0; s < 4; ++s) control.flagged_count[s] = 0;
+        for (int s = 0; s < A_STAGES; ++s) {
+            barrier_init(&control.a_full[s], 1);
+            barrier_init(&control.a_empty[s], 2 + EPILOGUE_WARPS);  // tensor core, norm warp, readers of the norms
+            barrier_init(&control.norm_full[s], 1);
+        }
+        for (int s = 0; s < ACC_STAGES; ++s) {
+            barrier_init(&control.acc_full[s], 1);
+            barrier_init(&control.acc_empty[s], EPILOGUE_WARPS / 2);
+        }
+        for (int s = 0; s < 2; ++s) {
+            barrier_init(&control.exchange_full[s], 12);
+            barrier_init(&control.exchange_empty[s], 4);
+        }
+        for (int s = 0; s < 4; ++s) control.pair_count[s] = control.crowded_count[s] = 0;
         control.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -297,8 +332,7 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
     if (warp == PRODUCER_WARP) {
         if (lane == 0) {
             int loaded_head = -1, code_loads = 0, step = 0;
-            bool ok = true;
-            for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
+            for (int tile = first_tile; tile < last_tile; ++tile, ++step) {
                 const int head = tile / tiles_per_head, row = (tile % tiles_per_head) * TILE_ROWS;
                 if (head != loaded_head) {
                     // the tensor core must have finished with the previous head's codes
@@ -312,8 +346,7 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                     ++code_loads;
                 }
                 const int stage = step % A_STAGES;
-                ok = barrier_wait(&control.a_empty[stage], ((step / A_STAGES) & 1) ^ 1, control, 2);
-                if (!ok) break;
+                if (!barrier_wait(&control.a_empty[stage], ((step / A_STAGES) & 1) ^ 1, control, 2)) break;
                 barrier_expect(&control.a_full[stage], uint32_t(A_BYTES));
                 for (int kb = 0; kb < KBLOCKS; ++kb)
                     tma_load(a_ring + stage * A_BYTES + kb * BLOCK_BYTES, &x_map, head * D + kb * KBLOCK, row, &control.a_full[stage]);
@@ -361,9 +394,26 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
             mma_commit(&control.drain);
             barrier_settle(&control.drain, 0);
         }
+    } else if (warp == NORM_WARP) {
+        int step = 0;
+        for (int tile = first_tile; tile < last_tile; ++tile, ++step) {
+            const int stage = step % A_STAGES;
+            if (!barrier_wait(&control.a_full[stage], (step / A_STAGES) & 1, control, 12)) break;
+#pragma unroll
+            for (int part = 0; part < TILE_ROWS / 32; ++part)
+                control.norm2[stage][part * 32 + lane] = shared_row_squares<D>(a_ring + stage * A_BYTES, part * 32 + lane, lane);
+            __syncwarp();
+            if (lane == 0) {
+                barrier_arrive(&control.norm_full[stage]);
+                barrier_arrive(&control.a_empty[stage]);
+            }
+        }
     } else {
-        const int quarter = warp & 3, group = warp >> 2, row_in_tile = quarter * 32 + lane;
-        const uint32_t lanes = tensor_memory + (uint32_t(quarter * 32) << 16) + group * (TILE_CODES / 2);
+        // Rows quarter*32 .. +31 of every tile; columns half*64 .. +63 of the accumulators whose running
+        // number has this warp's parity.
+        const int quarter = warp & 3, group = warp >> 2, half = group & 1, parity = group >> 1;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lanes = tensor_memory + (uint32_t(quarter * 32) << 16) + half * (TILE_CODES / 2);
         int loaded_head = -1, step = 0, product = 0, code_uses = 0;
         float code_max = 0.f;
         bool ok = true;
@@ -383,89 +433,117 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 if (lane == 0) barrier_arrive(&control.code_empty);
                 loaded_head = head;
             }
-            // the row's squared norm, from the tile the TMA brought
-            ok = barrier_wait(&control.a_full[stage], (step / A_STAGES) & 1, control, 10);
+            ok = barrier_wait(&control.norm_full[stage], (step / A_STAGES) & 1, control, 10);
             if (!ok) break;
-            const float norm2 = shared_row_squares<D>(a_ring + stage * A_BYTES, row_in_tile, lane);
+            const float norm2 = control.norm2[stage][row_in_tile];
             __syncwarp();
             if (lane == 0) barrier_arrive(&control.a_empty[stage]);
             // |tensor-core logit - exact| <= 4 D u sum|x e| (sixteen-term blocks whose addends may be truncated),
-            // |pinned logit - exact| <= D u sum|x e|, u = 2^-24, and sum|x e| <= |x|_2 |e|_2 =: bound.  Two logits
-            // further apart than delta = 2 * (5 D u bound), with a little slack, keep their order.
-            const float bound = sqrtf(norm2 * code_max) * 1.01f;
-            Margin margin;
-            margin.delta = 2.f * float(5 * D) * 5.9604645e-8f * bound * 1.001f + 1e-37f;
-            // gain = 2^100 / (power of two above the bound): threshold * gain stays finite
-            const unsigned exponent = max(__float_as_uint(bound) >> 23, 107u);
-            margin.gain = __uint_as_float((353u - exponent) << 23);
-            margin.sharp = margin.delta * margin.gain >= 1.f;
-            Leader leader{-INFINITY, 0, false};
+            // |pinned logit - exact| <= D u sum|x e|, u = 2^-24, and sum|x e| <= |x|_2 |e|_2.  Two logits
+            // further apart than delta = 2 * 5 D u |x|_2 |e|_2 (with a little slack) keep their order.
+            const float delta = 2.f * float(5 * D) * 5.9604645e-8f * sqrtf(norm2 * code_max) * 1.02f + 1e-37f;
+            Candidates mine{-INFINITY, 0, 0, 0};
             for (int j = 0; j < code_tiles; ++j, ++product) {
+                if ((product & 1) != parity) continue;
                 const int slot = product % ACC_STAGES;
                 ok = barrier_wait(&control.acc_full[slot], (product / ACC_STAGES) & 1, control, 6);
                 if (!ok) break;
                 fence_after_sync();
-                uint32_t r0[32], r1[32];
-                load_columns(r0, lanes + slot * TILE_CODES);
-                load_columns(r1, lanes + slot * TILE_CODES + 32);
+                const int column = j * TILE_CODES + half * (TILE_CODES / 2);
+                uint32_t r[32];
+                load_columns(r, lanes + slot * TILE_CODES);
+                wait_columns();
+                fold_chunk(mine, r, column, delta);
+                load_columns(r, lanes + slot * TILE_CODES + 32);
                 wait_columns();
                 fence_before_sync();
                 __syncwarp();
                 if (lane == 0) barrier_arrive(&control.acc_empty[slot]);  // the logits are in registers
-                const int chunk = j * (TILE_CODES / 32) + group * 2;
-                fold_chunk(leader, r0, chunk, margin);
-                fold_chunk(leader, r1, chunk + 1, margin);
+                fold_chunk(mine, r, column + 32, delta);
             }
             if (!ok) break;
             const int side = step & 1;
-            if (group == 1) {
+            if (group != 0) {
                 ok = barrier_wait(&control.exchange_empty[side], ((step >> 1) & 1) ^ 1, control, 7);
                 if (!ok) break;
-                control.exchange[side][row_in_tile] = Exchange{leader.first, leader.arg, leader.clean, 0};
+                control.exchange[side][group - 1][row_in_tile] = mine;
                 __syncwarp();
                 if (lane == 0) barrier_arrive(&control.exchange_full[side]);
-            } else {
-                ok = barrier_wait(&control.exchange_full[side], (step >> 1) & 1, control, 8);
-                if (!ok) break;
-                const Exchange other = control.exchange[side][row_in_tile];
-                __syncwarp();
-                if (lane == 0) barrier_arrive(&control.exchange_empty[side]);
-                const bool mine = leader.first >= other.first;
-                const bool apart = fabsf(leader.first - other.first) > margin.delta;  // false for NaN and for two -inf
-                const bool flagged = !(apart && (mine ? leader.clean : other.clean != 0));
-                const int arg = mine ? leader.arg : other.arg;
-                const int batch = row / n, position = row % n;
-                if (!flagged) labels[(int64_t(batch) * heads + head) * n + position] = arg;
-                const unsigned mask = __ballot_sync(FULL, flagged);
-                if (mask) {
-                    const int count = control.flagged_count[quarter], more = __popc(mask);
-                    if (count + more <= FLAG_CAPACITY) {
-                        if (flagged) control.flagged[quarter][count + __popc(mask & ((1u << lane) - 1))] = tile * TILE_ROWS + row_in_tile;
-                        __syncwarp();
-                        if (lane == 0) control.flagged_count[quarter] = count + more;
-                        __syncwarp();
-                    } else {  // list full: recompute here
-                        for (unsigned rest = mask; rest; rest &= rest - 1) {
-                            const int r = (tile % tiles_per_head) * TILE_ROWS + quarter * 32 + __ffs(rest) - 1;
-                            const int label = pinned_label<D>(x + (int64_t(r) * heads + head) * D, codebook + int64_t(head) * vocab * D, vocab, lane);
-                            if (lane == 0) labels[(int64_t(r / n) * heads + head) * n + r % n] = label;
-                        }
+                continue;
+            }
+            ok = barrier_wait(&control.exchange_full[side], (step >> 1) & 1, control, 8);
+            if (!ok) break;
+            const Candidates theirs[3] = {control.exchange[side][0][row_in_tile], control.exchange[side][1][row_in_tile],
+                                          control.exchange[side][2][row_in_tile]};
+            __syncwarp();
+            if (lane == 0) barrier_arrive(&control.exchange_empty[side]);
+            const float best = fmaxf(fmaxf(mine.first, theirs[0].first), fmaxf(theirs[1].first, theirs[2].first));
+            Candidates all{best, 0, 0, 0};
+            merge_candidates(all, mine, best, delta);
+#pragma unroll
+            for (int g = 0; g < 3; ++g) merge_candidates(all, theirs[g], best, delta);
+            const int64_t out = (int64_t(row / n) * heads + head) * n + row % n;
+            if (all.count == 1) labels[out] = all.a;
+            const int id = tile * TILE_ROWS + row_in_tile;
+            // near ties go to the pair list while it has room, everything else to the crowded list
+            unsigned pair_mask = __ballot_sync(FULL, all.count == 2);
+            if (pair_mask) {
+                const int count = control.pair_count[quarter], more = __popc(pair_mask);
+                if (count + more <= LIST_CAPACITY) {
+                    if (all.count == 2) {
+                        int* entry = control.pairs[quarter][count + __popc(pair_mask & ((1u << lane) - 1))];
+                        entry[0] = id, entry[1] = all.a, entry[2] = all.b;
+                    }
+                    __syncwarp();
+                    if (lane == 0) control.pair_count[quarter] = count + more;
+                    __syncwarp();
+                    pair_mask = 0;
+                }
+            }
+            const bool crowded = all.count != 1 && (all.count != 2 || pair_mask != 0);
+            const unsigned crowded_mask = __ballot_sync(FULL, crowded);
+            if (crowded_mask) {
+                const int count = control.crowded_count[quarter], more = __popc(crowded_mask);
+                if (count + more <= LIST_CAPACITY) {
+                    if (crowded) control.crowded[quarter][count + __popc(crowded_mask & ((1u << lane) - 1))] = id;
+                    __syncwarp();
+                    if (lane == 0) control.crowded_count[quarter] = count + more;
+                    __syncwarp();
+                } else {  // list full: recompute here
+                    for (unsigned rest = crowded_mask; rest; rest &= rest - 1) {
+                        const int r = (tile % tiles_per_head) * TILE_ROWS + quarter * 32 + __ffs(rest) - 1;
+                        const int label = pinned_label<D>(x + (int64_t(r) * heads + head) * D, codebook + int64_t(head) * vocab * D, vocab, lane);
+                        if (lane == 0) labels[(int64_t(r / n) * heads + head) * n + r % n] = label;
                     }
                 }
             }
         }
-        // Rows on the lists: pinned order, one warp per row, all eight warps.
+        // The lists: near ties one thread per row, crowded rows one warp per row, all sixteen warps.
         if (ok && group == 0) {
             __syncwarp();
             if (lane == 0) barrier_arrive(&control.list_ready);
         }
         if (ok && barrier_wait(&control.list_ready, 0, control, 9)) {
+            for (int list = 0; list < 4; ++list) {
+                const int count = *reinterpret_cast<volatile int*>(&control.pair_count[list]);
+                for (int entry = threadIdx.x; entry < count; entry += EPILOGUE_WARPS * 32) {
+                    const int id = control.pairs[list][entry][0], a = control.pairs[list][entry][1], b = control.pairs[list][entry][2];
+                    const int tile = id / TILE_ROWS, head = tile / tiles_per_head;
+                    const int r = (tile % tiles_per_head) * TILE_ROWS + id % TILE_ROWS;
+                    const __nv_bfloat16* source = x + (int64_t(r) * heads + head) * D;
+                    const __nv_bfloat16* head_codes = codebook + int64_t(head) * vocab * D;
+                    const float logit_a = pinned_logit<D>(source, head_codes + int64_t(a) * D);
+                    const float logit_b = pinned_logit<D>(source, head_codes + int64_t(b) * D);
+                    const bool first_wins = logit_a > logit_b || (logit_a == logit_b && a < b);
+                    labels[(int64_t(r / n) * heads + head) * n + r % n] = first_wins ? a : b;
+                }
+            }
             int turn = 0;
             for (int list = 0; list < 4; ++list) {
-                const int count = *reinterpret_cast<volatile int*>(&control.flagged_count[list]);
+                const int count = *reinterpret_cast<volatile int*>(&control.crowded_count[list]);
                 for (int entry = 0; entry < count; ++entry, ++turn) {
                     if (turn % EPILOGUE_WARPS != warp) continue;
-                    const int id = control.flagged[list][entry], tile = id / TILE_ROWS;
+                    const int id = control.crowded[list][entry], tile = id / TILE_ROWS;
                     const int head = tile / tiles_per_head, r = (tile % tiles_per_head) * TILE_ROWS + id % TILE_ROWS;
                     const int label = pinned_label<D>(x + (int64_t(r) * heads + head) * D, codebook + int64_t(head) * vocab * D, vocab, lane);
                     if (lane == 0) labels[(int64_t(r / n) * heads + head) * n + r % n] = label;
