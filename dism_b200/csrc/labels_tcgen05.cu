@@ -2,16 +2,16 @@
 //
 // Same contract as the general kernel in labels.cu (reference: dism_v3/python/flash_dism/emb_kernel.py:88-108,
 // kernels/interp_true.py:25-33) for the shapes the tensor-memory pipeline covers: D of 64 or 128,
-// a codebook of a multiple of 128 codes that fits in 128 KiB, N a multiple of 128.
+// a codebook of a multiple of 256 codes that fits in 128 KiB, N a multiple of 128.
 //
 // One persistent CTA per SM walks a contiguous range of (head, 128-row tile) pairs:
 //   producer warp   TMA: the head's whole codebook once (128-byte swizzled, K-major), then one
 //                   128 x D tile of x per step into a ring;
-//   MMA warp        one thread issues tcgen05.mma (M=128, N=128, K=16) for each 128-code slice of the
-//                   codebook into a ring of four FP32 accumulators: all of tensor memory;
+//   MMA warp        one thread issues tcgen05.mma (M=128, N=256, K=16) for each 256-code slice of the
+//                   codebook into one of two FP32 accumulators: all of tensor memory;
 //   norm warp       squared norms of the tile's rows (the margin below scales with them);
 //   sixteen         read the accumulators with tcgen05.ld (row = tensor-memory lane = thread; a warp
-//   epilogue warps  owns 32 rows and half the columns of every other accumulator) and keep, per row,
+//   epilogue warps  owns 32 rows and a quarter of the columns of every accumulator) and keep, per row,
 //                   the largest logit and the columns of all logits within a safety margin of it.
 //
 // The epilogue is the instruction bound of the kernel, and min/max/logic instructions issue at half
@@ -19,6 +19,7 @@
 // max: half an instruction per logit); the full-rate pipe marks the logits above the threshold with
 // a saturating FMA, g = sat((s - t) * gain), and a second FMA adds g * 2^column into a bit mask.
 // gain is a power of two chosen from the exponent of t so that g is exactly 0 or 1 for every float s.
+// The masks are folded into the row's candidates once per 64 columns.
 //
 // Labels are defined by the pinned FP32 order (d ascending, one rounding per add).  delta is a
 // rigorous bound on how far the tensor-core order can move the difference of two logits, so only
@@ -36,14 +37,16 @@ namespace dism {
 namespace {
 
 constexpr int TILE_ROWS = 128;   // rows of x per tile: the 128 lanes of tensor memory
-constexpr int TILE_CODES = 128;  // codes per accumulator: 128 FP32 columns
+constexpr int TILE_CODES = 256;  // codes per accumulator: 256 FP32 columns, the widest single instruction
 constexpr int KBLOCK = 64;       // elements in one 128-byte swizzled row
-constexpr int BLOCK_BYTES = TILE_ROWS * 128;
-constexpr int ACC_STAGES = 4;    // all 512 columns of tensor memory
+constexpr int BLOCK_BYTES = TILE_ROWS * 128;        // 128 rows of x, 64 elements each
+constexpr int CODE_BLOCK_BYTES = TILE_CODES * 128;  // 256 codes, 64 elements each
+constexpr int ACC_STAGES = 2;    // two accumulators: all 512 columns of tensor memory
 constexpr int MAX_A_STAGES = 4;
-constexpr int EPILOGUE_WARPS = 16, PRODUCER_WARP = 16, MMA_WARP = 17, NORM_WARP = 18, THREADS = 19 * 32;
+constexpr int NORM_RING = 4;     // norms are prepared one tile ahead; warps are never more than one tile apart
+constexpr int EPILOGUE_WARPS = 16, EPILOGUE_GROUPS = 4, PRODUCER_WARP = 16, MMA_WARP = 17, NORM_WARP = 18, THREADS = 19 * 32;
 constexpr int LIST_CAPACITY = 256;  // per finishing warp and list
-constexpr unsigned WAIT_LIMIT = 1u << 20, SETTLE_LIMIT = 1u << 14;
+constexpr unsigned WAIT_LIMIT = 1u << 16, SETTLE_LIMIT = 1u << 14, PARK_NANOSECONDS = 20000;  // a wait gives up after about a second at most
 constexpr int MAX_CODE_BYTES = 128 * 1024;
 
 // Columns that can still win a row: none yet (count 0), a, a and b, or too many to list (count 3).
@@ -54,11 +57,12 @@ struct Candidates {
 
 struct Control {
     uint64_t code_full, code_empty, drain, list_ready;
-    uint64_t a_full[MAX_A_STAGES], a_empty[MAX_A_STAGES], norm_full[MAX_A_STAGES];
+    uint64_t a_full[MAX_A_STAGES], a_empty[MAX_A_STAGES], norm_done[NORM_RING];
     uint64_t acc_full[ACC_STAGES], acc_empty[ACC_STAGES];
     uint64_t exchange_full[2], exchange_empty[2];
-    Candidates exchange[2][3][TILE_ROWS];
-    float norm2[MAX_A_STAGES][TILE_ROWS];
+    Candidates exchange[2][EPILOGUE_GROUPS - 1][TILE_ROWS];
+    float norm2[NORM_RING][TILE_ROWS];  // squared row norms of the tile of a step, ring over steps
+    float code_max[2 * NORM_RING];      // largest squared code norm of that tile's head; the norm warp may be five steps ahead
     int pairs[4][LIST_CAPACITY][3];  // near ties: row id and the two columns
     int crowded[4][LIST_CAPACITY];   // rows with more than two columns in reach
     int pair_count[4], crowded_count[4];
@@ -85,11 +89,19 @@ __device__ __forceinline__ bool barrier_test(uint64_t* bar, uint32_t parity) {
                  : "=r"(done) : "r"(shared_address(bar)), "r"(parity) : "memory");
     return done != 0;
 }
+// The same test, but the hardware may park the thread for up to `nanoseconds` while the phase is open.
+__device__ __forceinline__ bool barrier_test_parked(uint64_t* bar, uint32_t parity, uint32_t nanoseconds) {
+    uint32_t done;
+    asm volatile("{.reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p;}"
+                 : "=r"(done) : "r"(shared_address(bar)), "r"(parity), "r"(nanoseconds) : "memory");
+    return done != 0;
+}
 // Bounded wait.  False: this wait ran out (fault `code` recorded) or another role already gave up.
 __device__ __noinline__ bool barrier_wait_slow(uint64_t* bar, uint32_t parity, Control& control, int code) {
     for (unsigned tries = 0; tries < WAIT_LIMIT; ++tries) {
-        if (barrier_test(bar, parity)) return true;
-        if ((tries & 63) == 63 && *reinterpret_cast<volatile int*>(&control.abort)) return false;
+        if (barrier_test_parked(bar, parity, PARK_NANOSECONDS)) return true;
+        if (*reinterpret_cast<volatile int*>(&control.abort)) return false;
+        if (tries >= 4) __nanosleep(tries < 64 ? 40 : 200);  // a waiting warp must not eat the issue slots of working ones
     }
     *reinterpret_cast<volatile int*>(&control.abort) = 1;
     atomicCAS(&labels_fault_code, 0, code);
@@ -114,7 +126,7 @@ __device__ __forceinline__ uint64_t operand_descriptor(uint32_t address) {
     return uint64_t((address & 0x3ffff) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
            (uint64_t(2) << 61);
 }
-// bf16 x bf16 -> f32, both operands K-major, M = 128, N = 128
+// bf16 x bf16 -> f32, both operands K-major, M = 128, N = 256
 constexpr uint32_t INSTRUCTION = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(TILE_CODES >> 3) << 17) | (uint32_t(TILE_ROWS >> 4) << 24);
 
 __device__ __forceinline__ void mma(uint32_t accumulator, uint64_t a, uint64_t b, uint32_t accumulate) {
@@ -127,15 +139,12 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void load_columns(uint32_t (&r)[32], uint32_t address) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
-        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(address));
+// 32 consecutive FP32 columns of this thread's tensor-memory lane.  The destinations are float registers:
+// a bit-cast from integer registers after an asynchronous load costs a move per value.
+__device__ __forceinline__ void load_columns(float (&r)[32], uint32_t address) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]), "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]), "=f"(r[16]), "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]), "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
+                 : "r"(address));
 }
 __device__ __forceinline__ void wait_columns() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -151,39 +160,63 @@ __device__ __forceinline__ float fma_saturate(float a, float b, float c) {
     return d;
 }
 
-// Folds 32 logits (columns base .. base+31) into the row's candidates.
-//   t = max(first, chunk maximum) - delta; a logit at or below t cannot win the row.
-//   gain = 2^(27 - exponent of t), so (s - t) * gain is at least 8 for every float s > t (two
-//   distinct floats near t differ by at least 2^-24 |t|) and saturates to exactly 1; it is at most
-//   0 for s <= t and saturates to exactly 0.  The mask sums are therefore exact integers.
-// A chunk maximum more than delta above the old leader puts every earlier column out of reach.
-__device__ __forceinline__ void fold_chunk(Candidates& row, const uint32_t (&r)[32], int base, float delta) {
-    float m0 = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
-    float m1 = max3(__uint_as_float(r[3]), __uint_as_float(r[4]), __uint_as_float(r[5]));
+// Largest of 32 logits: sixteen three-input max instructions.
+__device__ __forceinline__ float chunk_max(const float (&r)[32]) {
+    float m0 = max3(r[0], r[1], r[2]);
+    float m1 = max3(r[3], r[4], r[5]);
 #pragma unroll
     for (int i = 6; i < 30; i += 4) {
-        m0 = max3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-        m1 = max3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        m0 = max3(m0, r[i], r[i + 1]);
+        m1 = max3(m1, r[i + 2], r[i + 3]);
     }
-    const float top = fmaxf(max3(m0, __uint_as_float(r[30]), __uint_as_float(r[31])), m1);
-    const float best = fmaxf(row.first, top);
-    const float threshold = best - delta;
-    const unsigned exponent = (__float_as_uint(threshold) >> 23) & 0xffu;
-    const bool scaled = exponent >= 27u && exponent < 255u;  // |t| in [2^-100, inf): the gain is a finite float
-    const float gain = __uint_as_float((281u - max(exponent, 27u)) << 23);
-    const float offset = -threshold * gain;
+    return fmaxf(max3(m0, r[30], r[31]), m1);
+}
+
+// Bit i set: logit i of the chunk is above the threshold.  (s - t) * gain saturates to exactly 1
+// or 0 (see fold_product), so the two sums are exact 16-bit integers.
+__device__ __forceinline__ unsigned chunk_mask(const float (&r)[32], float gain, float offset) {
     float low = 0.f, high = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        low = fmaf(fma_saturate(__uint_as_float(r[i]), gain, offset), float(1 << i), low);
-        high = fmaf(fma_saturate(__uint_as_float(r[16 + i]), gain, offset), float(1 << i), high);
+        low = fmaf(fma_saturate(r[i], gain, offset), float(1 << i), low);
+        high = fmaf(fma_saturate(r[16 + i], gain, offset), float(1 << i), high);
     }
-    const unsigned mask = unsigned(low) | (unsigned(high) << 16);
-    const int inside = __popc(mask), lowest = base + __ffs(mask) - 1, highest = base + 31 - __clz(mask);
-    const int kept = top > row.first + delta ? 0 : row.count;  // a clear new leader drops the earlier columns
+    return unsigned(low) | (unsigned(high) << 16);
+}
+
+// Threshold for a chunk: t = best - delta, where best is the largest logit of the row so far; a logit
+// at or below t cannot win the row.  gain = 2^(27 - exponent of t), so (s - t) * gain is at least 8
+// for every float s > t (two distinct floats near t differ by at least 2^-24 |t|) and at most 0 for
+// s <= t; the product with a power of two is exact.  Not valid: |t| below 2^-100 or not finite.
+struct Threshold {
+    float gain, offset;
+    bool valid;
+};
+__device__ __forceinline__ Threshold make_threshold(float best, float delta) {
+    const float threshold = best - delta;
+    const unsigned exponent = __float_as_uint(threshold) & 0x7f800000u;
+    Threshold t;
+    t.valid = exponent - (27u << 23) < (228u << 23);  // biased exponent in [27, 255)
+    t.gain = __uint_as_float((281u << 23) - exponent);
+    t.offset = -threshold * t.gain;
+    return t;
+}
+
+// Folds one accumulator half (columns base .. base+63: chunk maxima and masks) into the row's
+// candidates.  Each mask was taken against the best logit known at the time, which is at most the
+// best now, so it holds every column of its chunk within delta of the best now, and possibly more.
+// A chunk whose threshold was not valid carries a full mask and makes the row crowded if it matters.
+__device__ __forceinline__ void fold_product(Candidates& row, float top0, unsigned mask0, float top1, unsigned mask1, float best,
+                                             int base, float delta) {
+    const float reach = best - delta;
+    const unsigned m0 = top0 >= reach ? mask0 : 0u, m1 = top1 >= reach ? mask1 : 0u;
+    const int kept = row.first >= reach ? row.count : 0;  // a leader out of reach takes its columns with it
+    const int inside = __popc(m0) + __popc(m1);
+    const int lowest = base + (m0 ? __ffs(m0) - 1 : 31 + __ffs(m1));
+    const int highest = base + (m1 ? 63 - __clz(m1) : 31 - __clz(m0));
     row.b = (inside >= 1 && kept == 1) ? lowest : ((inside == 2 && kept == 0) ? highest : row.b);
     row.a = (inside >= 1 && kept == 0) ? lowest : row.a;
-    row.count = scaled ? min(kept + inside, 3) : 3;
+    row.count = min(kept + inside, 3);
     row.first = best;
 }
 
@@ -209,21 +242,21 @@ __device__ __forceinline__ float squares(uint4 raw, float sum) {
 // Squared norm of one 128-byte-swizzled operand row in shared memory (the swizzle permutes the
 // 16-byte pieces inside the row, which a sum of squares does not see).  Lanes start at different
 // pieces so that a warp reading 32 consecutive rows meets no bank conflict.
-template <int D>
+template <int D, int KBLOCK_BYTES>
 __device__ __forceinline__ float shared_row_squares(const unsigned char* tile, int row, int lane) {
     float sum = 0.f;
 #pragma unroll
     for (int kb = 0; kb < D / KBLOCK; ++kb)
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-            sum = squares(*reinterpret_cast<const uint4*>(tile + kb * BLOCK_BYTES + row * 128 + ((c + lane) & 7) * 16), sum);
+            sum = squares(*reinterpret_cast<const uint4*>(tile + kb * KBLOCK_BYTES + row * 128 + ((c + lane) & 7) * 16), sum);
     return sum;
 }
 
 // Pinned-order arg-max of one row by a whole warp; every lane returns the label.  A lane works on
 // four codes at a time, because the additions of one code form a serial chain.
 template <int D>
-__device__ int pinned_label(const __nv_bfloat16* __restrict__ row, const __nv_bfloat16* __restrict__ codes, int vocab, int lane) {
+__device__ __noinline__ int pinned_label(const __nv_bfloat16* __restrict__ row, const __nv_bfloat16* __restrict__ codes, int vocab, int lane) {
     float top = -INFINITY;
     int arg = 0x7fffffff;
     for (int v0 = lane; v0 < vocab; v0 += 128) {
@@ -263,7 +296,7 @@ __device__ int pinned_label(const __nv_bfloat16* __restrict__ row, const __nv_bf
 
 // Pinned-order logit of one row against one code, by one thread.
 template <int D>
-__device__ float pinned_logit(const __nv_bfloat16* __restrict__ row, const __nv_bfloat16* __restrict__ code) {
+__device__ __noinline__ float pinned_logit(const __nv_bfloat16* __restrict__ row, const __nv_bfloat16* __restrict__ code) {
     float acc = 0.f;
 #pragma unroll
     for (int c = 0; c < D / 8; ++c) {
@@ -290,7 +323,7 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
     unsigned char* base = raw + ((1024u - (shared_address(raw) & 1023u)) & 1023u);  // swizzled tiles: 1024-byte aligned
     const int code_tiles = vocab / TILE_CODES;
     unsigned char* codes = base;
-    unsigned char* a_ring = codes + code_tiles * KBLOCKS * BLOCK_BYTES;
+    unsigned char* a_ring = codes + code_tiles * KBLOCKS * CODE_BLOCK_BYTES;
     Control& control = *reinterpret_cast<Control*>(a_ring + A_STAGES * A_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int first_tile = int(int64_t(blockIdx.x) * total_tiles / gridDim.x);
@@ -298,20 +331,20 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
 
     if (threadIdx.x == 0) {
         barrier_init(&control.code_full, 1);
-        barrier_init(&control.code_empty, 1 + EPILOGUE_WARPS);  // the tensor core and the warps that measure the codes
+        barrier_init(&control.code_empty, 2);  // the tensor core and the norm warp
         barrier_init(&control.drain, 1);
         barrier_init(&control.list_ready, 4);
         for (int s = 0; s < A_STAGES; ++s) {
             barrier_init(&control.a_full[s], 1);
-            barrier_init(&control.a_empty[s], 2 + EPILOGUE_WARPS);  // tensor core, norm warp, readers of the norms
-            barrier_init(&control.norm_full[s], 1);
+            barrier_init(&control.a_empty[s], 2 + EPILOGUE_WARPS);  // tensor core, norm warp, the warps that measure the rows
         }
+        for (int s = 0; s < NORM_RING; ++s) barrier_init(&control.norm_done[s], 1 + EPILOGUE_WARPS);
         for (int s = 0; s < ACC_STAGES; ++s) {
             barrier_init(&control.acc_full[s], 1);
-            barrier_init(&control.acc_empty[s], EPILOGUE_WARPS / 2);
+            barrier_init(&control.acc_empty[s], EPILOGUE_WARPS);
         }
         for (int s = 0; s < 2; ++s) {
-            barrier_init(&control.exchange_full[s], 12);
+            barrier_init(&control.exchange_full[s], 4 * (EPILOGUE_GROUPS - 1));
             barrier_init(&control.exchange_empty[s], 4);
         }
         for (int s = 0; s < 4; ++s) control.pair_count[s] = control.crowded_count[s] = 0;
@@ -337,10 +370,10 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 if (head != loaded_head) {
                     // the tensor core must have finished with the previous head's codes
                     if (code_loads > 0 && !barrier_wait(&control.code_empty, (code_loads - 1) & 1, control, 1)) break;
-                    barrier_expect(&control.code_full, uint32_t(code_tiles * KBLOCKS * BLOCK_BYTES));
+                    barrier_expect(&control.code_full, uint32_t(code_tiles * KBLOCKS * CODE_BLOCK_BYTES));
                     for (int j = 0; j < code_tiles; ++j)
                         for (int kb = 0; kb < KBLOCKS; ++kb)
-                            tma_load(codes + (j * KBLOCKS + kb) * BLOCK_BYTES, &code_map, kb * KBLOCK, head * vocab + j * TILE_CODES,
+                            tma_load(codes + (j * KBLOCKS + kb) * CODE_BLOCK_BYTES, &code_map, kb * KBLOCK, head * vocab + j * TILE_CODES,
                                      &control.code_full);
                     loaded_head = head;
                     ++code_loads;
@@ -359,6 +392,9 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
         }
     } else if (warp == MMA_WARP) {
         if (lane == 0) {
+            // This thread is the only feeder of the tensor core and shares its scheduler with busy warps:
+            // descriptors are built once, and a K step only adds its byte offset (in 16-byte units).
+            const uint64_t a_base = operand_descriptor(shared_address(a_ring)), b_base = operand_descriptor(shared_address(codes));
             int loaded_head = -1, code_uses = 0, step = 0, product = 0;
             bool ok = true;
             for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
@@ -371,19 +407,19 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 const int stage = step % A_STAGES;
                 if (!barrier_wait(&control.a_full[stage], (step / A_STAGES) & 1, control, 4)) break;
                 fence_after_sync();
-                const uint32_t a_address = shared_address(a_ring + stage * A_BYTES);
+                const uint64_t a_tile = a_base + uint64_t(stage * (A_BYTES >> 4));
                 for (int j = 0; j < code_tiles; ++j, ++product) {
                     const int slot = product % ACC_STAGES;
                     ok = barrier_wait(&control.acc_empty[slot], ((product / ACC_STAGES) & 1) ^ 1, control, 5);
                     if (!ok) break;
                     fence_after_sync();
-                    const uint32_t b_address = shared_address(codes + j * KBLOCKS * BLOCK_BYTES);
+                    const uint64_t b_tile = b_base + uint64_t(j * (KBLOCKS * CODE_BLOCK_BYTES >> 4));
 #pragma unroll
                     for (int kb = 0; kb < KBLOCKS; ++kb)
 #pragma unroll
                         for (int ks = 0; ks < KBLOCK / 16; ++ks)
-                            mma(tensor_memory + slot * TILE_CODES, operand_descriptor(a_address + kb * BLOCK_BYTES + ks * 32),
-                                operand_descriptor(b_address + kb * BLOCK_BYTES + ks * 32), (kb | ks) != 0);
+                            mma(tensor_memory + slot * TILE_CODES, a_tile + uint64_t((kb * BLOCK_BYTES + ks * 32) >> 4),
+                                b_tile + uint64_t((kb * CODE_BLOCK_BYTES + ks * 32) >> 4), (kb | ks) != 0);
                     mma_commit(&control.acc_full[slot]);
                 }
                 if (!ok) break;
@@ -395,71 +431,99 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
             barrier_settle(&control.drain, 0);
         }
     } else if (warp == NORM_WARP) {
-        int step = 0;
-        for (int tile = first_tile; tile < last_tile; ++tile, ++step) {
-            const int stage = step % A_STAGES;
-            if (!barrier_wait(&control.a_full[stage], (step / A_STAGES) & 1, control, 12)) break;
-#pragma unroll
-            for (int part = 0; part < TILE_ROWS / 32; ++part)
-                control.norm2[stage][part * 32 + lane] = shared_row_squares<D>(a_ring + stage * A_BYTES, part * 32 + lane, lane);
-            __syncwarp();
-            if (lane == 0) {
-                barrier_arrive(&control.norm_full[stage]);
-                barrier_arrive(&control.a_empty[stage]);
-            }
-        }
-    } else {
-        // Rows quarter*32 .. +31 of every tile; columns half*64 .. +63 of the accumulators whose running
-        // number has this warp's parity.
-        const int quarter = warp & 3, group = warp >> 2, half = group & 1, parity = group >> 1;
-        const int row_in_tile = quarter * 32 + lane;
-        const uint32_t lanes = tensor_memory + (uint32_t(quarter * 32) << 16) + half * (TILE_CODES / 2);
-        int loaded_head = -1, step = 0, product = 0, code_uses = 0;
+        int step = 0, loaded_head = -1, code_uses = 0;
         float code_max = 0.f;
-        bool ok = true;
-        for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
-            const int head = tile / tiles_per_head, row = (tile % tiles_per_head) * TILE_ROWS + row_in_tile;  // row in [B*N]
-            const int stage = step % A_STAGES;
-            if (head != loaded_head) {  // largest squared code norm of the head, per warp
-                ok = barrier_wait(&control.code_full, code_uses & 1, control, 11);
-                if (!ok) break;
+        for (int tile = first_tile; tile < last_tile; ++tile, ++step) {
+            const int stage = step % A_STAGES, head = tile / tiles_per_head;
+            if (head != loaded_head) {  // largest squared code norm of the head
+                if (!barrier_wait(&control.code_full, code_uses & 1, control, 11)) break;
                 ++code_uses;
                 code_max = 0.f;
                 for (int v = lane; v < vocab; v += 32)
-                    code_max = fmaxf(code_max, shared_row_squares<D>(codes + (v / TILE_CODES) * KBLOCKS * BLOCK_BYTES, v % TILE_CODES, lane));
+                    code_max = fmaxf(code_max, shared_row_squares<D, CODE_BLOCK_BYTES>(codes + (v / TILE_CODES) * KBLOCKS * CODE_BLOCK_BYTES, v % TILE_CODES, lane));
 #pragma unroll
                 for (int s = 16; s; s >>= 1) code_max = fmaxf(code_max, __shfl_xor_sync(FULL, code_max, s));
                 __syncwarp();
                 if (lane == 0) barrier_arrive(&control.code_empty);
                 loaded_head = head;
             }
-            ok = barrier_wait(&control.norm_full[stage], (step / A_STAGES) & 1, control, 10);
-            if (!ok) break;
-            const float norm2 = control.norm2[stage][row_in_tile];
+            // The landing of this step's tile paces this warp: by then every epilogue warp has read the slot's
+            // previous value.  The stage may not be refilled before this warp has seen the landing (a waiter
+            // that misses a whole phase of an mbarrier waits for the wrong one), hence the arrival below.
+            if (!barrier_wait(&control.a_full[stage], (step / A_STAGES) & 1, control, 12)) break;
+            if (lane == 0) {
+                barrier_arrive(&control.a_empty[stage]);
+                control.code_max[step % (2 * NORM_RING)] = code_max;
+                barrier_arrive(&control.norm_done[step % NORM_RING]);
+            }
+        }
+    } else {
+        // Rows quarter*32 .. +31 of every tile; columns group*64 .. +63 of every accumulator.
+        const int quarter = warp & 3, group = warp >> 2, row_in_tile = quarter * 32 + lane;
+        const uint32_t lanes = tensor_memory + (uint32_t(quarter * 32) << 16) + group * (TILE_CODES / EPILOGUE_GROUPS);
+        int step = 0, product = 0;
+        bool ok = true;
+        // Squared row norms of the tile of step t, shared by all epilogue threads: four threads per row,
+        // each sums a quarter of the row's 16-byte pieces (which ones does not matter, so the swizzle is
+        // ignored; the rotation by row keeps the warp's reads off each other's banks).
+        auto measure_rows = [&](int t) -> bool {
+            const int stage = t % A_STAGES;
+            if (!barrier_wait(&control.a_full[stage], (t / A_STAGES) & 1, control, 10)) return false;
+            const int r = (warp * 32 + lane) >> 2, part = lane & 3;
+            const unsigned char* tile_rows = a_ring + stage * A_BYTES + r * 128;
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int kb = 0; kb < KBLOCKS; ++kb) {
+                sum0 = squares(*reinterpret_cast<const uint4*>(tile_rows + kb * BLOCK_BYTES + ((part * 2 + r) & 7) * 16), sum0);
+                sum1 = squares(*reinterpret_cast<const uint4*>(tile_rows + kb * BLOCK_BYTES + ((part * 2 + 1 + r) & 7) * 16), sum1);
+            }
+            float sum = sum0 + sum1;
+            sum += __shfl_xor_sync(FULL, sum, 1);
+            sum += __shfl_xor_sync(FULL, sum, 2);
+            if (part == 0) control.norm2[t % NORM_RING][r] = sum;
             __syncwarp();
-            if (lane == 0) barrier_arrive(&control.a_empty[stage]);
+            if (lane == 0) {
+                barrier_arrive(&control.a_empty[stage]);
+                barrier_arrive(&control.norm_done[t % NORM_RING]);
+            }
+            return true;
+        };
+        if (first_tile < last_tile) ok = measure_rows(0);
+        for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
+            const int head = tile / tiles_per_head, row = (tile % tiles_per_head) * TILE_ROWS + row_in_tile;  // row in [B*N]
+            if (tile + 1 < last_tile) {
+                ok = measure_rows(step + 1);
+                if (!ok) break;
+            }
+            ok = barrier_wait(&control.norm_done[step % NORM_RING], (step / NORM_RING) & 1, control, 13);
+            if (!ok) break;
+            const float norm2 = control.norm2[step % NORM_RING][row_in_tile], code_max = control.code_max[step % (2 * NORM_RING)];
             // |tensor-core logit - exact| <= 4 D u sum|x e| (sixteen-term blocks whose addends may be truncated),
             // |pinned logit - exact| <= D u sum|x e|, u = 2^-24, and sum|x e| <= |x|_2 |e|_2.  Two logits
             // further apart than delta = 2 * 5 D u |x|_2 |e|_2 (with a little slack) keep their order.
             const float delta = 2.f * float(5 * D) * 5.9604645e-8f * sqrtf(norm2 * code_max) * 1.02f + 1e-37f;
             Candidates mine{-INFINITY, 0, 0, 0};
             for (int j = 0; j < code_tiles; ++j, ++product) {
-                if ((product & 1) != parity) continue;
                 const int slot = product % ACC_STAGES;
                 ok = barrier_wait(&control.acc_full[slot], (product / ACC_STAGES) & 1, control, 6);
                 if (!ok) break;
                 fence_after_sync();
-                const int column = j * TILE_CODES + half * (TILE_CODES / 2);
-                uint32_t r[32];
-                load_columns(r, lanes + slot * TILE_CODES);
+                const uint32_t address = lanes + slot * TILE_CODES;
+                float r[32];
+                load_columns(r, address);
                 wait_columns();
-                fold_chunk(mine, r, column, delta);
-                load_columns(r, lanes + slot * TILE_CODES + 32);
+                const float top0 = chunk_max(r), best0 = fmaxf(mine.first, top0);
+                const Threshold t0 = make_threshold(best0, delta);
+                const unsigned mask0 = t0.valid ? chunk_mask(r, t0.gain, t0.offset) : ~0u;
+                load_columns(r, address + 32);
                 wait_columns();
                 fence_before_sync();
                 __syncwarp();
                 if (lane == 0) barrier_arrive(&control.acc_empty[slot]);  // the logits are in registers
-                fold_chunk(mine, r, column + 32, delta);
+                const float top1 = chunk_max(r), best1 = fmaxf(best0, top1);
+                const Threshold t1 = make_threshold(best1, delta);
+                const unsigned mask1 = t1.valid ? chunk_mask(r, t1.gain, t1.offset) : ~0u;
+                fold_product(mine, top0, mask0, top1, mask1, best1, j * TILE_CODES + group * (TILE_CODES / EPILOGUE_GROUPS), delta);
             }
             if (!ok) break;
             const int side = step & 1;
@@ -473,15 +537,15 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
             }
             ok = barrier_wait(&control.exchange_full[side], (step >> 1) & 1, control, 8);
             if (!ok) break;
-            const Candidates theirs[3] = {control.exchange[side][0][row_in_tile], control.exchange[side][1][row_in_tile],
-                                          control.exchange[side][2][row_in_tile]};
+            const Candidates theirs[EPILOGUE_GROUPS - 1] = {control.exchange[side][0][row_in_tile], control.exchange[side][1][row_in_tile],
+                                                            control.exchange[side][2][row_in_tile]};
             __syncwarp();
             if (lane == 0) barrier_arrive(&control.exchange_empty[side]);
             const float best = fmaxf(fmaxf(mine.first, theirs[0].first), fmaxf(theirs[1].first, theirs[2].first));
             Candidates all{best, 0, 0, 0};
             merge_candidates(all, mine, best, delta);
 #pragma unroll
-            for (int g = 0; g < 3; ++g) merge_candidates(all, theirs[g], best, delta);
+            for (int g = 0; g < EPILOGUE_GROUPS - 1; ++g) merge_candidates(all, theirs[g], best, delta);
             const int64_t out = (int64_t(row / n) * heads + head) * n + row % n;
             if (all.count == 1) labels[out] = all.a;
             const int id = tile * TILE_ROWS + row_in_tile;
@@ -518,7 +582,7 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 }
             }
         }
-        // The lists: near ties one thread per row, crowded rows one warp per row, all sixteen warps.
+        // The lists: near ties one thread per row, crowded rows one warp per row, all epilogue warps.
         if (ok && group == 0) {
             __syncwarp();
             if (lane == 0) barrier_arrive(&control.list_ready);
@@ -575,12 +639,12 @@ EncodeTiled encode_tiled() {
     return entry;
 }
 
-// bf16 matrix [rows, columns] (row stride in elements) read in boxes of 64 columns by 128 rows, 128-byte swizzle
-bool make_map(CUtensorMap* map, const void* data, uint64_t rows, uint64_t columns, uint64_t row_stride) {
+// bf16 matrix [rows, columns] (row stride in elements) read in boxes of 64 columns by box_rows rows, 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* data, uint64_t rows, uint64_t columns, uint64_t row_stride, int box_rows) {
     const EncodeTiled encode = encode_tiled();
     if (!encode) return false;
     const cuuint64_t dims[2] = {columns, rows}, strides[1] = {row_stride * 2};
-    const cuuint32_t box[2] = {KBLOCK, TILE_ROWS}, element_strides[2] = {1, 1};
+    const cuuint32_t box[2] = {KBLOCK, cuuint32_t(box_rows)}, element_strides[2] = {1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(data), dims, strides, box, element_strides,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -608,8 +672,8 @@ bool labels_tcgen05_covers(const void* x, const void* codebook, int batch, int n
 cudaError_t launch_labels_tcgen05(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int batch, int n, int heads, int d,
                                   int vocab, int* labels, cudaStream_t stream) {
     CUtensorMap x_map, code_map;
-    if (!make_map(&x_map, x, uint64_t(batch) * n, uint64_t(heads) * d, uint64_t(heads) * d) ||
-        !make_map(&code_map, codebook, uint64_t(heads) * vocab, uint64_t(d), uint64_t(d)))
+    if (!make_map(&x_map, x, uint64_t(batch) * n, uint64_t(heads) * d, uint64_t(heads) * d, TILE_ROWS) ||
+        !make_map(&code_map, codebook, uint64_t(heads) * vocab, uint64_t(d), uint64_t(d), TILE_CODES))
         return cudaErrorInvalidValue;
     const int tiles_per_head = int(int64_t(batch) * n / TILE_ROWS), total_tiles = tiles_per_head * heads;
     KernelTimer timer("labels", stream);
