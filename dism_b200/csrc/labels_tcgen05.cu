@@ -10,6 +10,8 @@
 //   MMA warp        one thread issues tcgen05.mma (M=128, N=256, K=16) for each 256-code slice of the
 //                   codebook into one of two FP32 accumulators: all of tensor memory;
 //   norm warp       squared norms of the tile's rows (the margin below scales with them);
+//   two finishing   put the column ranges of a row together: label, pair list or crowded list;
+//   warps
 //   sixteen         read the accumulators with tcgen05.ld (row = tensor-memory lane = thread; a warp
 //   epilogue warps  owns 32 rows and a quarter of the columns of every accumulator) and keep, per row,
 //                   the largest logit and the columns of all logits within a safety margin of it.
@@ -44,8 +46,9 @@ constexpr int CODE_BLOCK_BYTES = TILE_CODES * 128;  // 256 codes, 64 elements ea
 constexpr int ACC_STAGES = 2;    // two accumulators: all 512 columns of tensor memory
 constexpr int MAX_A_STAGES = 4;
 constexpr int NORM_RING = 4;     // norms are prepared one tile ahead; warps are never more than one tile apart
-constexpr int EPILOGUE_WARPS = 16, EPILOGUE_GROUPS = 4, PRODUCER_WARP = 16, MMA_WARP = 17, NORM_WARP = 18, THREADS = 19 * 32;
-constexpr int LIST_CAPACITY = 256;  // per finishing warp and list
+constexpr int EPILOGUE_WARPS = 16, EPILOGUE_GROUPS = 4, PRODUCER_WARP = 16, MMA_WARP = 17, NORM_WARP = 18;
+constexpr int FINISH_WARP = 19, FINISH_WARPS = 2, THREADS = (FINISH_WARP + FINISH_WARPS) * 32;
+constexpr int LIST_CAPACITY = 128;  // per quarter of the rows and list
 constexpr unsigned WAIT_LIMIT = 1u << 16, SETTLE_LIMIT = 1u << 14, PARK_NANOSECONDS = 20000;  // a wait gives up after about a second at most
 constexpr int MAX_CODE_BYTES = 128 * 1024;
 
@@ -60,7 +63,7 @@ struct Control {
     uint64_t a_full[MAX_A_STAGES], a_empty[MAX_A_STAGES], norm_done[NORM_RING];
     uint64_t acc_full[ACC_STAGES], acc_empty[ACC_STAGES];
     uint64_t exchange_full[2], exchange_empty[2];
-    Candidates exchange[2][EPILOGUE_GROUPS - 1][TILE_ROWS];
+    Candidates exchange[2][EPILOGUE_GROUPS][TILE_ROWS];
     float norm2[NORM_RING][TILE_ROWS];  // squared row norms of the tile of a step, ring over steps
     float code_max[2 * NORM_RING];      // largest squared code norm of that tile's head; the norm warp may be five steps ahead
     int pairs[4][LIST_CAPACITY][3];  // near ties: row id and the two columns
@@ -109,6 +112,23 @@ __device__ __noinline__ bool barrier_wait_slow(uint64_t* bar, uint32_t parity, C
 }
 __device__ __forceinline__ bool barrier_wait(uint64_t* bar, uint32_t parity, Control& control, int code) {
     return barrier_test(bar, parity) || barrier_wait_slow(bar, parity, control, code);
+}
+// The same for the warp that feeds the tensor core: it is on the critical path of every accumulator and
+// polls without sleeping.
+__device__ __noinline__ bool barrier_wait_eager(uint64_t* bar, uint32_t parity, Control& control, int code) {
+    for (unsigned tries = 0; tries < WAIT_LIMIT * 64; ++tries) {
+        if (barrier_test(bar, parity)) return true;
+        if ((tries & 255) == 255 && *reinterpret_cast<volatile int*>(&control.abort)) return false;
+    }
+    *reinterpret_cast<volatile int*>(&control.abort) = 1;
+    atomicCAS(&labels_fault_code, 0, code);
+    return false;
+}
+// One lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t elected;
+    asm volatile("{.reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p;}" : "=r"(elected));
+    return elected != 0;
 }
 // After a fault: give copies or products in flight a bounded time to land before the CTA leaves.
 __device__ __noinline__ void barrier_settle(uint64_t* bar, uint32_t parity) {
@@ -218,6 +238,14 @@ __device__ __forceinline__ void fold_product(Candidates& row, float top0, unsign
     row.a = (inside >= 1 && kept == 0) ? lowest : row.a;
     row.count = min(kept + inside, 3);
     row.first = best;
+}
+
+// |tensor-core logit - exact| <= 4 D u sum|x e| (sixteen-term blocks whose addends may be truncated),
+// |pinned logit - exact| <= D u sum|x e|, u = 2^-24, and sum|x e| <= |x|_2 |e|_2.  Two logits
+// further apart than delta = 2 * 5 D u |x|_2 |e|_2 (with a little slack) keep their order.
+template <int D>
+__device__ __forceinline__ float margin(float row_norm2, float code_norm2) {
+    return 2.f * float(5 * D) * 5.9604645e-8f * sqrtf(row_norm2 * code_norm2) * 1.02f + 1e-37f;
 }
 
 // Adds the candidates of another column range of the same row.
@@ -333,7 +361,7 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
         barrier_init(&control.code_full, 1);
         barrier_init(&control.code_empty, 2);  // the tensor core and the norm warp
         barrier_init(&control.drain, 1);
-        barrier_init(&control.list_ready, 4);
+        barrier_init(&control.list_ready, FINISH_WARPS);
         for (int s = 0; s < A_STAGES; ++s) {
             barrier_init(&control.a_full[s], 1);
             barrier_init(&control.a_empty[s], 2 + EPILOGUE_WARPS);  // tensor core, norm warp, the warps that measure the rows
@@ -344,8 +372,8 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
             barrier_init(&control.acc_empty[s], EPILOGUE_WARPS);
         }
         for (int s = 0; s < 2; ++s) {
-            barrier_init(&control.exchange_full[s], 4 * (EPILOGUE_GROUPS - 1));
-            barrier_init(&control.exchange_empty[s], 4);
+            barrier_init(&control.exchange_full[s], EPILOGUE_WARPS);
+            barrier_init(&control.exchange_empty[s], FINISH_WARPS);
         }
         for (int s = 0; s < 4; ++s) control.pair_count[s] = control.crowded_count[s] = 0;
         control.abort = 0;
@@ -391,29 +419,32 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
             }
         }
     } else if (warp == MMA_WARP) {
-        if (lane == 0) {
-            // This thread is the only feeder of the tensor core and shares its scheduler with busy warps:
-            // descriptors are built once, and a K step only adds its byte offset (in 16-byte units).
-            const uint64_t a_base = operand_descriptor(shared_address(a_ring)), b_base = operand_descriptor(shared_address(codes));
-            int loaded_head = -1, code_uses = 0, step = 0, product = 0;
-            bool ok = true;
-            for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
-                const int head = tile / tiles_per_head;
-                if (head != loaded_head) {
-                    if (!barrier_wait(&control.code_full, code_uses & 1, control, 3)) break;
-                    ++code_uses;
-                    loaded_head = head;
-                }
-                const int stage = step % A_STAGES;
-                if (!barrier_wait(&control.a_full[stage], (step / A_STAGES) & 1, control, 4)) break;
+        // The whole warp walks the loop, so that addresses and descriptors live in uniform registers; one
+        // elected lane issues the products and their commits.  Descriptors are built once, and a K step
+        // only adds its byte offset (in 16-byte units).
+        const uint64_t a_base = operand_descriptor(shared_address(a_ring)), b_base = operand_descriptor(shared_address(codes));
+        int head = first_tile / tiles_per_head, tile_in_head = first_tile % tiles_per_head;
+        int loaded_head = -1, code_uses = 0, step = 0, product = 0;
+        bool ok = true;
+        for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
+            if (head != loaded_head) {
+                ok = __all_sync(FULL, barrier_wait_eager(&control.code_full, code_uses & 1, control, 3));
+                if (!ok) break;
+                ++code_uses;
+                loaded_head = head;
+            }
+            const int stage = step % A_STAGES;
+            ok = __all_sync(FULL, barrier_wait_eager(&control.a_full[stage], (step / A_STAGES) & 1, control, 4));
+            if (!ok) break;
+            fence_after_sync();
+            const uint64_t a_tile = a_base + uint64_t(stage * (A_BYTES >> 4));
+            for (int j = 0; j < code_tiles; ++j, ++product) {
+                const int slot = product % ACC_STAGES;
+                ok = __all_sync(FULL, barrier_wait_eager(&control.acc_empty[slot], ((product / ACC_STAGES) & 1) ^ 1, control, 5));
+                if (!ok) break;
                 fence_after_sync();
-                const uint64_t a_tile = a_base + uint64_t(stage * (A_BYTES >> 4));
-                for (int j = 0; j < code_tiles; ++j, ++product) {
-                    const int slot = product % ACC_STAGES;
-                    ok = barrier_wait(&control.acc_empty[slot], ((product / ACC_STAGES) & 1) ^ 1, control, 5);
-                    if (!ok) break;
-                    fence_after_sync();
-                    const uint64_t b_tile = b_base + uint64_t(j * (KBLOCKS * CODE_BLOCK_BYTES >> 4));
+                const uint64_t b_tile = b_base + uint64_t(j * (KBLOCKS * CODE_BLOCK_BYTES >> 4));
+                if (elect_one()) {
 #pragma unroll
                     for (int kb = 0; kb < KBLOCKS; ++kb)
 #pragma unroll
@@ -422,14 +453,21 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                                 b_tile + uint64_t((kb * CODE_BLOCK_BYTES + ks * 32) >> 4), (kb | ks) != 0);
                     mma_commit(&control.acc_full[slot]);
                 }
-                if (!ok) break;
-                mma_commit(&control.a_empty[stage]);
-                if (tile + 1 < last_tile && (tile + 1) / tiles_per_head != head) mma_commit(&control.code_empty);
+                __syncwarp();
             }
-            // every product issued above has completed once this commit arrives
-            mma_commit(&control.drain);
-            barrier_settle(&control.drain, 0);
+            if (!ok) break;
+            const bool last_of_head = tile_in_head + 1 == tiles_per_head;
+            if (elect_one()) {
+                mma_commit(&control.a_empty[stage]);
+                if (tile + 1 < last_tile && last_of_head) mma_commit(&control.code_empty);
+            }
+            __syncwarp();
+            if (last_of_head) { tile_in_head = 0; ++head; } else ++tile_in_head;
         }
+        // every product issued above has completed once this commit arrives
+        if (elect_one()) mma_commit(&control.drain);
+        __syncwarp();
+        barrier_settle(&control.drain, 0);
     } else if (warp == NORM_WARP) {
         int step = 0, loaded_head = -1, code_uses = 0;
         float code_max = 0.f;
@@ -456,6 +494,76 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 control.code_max[step % (2 * NORM_RING)] = code_max;
                 barrier_arrive(&control.norm_done[step % NORM_RING]);
             }
+        }
+    } else if (warp >= FINISH_WARP) {
+        // Two warps put the four column ranges of a row together, off the path that paces the accumulators:
+        // one column in reach is the label; two go to the pair list; more, or no valid threshold, to the
+        // crowded list.  Each warp owns two quarters of the rows and their lists.
+        const int tiles_per_batch = n / TILE_ROWS;
+        int head = first_tile / tiles_per_head, tile_in_batch = first_tile % tiles_per_head % tiles_per_batch;
+        int batch = first_tile % tiles_per_head / tiles_per_batch, step = 0;
+        bool ok = true;
+        for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
+            const int side = step & 1;
+            ok = barrier_wait(&control.exchange_full[side], (step >> 1) & 1, control, 8);
+            if (!ok) break;
+            const float code_max = control.code_max[step % (2 * NORM_RING)];
+            const __nv_bfloat16* head_codes = codebook + int64_t(head) * vocab * D;
+#pragma unroll 1
+            for (int quarter = (warp - FINISH_WARP) * 2; quarter < (warp - FINISH_WARP) * 2 + 2; ++quarter) {
+                const int row_in_tile = quarter * 32 + lane, position = tile_in_batch * TILE_ROWS + row_in_tile;
+                const float delta = margin<D>(control.norm2[step % NORM_RING][row_in_tile], code_max);
+                const Candidates part[EPILOGUE_GROUPS] = {control.exchange[side][0][row_in_tile], control.exchange[side][1][row_in_tile],
+                                                          control.exchange[side][2][row_in_tile], control.exchange[side][3][row_in_tile]};
+                const float best = fmaxf(fmaxf(part[0].first, part[1].first), fmaxf(part[2].first, part[3].first));
+                Candidates all{best, 0, 0, 0};
+#pragma unroll
+                for (int g = 0; g < EPILOGUE_GROUPS; ++g) merge_candidates(all, part[g], best, delta);
+                if (all.count == 1) labels[(int64_t(batch) * heads + head) * n + position] = all.a;
+                const int id = tile * TILE_ROWS + row_in_tile;
+                // near ties go to the pair list while it has room, everything else to the crowded list
+                unsigned pair_mask = __ballot_sync(FULL, all.count == 2);
+                if (pair_mask) {
+                    const int count = control.pair_count[quarter], more = __popc(pair_mask);
+                    if (count + more <= LIST_CAPACITY) {
+                        if (all.count == 2) {
+                            int* entry = control.pairs[quarter][count + __popc(pair_mask & ((1u << lane) - 1))];
+                            entry[0] = id, entry[1] = all.a, entry[2] = all.b;
+                        }
+                        __syncwarp();
+                        if (lane == 0) control.pair_count[quarter] = count + more;
+                        __syncwarp();
+                        pair_mask = 0;
+                    }
+                }
+                const bool crowded = all.count != 1 && (all.count != 2 || pair_mask != 0);
+                const unsigned crowded_mask = __ballot_sync(FULL, crowded);
+                if (crowded_mask) {
+                    const int count = control.crowded_count[quarter], more = __popc(crowded_mask);
+                    if (count + more <= LIST_CAPACITY) {
+                        if (crowded) control.crowded[quarter][count + __popc(crowded_mask & ((1u << lane) - 1))] = id;
+                        __syncwarp();
+                        if (lane == 0) control.crowded_count[quarter] = count + more;
+                        __syncwarp();
+                    } else {  // list full: recompute here
+                        for (unsigned rest = crowded_mask; rest; rest &= rest - 1) {
+                            const int p = tile_in_batch * TILE_ROWS + quarter * 32 + __ffs(rest) - 1;
+                            const int label = pinned_label<D>(x + ((int64_t(batch) * n + p) * heads + head) * D, head_codes, vocab, lane);
+                            if (lane == 0) labels[(int64_t(batch) * heads + head) * n + p] = label;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) barrier_arrive(&control.exchange_empty[side]);
+            if (++tile_in_batch == tiles_per_batch) {
+                tile_in_batch = 0;
+                if (++batch == tiles_per_head / tiles_per_batch) { batch = 0; ++head; }
+            }
+        }
+        if (ok) {
+            __syncwarp();
+            if (lane == 0) barrier_arrive(&control.list_ready);
         }
     } else {
         // Rows quarter*32 .. +31 of every tile; columns group*64 .. +63 of every accumulator.
@@ -490,7 +598,6 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
         };
         if (first_tile < last_tile) ok = measure_rows(0);
         for (int tile = first_tile; tile < last_tile && ok; ++tile, ++step) {
-            const int head = tile / tiles_per_head, row = (tile % tiles_per_head) * TILE_ROWS + row_in_tile;  // row in [B*N]
             if (tile + 1 < last_tile) {
                 ok = measure_rows(step + 1);
                 if (!ok) break;
@@ -498,10 +605,7 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
             ok = barrier_wait(&control.norm_done[step % NORM_RING], (step / NORM_RING) & 1, control, 13);
             if (!ok) break;
             const float norm2 = control.norm2[step % NORM_RING][row_in_tile], code_max = control.code_max[step % (2 * NORM_RING)];
-            // |tensor-core logit - exact| <= 4 D u sum|x e| (sixteen-term blocks whose addends may be truncated),
-            // |pinned logit - exact| <= D u sum|x e|, u = 2^-24, and sum|x e| <= |x|_2 |e|_2.  Two logits
-            // further apart than delta = 2 * 5 D u |x|_2 |e|_2 (with a little slack) keep their order.
-            const float delta = 2.f * float(5 * D) * 5.9604645e-8f * sqrtf(norm2 * code_max) * 1.02f + 1e-37f;
+            const float delta = margin<D>(norm2, code_max);
             Candidates mine{-INFINITY, 0, 0, 0};
             for (int j = 0; j < code_tiles; ++j, ++product) {
                 const int slot = product % ACC_STAGES;
@@ -527,66 +631,13 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
             }
             if (!ok) break;
             const int side = step & 1;
-            if (group != 0) {
-                ok = barrier_wait(&control.exchange_empty[side], ((step >> 1) & 1) ^ 1, control, 7);
-                if (!ok) break;
-                control.exchange[side][group - 1][row_in_tile] = mine;
-                __syncwarp();
-                if (lane == 0) barrier_arrive(&control.exchange_full[side]);
-                continue;
-            }
-            ok = barrier_wait(&control.exchange_full[side], (step >> 1) & 1, control, 8);
+            ok = barrier_wait(&control.exchange_empty[side], ((step >> 1) & 1) ^ 1, control, 7);
             if (!ok) break;
-            const Candidates theirs[EPILOGUE_GROUPS - 1] = {control.exchange[side][0][row_in_tile], control.exchange[side][1][row_in_tile],
-                                                            control.exchange[side][2][row_in_tile]};
+            control.exchange[side][group][row_in_tile] = mine;
             __syncwarp();
-            if (lane == 0) barrier_arrive(&control.exchange_empty[side]);
-            const float best = fmaxf(fmaxf(mine.first, theirs[0].first), fmaxf(theirs[1].first, theirs[2].first));
-            Candidates all{best, 0, 0, 0};
-            merge_candidates(all, mine, best, delta);
-#pragma unroll
-            for (int g = 0; g < EPILOGUE_GROUPS - 1; ++g) merge_candidates(all, theirs[g], best, delta);
-            const int64_t out = (int64_t(row / n) * heads + head) * n + row % n;
-            if (all.count == 1) labels[out] = all.a;
-            const int id = tile * TILE_ROWS + row_in_tile;
-            // near ties go to the pair list while it has room, everything else to the crowded list
-            unsigned pair_mask = __ballot_sync(FULL, all.count == 2);
-            if (pair_mask) {
-                const int count = control.pair_count[quarter], more = __popc(pair_mask);
-                if (count + more <= LIST_CAPACITY) {
-                    if (all.count == 2) {
-                        int* entry = control.pairs[quarter][count + __popc(pair_mask & ((1u << lane) - 1))];
-                        entry[0] = id, entry[1] = all.a, entry[2] = all.b;
-                    }
-                    __syncwarp();
-                    if (lane == 0) control.pair_count[quarter] = count + more;
-                    __syncwarp();
-                    pair_mask = 0;
-                }
-            }
-            const bool crowded = all.count != 1 && (all.count != 2 || pair_mask != 0);
-            const unsigned crowded_mask = __ballot_sync(FULL, crowded);
-            if (crowded_mask) {
-                const int count = control.crowded_count[quarter], more = __popc(crowded_mask);
-                if (count + more <= LIST_CAPACITY) {
-                    if (crowded) control.crowded[quarter][count + __popc(crowded_mask & ((1u << lane) - 1))] = id;
-                    __syncwarp();
-                    if (lane == 0) control.crowded_count[quarter] = count + more;
-                    __syncwarp();
-                } else {  // list full: recompute here
-                    for (unsigned rest = crowded_mask; rest; rest &= rest - 1) {
-                        const int r = (tile % tiles_per_head) * TILE_ROWS + quarter * 32 + __ffs(rest) - 1;
-                        const int label = pinned_label<D>(x + (int64_t(r) * heads + head) * D, codebook + int64_t(head) * vocab * D, vocab, lane);
-                        if (lane == 0) labels[(int64_t(r / n) * heads + head) * n + r % n] = label;
-                    }
-                }
-            }
+            if (lane == 0) barrier_arrive(&control.exchange_full[side]);
         }
         // The lists: near ties one thread per row, crowded rows one warp per row, all epilogue warps.
-        if (ok && group == 0) {
-            __syncwarp();
-            if (lane == 0) barrier_arrive(&control.list_ready);
-        }
         if (ok && barrier_wait(&control.list_ready, 0, control, 9)) {
             for (int list = 0; list < 4; ++list) {
                 const int count = *reinterpret_cast<volatile int*>(&control.pair_count[list]);
@@ -650,10 +701,14 @@ bool make_map(CUtensorMap* map, const void* data, uint64_t rows, uint64_t column
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Dynamic shared memory of a CTA: the codebook, the ring of row tiles, the control block, alignment slack.
+int shared_bytes(int d, int vocab) { return vocab * d * 2 + (d == 64 ? 4 : 2) * (d / KBLOCK) * BLOCK_BYTES + int(sizeof(Control)) + 1024; }
+constexpr int SHARED_LIMIT = 227 * 1024;
+
 template <int D>
 cudaError_t launch(const CUtensorMap& x_map, const CUtensorMap& code_map, const __nv_bfloat16* x, const __nv_bfloat16* codebook,
                    int n, int heads, int vocab, int tiles_per_head, int total_tiles, int* labels, cudaStream_t stream) {
-    const int bytes = vocab * D * 2 + (D == 64 ? 4 : 2) * (D / KBLOCK) * BLOCK_BYTES + int(sizeof(Control)) + 1024;
+    const int bytes = shared_bytes(D, vocab);
     const cudaError_t status = cudaFuncSetAttribute(labels_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (status != cudaSuccess) return status;
     const int grid = total_tiles < device_sm_count() ? total_tiles : device_sm_count();
@@ -664,7 +719,7 @@ cudaError_t launch(const CUtensorMap& x_map, const CUtensorMap& code_map, const 
 }  // namespace
 
 bool labels_tcgen05_covers(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab) {
-    return (d == 64 || d == 128) && vocab % TILE_CODES == 0 && int64_t(vocab) * d * 2 <= MAX_CODE_BYTES && n % TILE_ROWS == 0 &&
+    return (d == 64 || d == 128) && vocab % TILE_CODES == 0 && int64_t(vocab) * d * 2 <= MAX_CODE_BYTES && shared_bytes(d, vocab) <= SHARED_LIMIT && n % TILE_ROWS == 0 &&
            int64_t(batch) * n * heads < (int64_t(1) << 31) && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
            reinterpret_cast<uintptr_t>(codebook) % 16 == 0 && encode_tiled() != nullptr;
 }
