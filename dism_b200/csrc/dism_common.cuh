@@ -259,6 +259,9 @@ size_t index_bytes(int batch_heads, int n, int sides);
 // Builds the index of `labels` ([BH, N]) into `workspace` (side 0 at the front, side 1 after it).
 cudaError_t launch_build_index(const int* labels, int batch_heads, int n, void* workspace, int side, int sides,
                                cudaStream_t stream);
+// Both sides of a readout (labels0 -> side 0, labels1 -> side 1) in one launch.
+cudaError_t launch_build_index_pair(const int* labels0, const int* labels1, int batch_heads, int n, void* workspace,
+                                    cudaStream_t stream);
 SideIndex side_index(void* workspace, int batch_heads, int n, int side, int sides);
 
 size_t longest_match_workspace_bytes(int batch, int n);

@@ -87,9 +87,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
                                  __nv_bfloat16* dsk, __nv_bfloat16* dv, float* dtau, void* workspace,
                                  cudaStream_t stream) {
     const int batch_heads = shape.batch * shape.heads;
-    cudaError_t status = launch_build_index(ik, batch_heads, shape.n, workspace, 0, 2, stream);
-    if (status != cudaSuccess) return status;
-    status = launch_build_index(iq, batch_heads, shape.n, workspace, 1, 2, stream);
+    cudaError_t status = launch_build_index_pair(ik, iq, batch_heads, shape.n, workspace, stream);
     if (status != cudaSuccess) return status;
     const SideIndex keys = side_index(workspace, batch_heads, shape.n, 0, 2), queries = side_index(workspace, batch_heads, shape.n, 1, 2);
     char* cursor = static_cast<char*>(workspace) + index_bytes(batch_heads, shape.n, 2);

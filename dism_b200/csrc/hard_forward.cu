@@ -70,9 +70,7 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
                                 int lut_stride, int ctas, __nv_bfloat16* out, float* lse2, void* workspace,
                                 cudaStream_t stream) {
     const int batch_heads = shape.batch * shape.heads;
-    cudaError_t status = launch_build_index(ik, batch_heads, shape.n, workspace, 0, 2, stream);
-    if (status != cudaSuccess) return status;
-    status = launch_build_index(iq, batch_heads, shape.n, workspace, 1, 2, stream);
+    cudaError_t status = launch_build_index_pair(ik, iq, batch_heads, shape.n, workspace, stream);
     if (status != cudaSuccess) return status;
     BlockArgs args{};
     args.sq = sq; args.sk = sk; args.v = v;

@@ -72,11 +72,21 @@ __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, co
     }
 }
 
-__global__ __launch_bounds__(INDEX_THREADS) void build_index_kernel(const int* __restrict__ labels, int n,
-                                                                    int2* __restrict__ entries,
-                                                                    int2* __restrict__ scratch,
-                                                                    int* __restrict__ previous,
-                                                                    int* __restrict__ starts) {
+// Where one side's index goes, and the labels it is built from.
+struct IndexSide {
+    const int* labels;
+    int2 *entries, *scratch;
+    int *previous, *starts;
+};
+
+// blockIdx.y picks the side: both sides of a readout are built by one launch, two CTAs to an SM.
+__global__ __launch_bounds__(INDEX_THREADS, 2) void build_index_kernel(const IndexSide side0, const IndexSide side1, int n) {
+    const IndexSide& side = blockIdx.y ? side1 : side0;
+    const int* __restrict__ labels = side.labels;
+    int2* __restrict__ entries = side.entries;
+    int2* __restrict__ scratch = side.scratch;
+    int* __restrict__ previous = side.previous;
+    int* __restrict__ starts = side.starts;
     __shared__ int base[PASS_BINS], total[PASS_BINS];
     __shared__ unsigned short counts[INDEX_THREADS / 32][PASS_BINS];
     __shared__ int histogram[BUCKETS];
@@ -143,14 +153,25 @@ SideIndex side_index(void* workspace, int batch_heads, int n, int side, int side
                      reinterpret_cast<const int*>(p + items * 2 * sizeof(int2))};
 }
 
+static IndexSide index_side(const int* labels, void* workspace, int batch_heads, int n, int side, int sides) {
+    const SideIndex index = side_index(workspace, batch_heads, n, side, sides);
+    int2* entries = const_cast<int2*>(index.entries);
+    return IndexSide{labels, entries, entries + size_t(batch_heads) * n, const_cast<int*>(index.previous), const_cast<int*>(index.starts)};
+}
+
 cudaError_t launch_build_index(const int* labels, int batch_heads, int n, void* workspace, int side, int sides,
                                cudaStream_t stream) {
-    SideIndex index = side_index(workspace, batch_heads, n, side, sides);
-    int2* entries = const_cast<int2*>(index.entries);
+    const IndexSide target = index_side(labels, workspace, batch_heads, n, side, sides);
     KernelTimer timer("build_index", stream);
-    build_index_kernel<<<batch_heads, INDEX_THREADS, 0, stream>>>(labels, n, entries, entries + size_t(batch_heads) * n,
-                                                                  const_cast<int*>(index.previous),
-                                                                  const_cast<int*>(index.starts));
+    build_index_kernel<<<dim3(batch_heads, 1), INDEX_THREADS, 0, stream>>>(target, target, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_build_index_pair(const int* labels0, const int* labels1, int batch_heads, int n, void* workspace,
+                                    cudaStream_t stream) {
+    KernelTimer timer("build_index", stream);
+    build_index_kernel<<<dim3(batch_heads, 2), INDEX_THREADS, 0, stream>>>(index_side(labels0, workspace, batch_heads, n, 0, 2),
+                                                                             index_side(labels1, workspace, batch_heads, n, 1, 2), n);
     return cudaGetLastError();
 }
 
