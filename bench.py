@@ -36,8 +36,10 @@ KERNEL_BYTES = {
     'hard_backward_key': 588,    # the same reads; dsk 64, dv 128 written
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at the full shape, from the ncu captures
-# summarised under profiles/ (captured at batch 2 and scaled by 4: traffic grows with the rows).
-TRAFFIC = {'labels': 138.5e6, 'hard_forward': 301e6, 'hard_backward_query': 466e6, 'hard_backward_key': 494e6}
+# summarised under profiles/ (captured at batch 2 and scaled by 4: traffic grows with the rows).  At
+# batch 2 part of the outputs stays in the 126 MB L2, which is why three of the figures are below the
+# algorithmic bytes.
+TRAFFIC = {'labels': 138.7e6, 'hard_forward': 338.7e6, 'hard_backward_query': 529.0e6, 'hard_backward_key': 535.5e6}
 STEP_BYTES = 2 * 132 + 396 + 716  # whole path: two label launches, forward, backward (inputs counted once)
 
 
@@ -137,7 +139,9 @@ def run_ours(args):
         grads = backward_hard(x['sq'], x['sk'], x['v'], x['dout'], iq, ik, params['hard'], norm,
                               dict(boundary=None, log_weights=lut))
         mark()
-        launches[0] += 2 + 2 + 1 + 4  # labels x2, (lut, forward), lut, (dlut, query, key, tau)
+        # labels x2; readout: log weights, index, tiles, forward; log weights; backward: their derivative,
+        # index, tiles x2, query-major, key-major, tau reduction
+        launches[0] += 2 + 4 + 1 + 7
         return out, norm, grads
 
     def _event():

@@ -150,26 +150,54 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
     const float weight_one = __ldg(lut + 1);
 
     // Tiles differ a lot in their number of key steps, so warps take them one at a time from a counter.
-    for (;;) {
-        int tile = 0;
-        if (lane == 0) tile = atomicAdd(a.next_tile + bh, 1);
-        tile = __shfl_sync(FULL, tile, 0);
-        if (tile >= tile_count) break;
-        const int4 plan = __ldg(tiles + tile);
+    // Getting to a tile's rows takes a chain of dependent reads (counter, descriptor, index entries), so the
+    // chain runs ahead of the arithmetic: while tile i is worked on, the index entries of tile i+1, the
+    // descriptor of tile i+2 and the number of tile i+3 are in flight.  A warp may claim up to three
+    // numbers past the end; they are ignored.
+    const int fixed_active = a.documents ? 0 : a.hard[b * a.heads + h];
+    auto claim = [&]() { return lane == 0 ? atomicAdd(a.next_tile + bh, 1) : 0; };  // lane 0 holds the number
+    auto descriptor = [&](int tile) { return tile < tile_count ? __ldg(tiles + tile) : make_int4(0, 0, 0, 0); };
+    struct Entries {
+        int2 owner, key;  // lane r < QT: query r of the tile; lane c < KT: key c of the first key step
+        int owner_previous, key_previous;
+    };
+    auto entries_of = [&](const int4 plan) {
+        Entries e{make_int2(-1, 0), make_int2(0x7fffffff, 0), 0, 0};
+        if (lane < plan.y) {
+            e.owner = __ldg(query_entries + plan.x + lane);
+            e.owner_previous = __ldg(query_previous + plan.x + lane);
+        }
+        if (lane < KT && plan.z + lane < plan.w) {
+            e.key = __ldg(key_entries + plan.z + lane);
+            e.key_previous = __ldg(key_previous + plan.z + lane);
+        }
+        return e;
+    };
+    int tile = __shfl_sync(FULL, claim(), 0);
+    int claimed = claim();
+    int4 plan = descriptor(tile);
+    int next_tile = __shfl_sync(FULL, claimed, 0);
+    claimed = claim();
+    int4 next_plan = descriptor(next_tile);
+    Entries fetched = entries_of(plan);
+    for (; tile < tile_count; ) {
+        const int after_next = __shfl_sync(FULL, claimed, 0);
+        claimed = claim();
+        const int4 after_next_plan = descriptor(after_next);
+        const Entries next_fetched = entries_of(next_plan);
         const int q0 = plan.x, queries = plan.y;
+        (void)q0;
         __syncwarp();
         if (lane < QT) {
-            int2 entry = make_int2(-1, 0);
-            int previous = 0, begin = 0, active = 0;
+            const int2 entry = fetched.owner;
+            const int previous = fetched.owner_previous;
+            int begin = 0, active = 0;
             if (lane < queries) {
-                entry = __ldg(query_entries + q0 + lane);
-                previous = __ldg(query_previous + q0 + lane);
-                int hard_row = b;
+                active = fixed_active;
                 if (a.documents) {
                     begin = __ldg(a.documents + entry.x / 256).x;
-                    hard_row = entry.x / (a.n / a.hard_rows);
+                    active = a.hard[entry.x / (a.n / a.hard_rows) * a.heads + h];
                 }
-                active = a.hard[hard_row * a.heads + h];
             }
             mine.position[lane] = entry.x;
             mine.label[lane] = entry.y;
@@ -220,16 +248,9 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
             return pair ? (longer ? 2 : 1) : 0;
         };
         // Labels of a key step and its sk / v rows (cp.async); rows beyond the range are zero-filled.
-        auto stage_keys = [&](KeyStage<R, DV>& keys, int k0) {
-            int key_position = 0x7fffffff;
+        auto stage_entries = [&](KeyStage<R, DV>& keys, int2 entry, int before) {
+            const int key_position = lane < KT ? entry.x : 0x7fffffff;
             if (lane < KT) {
-                int2 entry = make_int2(0x7fffffff, 0);
-                int before = 0;
-                if (k0 + lane < key_end) {
-                    entry = __ldg(key_entries + k0 + lane);
-                    before = __ldg(key_previous + k0 + lane);
-                }
-                key_position = entry.x;
                 keys.position[lane] = entry.x;
                 keys.label[lane] = entry.y;
                 keys.previous[lane] = before;
@@ -251,6 +272,15 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
             }
             cp_async_commit();
         };
+        auto stage_keys = [&](KeyStage<R, DV>& keys, int k0) {
+            int2 entry = make_int2(0x7fffffff, 0);
+            int before = 0;
+            if (lane < KT && k0 + lane < key_end) {
+                entry = __ldg(key_entries + k0 + lane);
+                before = __ldg(key_previous + k0 + lane);
+            }
+            stage_entries(keys, entry, before);
+        };
         // Multiplies a row's running state when its maximum rises to x.
         auto raise = [&](int s, float x) {
             const float alpha = ex2(maximum[s] - x);
@@ -260,7 +290,10 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
             maximum[s] = x;
         };
 
-        if (key_begin < key_end) stage_keys(mine.stage[0], key_begin);
+        if (key_begin < key_end) {
+            if (a.documents) stage_keys(mine.stage[0], key_begin);  // the first step moved with the documents
+            else stage_entries(mine.stage[0], fetched.key, fetched.key_previous);
+        }
         int buffer = 0;
         for (int k0 = key_begin; k0 < key_end; k0 += KT, buffer ^= 1) {
             const bool more = k0 + KT < key_end;
@@ -371,6 +404,8 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
                 *reinterpret_cast<__nv_bfloat162*>(out + c * 8) = __floats2bfloat162_rn(acc[c][2 * s] * inverse, acc[c][2 * s + 1] * inverse);
             if (t == 0) a.lse2[int64_t(bh) * a.n + position[s]] = active[s] ? maximum[s] + log2f(denominator[s]) : 0.f;
         }
+        tile = next_tile, plan = next_plan, fetched = next_fetched;
+        next_tile = after_next, next_plan = after_next_plan;
     }
 }
 
