@@ -17,9 +17,8 @@ namespace dism {
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float LOG_ZERO = -1000000.f;  // LUT entry of length 0 (dism_v3/src/hard_forward.cu:15)
 constexpr int BUCKETS = 4096;           // label buckets of the position index
-constexpr int OWN = 8;                  // rows per warp (one per group of four lanes)
-constexpr int WARPS = 8;                // warps per CTA
-constexpr int BLOCK_ROWS = WARPS * OWN;
+constexpr int OWN = 8;                  // rows per warp of the longest-match kernel
+constexpr int WARPS = 8;                // its warps per CTA
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -27,45 +26,6 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 __device__ __forceinline__ float bf2f(__nv_bfloat16 x) { return __bfloat162float(x); }
-
-// COUNT consecutive bf16 values (a multiple of 8, 16 bytes aligned) as floats.
-template <int COUNT>
-__device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float (&out)[COUNT]) {
-    static_assert(COUNT % 8 == 0, "vector loads of 8 values");
-    if constexpr (COUNT % 8 == 0) {
-#pragma unroll
-        for (int c = 0; c < COUNT / 8; ++c) {
-            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p) + c);
-            const unsigned word[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                out[c * 8 + 2 * e] = __uint_as_float(word[e] << 16);
-                out[c * 8 + 2 * e + 1] = __uint_as_float(word[e] & 0xffff0000u);
-            }
-        }
-    }
-}
-template <int COUNT>
-__device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const float (&in)[COUNT]) {
-    static_assert(COUNT % 8 == 0, "vector stores of 8 values");
-    unsigned word[COUNT / 2];
-#pragma unroll
-    for (int e = 0; e < COUNT / 2; ++e) {
-        __nv_bfloat162 pair = __floats2bfloat162_rn(in[2 * e], in[2 * e + 1]);
-        word[e] = *reinterpret_cast<unsigned*>(&pair);
-    }
-    if constexpr (COUNT % 8 == 0) {
-#pragma unroll
-        for (int c = 0; c < COUNT / 8; ++c)
-            reinterpret_cast<uint4*>(p)[c] = make_uint4(word[4 * c], word[4 * c + 1], word[4 * c + 2], word[4 * c + 3]);
-    }
-}
-// Sum over the four lanes of a group.
-__device__ __forceinline__ float group_sum(float x) {
-    x += __shfl_xor_sync(FULL, x, 1);
-    x += __shfl_xor_sync(FULL, x, 2);
-    return x;
-}
 
 __device__ __forceinline__ int bucket_of(int label) {
     unsigned x = unsigned(label);  // labels below 4096 keep a bucket each
@@ -143,8 +103,6 @@ __device__ __forceinline__ void partner_range(const SideIndex& index, int label,
 // bf16 on every lane) are gathered with cp.async into a
 // small shared-memory ring that each lane reads back itself, so several pairs' loads are in
 // flight per lane group while earlier pairs are being accumulated.
-constexpr int STAGES = 3;
-
 __device__ __forceinline__ void cp_async16(void* shared, const void* global) {
     const unsigned target = static_cast<unsigned>(__cvta_generic_to_shared(shared));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target), "l"(global));
@@ -153,83 +111,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
-template <int RPL, int VPL>
-struct alignas(16) GatherRing {  // 16-byte pieces: the struct keeps that alignment wherever it is embedded
-    // [stage][lane] keeps consecutive lanes 16 or more bytes apart without bank conflicts
-    __nv_bfloat16 b[STAGES][32][VPL];
-    __nv_bfloat16 a[STAGES][32][RPL];
-};
-
-template <int COUNT>
-__device__ __forceinline__ void unpack_bf16(const __nv_bfloat16* shared, float (&out)[COUNT]) {
-    if constexpr (COUNT % 8 == 0) {
-#pragma unroll
-        for (int c = 0; c < COUNT / 8; ++c) {
-            const uint4 raw = reinterpret_cast<const uint4*>(shared)[c];
-            const unsigned word[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                out[c * 8 + 2 * e] = __uint_as_float(word[e] << 16);
-                out[c * 8 + 2 * e + 1] = __uint_as_float(word[e] & 0xffff0000u);
-            }
-        }
-    }
-}
-
-// Works through the queued partners of the warp's rows: lane group g takes row g's queue in
-// order.  `a_base` / `b_base` point at this lane's slice of position 0; positions are
-// `a_stride` / `b_stride` elements apart.  consume(live, slot, a, b) is called once per round by
-// every lane (group sums inside it need the whole warp); live lanes have their vectors loaded.
-template <int RPL, int VPL, class Consume>
-__device__ __forceinline__ void drain_partners(const int* positions /* queue->position[group] */, int mine, int rounds,
-                                               GatherRing<RPL, VPL>* ring, const __nv_bfloat16* a_base,
-                                               int64_t a_stride, bool has_a, const __nv_bfloat16* b_base,
-                                               int64_t b_stride, int lane, Consume&& consume) {
-    static_assert(RPL == 8 && VPL % 8 == 0, "every gathered slice is a whole number of 16-byte pieces");
-    auto issue = [&](int slot) {
-        if (slot < mine) {
-            const int position = positions[slot], stage = slot % STAGES;
-            const __nv_bfloat16* a = a_base + position * a_stride;
-            const __nv_bfloat16* b = b_base + position * b_stride;
-            if (has_a) cp_async16(&ring->a[stage][lane][0], a);
-#pragma unroll
-            for (int c = 0; c < VPL / 8; ++c) cp_async16(&ring->b[stage][lane][c * 8], b + c * 8);
-        }
-        cp_async_commit();
-    };
-#pragma unroll
-    for (int slot = 0; slot < STAGES - 1; ++slot) issue(slot);
-    for (int slot = 0; slot < rounds; ++slot) {
-        issue(slot + STAGES - 1);
-        cp_async_wait<STAGES - 1>();
-        const bool live = slot < mine;
-        float a[RPL], b[VPL];
-#pragma unroll
-        for (int c = 0; c < RPL; ++c) a[c] = 0.f;
-        if (live) {
-            if (has_a) unpack_bf16<RPL>(&ring->a[slot % STAGES][lane][0], a);
-            unpack_bf16<VPL>(&ring->b[slot % STAGES][lane][0], b);
-        }
-        consume(live, slot, a, b);
-    }
-}
-
-// Arguments of the row-owned kernels; pointers a kernel does not use stay null.
-struct RowsArgs {
-    const __nv_bfloat16 *sq, *sk, *v, *dout;
-    const int *iq, *ik, *boundary;
-    const uint8_t* hard;
-    const float *lut, *dlut, *lse2;
-    SideIndex index;        // position index of the partner side
-    const int2* documents;  // packed layout: (begin, end) of the document of every 256-row block, or null
-    int hard_rows;          // rows of the hard-flag matrix (the batch size unless packed)
-    __nv_bfloat16 *out, *dsk, *dv;
-    float *lse2_out, *dsq, *dtau_rows;
-    int batch, heads, n, lut_stride, tasks;
-};
-
-// Optional per-kernel timing: when switched on through the C ABI, every launcher brackets its
-// kernels with CUDA events on the launch stream.  Off by default (one branch per launch).
 struct KernelTimer {
     KernelTimer(const char* name, cudaStream_t stream);
     ~KernelTimer();

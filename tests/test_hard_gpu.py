@@ -273,8 +273,9 @@ def labels_fault():
 @pytest.mark.parametrize('shape', [(2, 1024, 4, 64, 512), (1, 256, 2, 128, 256), (3, 128, 5, 64, 128),
                                    (1, 2048, 3, 64, 1024), (2, 640, 16, 128, 512), (1, 27 * 128, 7, 64, 384)])
 def test_labels_tensor_memory_pipeline(api, oracle, shape):
-    """Shapes the tcgen05 pipeline covers (D 64/128, V a multiple of 128, N a multiple of 128): bit-exact
-    labels, including duplicated codes (exact ties: the lowest index), near ties and zero rows."""
+    """Shapes the tcgen05 pipeline covers (D 64/128, V a multiple of 256, N a multiple of 128) and neighbours
+    that fall back to the mma.sync kernel (V 128, 384): bit-exact labels, including duplicated codes (exact
+    ties: the lowest index), near ties and zero rows."""
     b, n, h, d, v = shape
     g = torch.Generator().manual_seed(b * 1000 + n + v)
     x = torch.randn(b, n, h, d, generator=g).bfloat16()
