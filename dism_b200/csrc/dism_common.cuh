@@ -98,14 +98,16 @@ __device__ __forceinline__ void partner_range(const SideIndex& index, int label,
     }
 }
 
-// ---- gather ring -------------------------------------------------------------------------------
-// The per-pair vectors (A: eight bf16 on the lanes that hold a slice of the R-wide vector, B: VPL
-// bf16 on every lane) are gathered with cp.async into a
-// small shared-memory ring that each lane reads back itself, so several pairs' loads are in
-// flight per lane group while earlier pairs are being accumulated.
+// ---- asynchronous 16-byte copies into shared memory ------------------------------------------
 __device__ __forceinline__ void cp_async16(void* shared, const void* global) {
     const unsigned target = static_cast<unsigned>(__cvta_generic_to_shared(shared));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target), "l"(global));
+}
+// The same, but `bytes` (16 or 0) are read and the rest of the 16 is filled with zeros: a missing row
+// costs no branch.  `global` must be a mapped address even when nothing is read.
+__device__ __forceinline__ void cp_async16_or_zeros(void* shared, const void* global, int bytes) {
+    const unsigned target = static_cast<unsigned>(__cvta_generic_to_shared(shared));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(global), "r"(bytes));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int PENDING>

@@ -78,11 +78,18 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
     const int4* tiles = a.tiles + int64_t(bh) * a.tile_capacity;
     const int tile_count = __ldg(a.tile_starts + int64_t(bh) * (BUCKETS + 1) + BUCKETS);
     const float weight_one = __ldg(lut + 1), derivative_one = __ldg(dlut + 1);
+    const float weight_two = a.lut_stride > 2 ? __ldg(lut + 2) : 0.f, derivative_two = a.lut_stride > 2 ? __ldg(dlut + 2) : 0.f;
     // the owners' two vectors (rows of the first product) and the partners' (staged per step)
     const __nv_bfloat16* own_a = QUERY_MAJOR ? a.sq : a.sk;    // R wide
     const __nv_bfloat16* own_b = QUERY_MAJOR ? a.dout : a.v;   // DV wide
     const __nv_bfloat16* other_a = QUERY_MAJOR ? a.sk : a.sq;
     const __nv_bfloat16* other_b = QUERY_MAJOR ? a.v : a.dout;
+
+    // gathered rows: a lane always copies the same 16-byte piece of a row, so its source is one pointer
+    // plus position * stride (32-bit product: a (batch, head) slice spans less than 4 GB)
+    const unsigned a_stride = unsigned(a.heads) * R * 2, b_stride = unsigned(a.heads) * DV * 2;
+    const char* a_lane = reinterpret_cast<const char*>(other_a + vec0 * R) + (lane % (R / 8)) * 16;
+    const char* b_lane = reinterpret_cast<const char*>(other_b + vec0 * DV) + (lane % (DV / 8)) * 16;
 
     for (;;) {
         int tile = 0;
@@ -183,12 +190,11 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
         float sum_se[2] = {0.f, 0.f}, u[2] = {0.f, 0.f}, v[2] = {0.f, 0.f}, w[2] = {0.f, 0.f}, z[2] = {0.f, 0.f};
         int ordinary_total[2] = {0, 0};
 
-        auto classify = [&](const PartnerStage<R, DV>& partners, int s, int column) {
-            const int other = partners.position[column];
-            bool pair = active[s] && partners.label[column] == label[s];
+        auto classify = [&](int s, int other, int other_label, int other_previous) {
+            bool pair = active[s] && other_label == label[s];
             if (QUERY_MAJOR) pair = pair && other <= position[s] && other >= begin[s];
             else pair = pair && other >= position[s] && other < end[s];
-            const bool longer = pair && other > begin[s] && position[s] > begin[s] && partners.previous[column] == previous[s];
+            const bool longer = pair && other > begin[s] && position[s] > begin[s] && other_previous == previous[s];
             return pair ? (longer ? 2 : 1) : 0;
         };
         auto stage_partners = [&](PartnerStage<R, DV>& partners, int k0) {
@@ -209,20 +215,18 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                 partners.norm[lane] = normaliser;
                 partners.common[lane] = ex2(weight_one - normaliser);
             }
-            constexpr int A_PIECES = KT * R / 8, B_PIECES = KT * DV / 8;
+            constexpr int A_ROWS = 32 / (R / 8), B_ROWS = 32 / (DV / 8);  // rows a warp covers per round
 #pragma unroll
-            for (int piece = lane; piece < A_PIECES; piece += 32) {
-                const int row = piece / (R / 8), c = piece % (R / 8);
+            for (int row = lane / (R / 8); row < KT; row += A_ROWS) {
                 const int at = __shfl_sync(FULL, other, row);
-                if (at != 0x7fffffff) cp_async16(&partners.a[row][c * 8], other_a + (vec0 + int64_t(at) * a.heads) * R + c * 8);
-                else *reinterpret_cast<uint4*>(&partners.a[row][c * 8]) = make_uint4(0, 0, 0, 0);
+                const bool present = at != 0x7fffffff;
+                cp_async16_or_zeros(&partners.a[row][(lane % (R / 8)) * 8], a_lane + (present ? uint64_t(unsigned(at)) * a_stride : 0), present ? 16 : 0);
             }
 #pragma unroll
-            for (int piece = lane; piece < B_PIECES; piece += 32) {
-                const int row = piece / (DV / 8), c = piece % (DV / 8);
+            for (int row = lane / (DV / 8); row < KT; row += B_ROWS) {
                 const int at = __shfl_sync(FULL, other, row);
-                if (at != 0x7fffffff) cp_async16(&partners.b[row][c * 8], other_b + (vec0 + int64_t(at) * a.heads) * DV + c * 8);
-                else *reinterpret_cast<uint4*>(&partners.b[row][c * 8]) = make_uint4(0, 0, 0, 0);
+                const bool present = at != 0x7fffffff;
+                cp_async16_or_zeros(&partners.b[row][(lane % (DV / 8)) * 8], b_lane + (present ? uint64_t(unsigned(at)) * b_stride : 0), present ? 16 : 0);
             }
             cp_async_commit();
         };
@@ -256,13 +260,21 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                 }
             }
             unsigned ordinary_bits = 0, longer_bits = 0;  // one bit per element of this lane, at s * 4 + j * 2 + e
+            int2 other_position[2], other_label[2], other_previous[2];  // this lane's four columns: j * 8 + 2 t + e
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                other_position[j] = *reinterpret_cast<const int2*>(&partners.position[j * 8 + 2 * t]);
+                other_label[j] = *reinterpret_cast<const int2*>(&partners.label[j * 8 + 2 * t]);
+                other_previous[j] = *reinterpret_cast<const int2*>(&partners.previous[j * 8 + 2 * t]);
+            }
 #pragma unroll
             for (int s = 0; s < 2; ++s)
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const int kind = classify(partners, s, j * 8 + 2 * t + e);
+                        const int kind = classify(s, e ? other_position[j].y : other_position[j].x, e ? other_label[j].y : other_label[j].x,
+                                                  e ? other_previous[j].y : other_previous[j].x);
                         ordinary_bits |= unsigned(kind == 1) << (s * 4 + j * 2 + e);
                         longer_bits |= unsigned(kind == 2) << (s * 4 + j * 2 + e);
                     }
@@ -276,23 +288,20 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
 #pragma unroll
                     for (int s = 0; s < 2; ++s) {
                         unsigned waiting = __ballot_sync(FULL, holder && ((longer_bits >> (s * 4 + j * 2 + e)) & 1u));
+                        // the pair's two scalars are elements of the tiles just multiplied: the holder lane's registers
+                        const float element_s = j ? (e ? s_tile[1][2 * s + 1] : s_tile[1][2 * s]) : (e ? s_tile[0][2 * s + 1] : s_tile[0][2 * s]);
+                        const float element_e = j ? (e ? e_tile[1][2 * s + 1] : e_tile[1][2 * s]) : (e ? e_tile[0][2 * s + 1] : e_tile[0][2 * s]);
                         for (; waiting; waiting &= waiting - 1) {
-                            const int row = ((__ffs(waiting) - 1) >> 2) + 8 * s;
+                            const int source_lane = __ffs(waiting) - 1, row = (source_lane >> 2) + 8 * s;
                             const int owner_position = mine.position[row], other = partners.position[column];
                             const int qi = QUERY_MAJOR ? owner_position : other, kj = QUERY_MAJOR ? other : owner_position;
                             const int length = run_length(iq, ik, boundary, a.n, qi, kj, lane, mine.begin[row]);
-                            const float x = __ldg(lut + length);
+                            const float x = length == 2 ? weight_two : __ldg(lut + length);
                             const float p = ex2(x - (QUERY_MAJOR ? mine.norm[row] : partners.norm[column]));
-                            // the pair's two scalars from the vectors themselves
-                            const int64_t own_at = vec0 + int64_t(owner_position) * a.heads;
-                            float part_s = 0.f, part_e = 0.f;
-                            if (lane < R) part_s = bf2f(own_a[own_at * R + lane]) * bf2f(partners.a[column][lane]);
-#pragma unroll
-                            for (int c = lane; c < DV; c += 32) part_e = fmaf(bf2f(own_b[own_at * DV + c]), bf2f(partners.b[column][c]), part_e);
-                            const float score = warp_sum(part_s), slope = warp_sum(part_e);
+                            const float score = __shfl_sync(FULL, element_s, source_lane), slope = __shfl_sync(FULL, element_e, source_lane);
                             if (g == (row & 7)) {  // the four lanes that hold this row
                                 if (QUERY_MAJOR) {
-                                    const float gap = __ldg(dlut + length) - mine.center[row];
+                                    const float gap = (length == 2 ? derivative_two : __ldg(dlut + length)) - mine.center[row];
                                     const float pse = p * score * slope, pe = p * slope;
                                     u[s] += pse;
                                     v[s] = fmaf(p, gap, v[s]);

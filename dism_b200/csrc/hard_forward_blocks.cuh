@@ -147,7 +147,12 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
     const int* query_previous = a.queries.previous + int64_t(bh) * a.n;
     const int4* tiles = a.tiles + int64_t(bh) * a.tile_capacity;
     const int tile_count = __ldg(a.tile_starts + int64_t(bh) * (BUCKETS + 1) + BUCKETS);
-    const float weight_one = __ldg(lut + 1);
+    const float weight_one = __ldg(lut + 1), weight_two = a.lut_stride > 2 ? __ldg(lut + 2) : 0.f;
+    // gathered rows: a lane always copies the same 16-byte piece of a row, so its source is one pointer
+    // plus position * stride (32-bit product: a (batch, head) slice spans less than 4 GB)
+    const unsigned sk_stride = unsigned(a.heads) * R * 2, v_stride = unsigned(a.heads) * DV * 2;
+    const char* sk_lane = reinterpret_cast<const char*>(a.sk + vec0 * R) + (lane % (R / 8)) * 16;
+    const char* v_lane = reinterpret_cast<const char*>(a.v + vec0 * DV) + (lane % (DV / 8)) * 16;
 
     // Tiles differ a lot in their number of key steps, so warps take them one at a time from a counter.
     // Getting to a tile's rows takes a chain of dependent reads (counter, descriptor, index entries), so the
@@ -241,10 +246,9 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
         for (int c = 0; c < VTILES; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
 
         // The kind of one score element: 1 = ordinary pair (run length 1), 2 = longer run, 0 = no pair.
-        auto classify = [&](const KeyStage<R, DV>& keys, int s, int column) {
-            const int key_position = keys.position[column];
-            const bool pair = active[s] && keys.label[column] == label[s] && key_position <= position[s] && key_position >= begin[s];
-            const bool longer = pair && key_position > begin[s] && position[s] > begin[s] && keys.previous[column] == previous[s];
+        auto classify = [&](int s, int key_position, int key_label, int key_previous) {
+            const bool pair = active[s] && key_label == label[s] && key_position <= position[s] && key_position >= begin[s];
+            const bool longer = pair && key_position > begin[s] && position[s] > begin[s] && key_previous == previous[s];
             return pair ? (longer ? 2 : 1) : 0;
         };
         // Labels of a key step and its sk / v rows (cp.async); rows beyond the range are zero-filled.
@@ -255,20 +259,18 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
                 keys.label[lane] = entry.y;
                 keys.previous[lane] = before;
             }
-            constexpr int SK_PIECES = KT * R / 8, V_PIECES = KT * DV / 8;
+            constexpr int SK_ROWS = 32 / (R / 8), V_ROWS = 32 / (DV / 8);  // rows a warp covers per round
 #pragma unroll
-            for (int piece = lane; piece < SK_PIECES; piece += 32) {
-                const int key = piece / (R / 8), c = piece % (R / 8);
+            for (int key = lane / (R / 8); key < KT; key += SK_ROWS) {
                 const int at = __shfl_sync(FULL, key_position, key);
-                if (at != 0x7fffffff) cp_async16(&keys.sk[key][c * 8], a.sk + (vec0 + int64_t(at) * a.heads) * R + c * 8);
-                else *reinterpret_cast<uint4*>(&keys.sk[key][c * 8]) = make_uint4(0, 0, 0, 0);
+                const bool present = at != 0x7fffffff;
+                cp_async16_or_zeros(&keys.sk[key][(lane % (R / 8)) * 8], sk_lane + (present ? uint64_t(unsigned(at)) * sk_stride : 0), present ? 16 : 0);
             }
 #pragma unroll
-            for (int piece = lane; piece < V_PIECES; piece += 32) {
-                const int key = piece / (DV / 8), c = piece % (DV / 8);
+            for (int key = lane / (DV / 8); key < KT; key += V_ROWS) {
                 const int at = __shfl_sync(FULL, key_position, key);
-                if (at != 0x7fffffff) cp_async16(&keys.v[key][c * 8], a.v + (vec0 + int64_t(at) * a.heads) * DV + c * 8);
-                else *reinterpret_cast<uint4*>(&keys.v[key][c * 8]) = make_uint4(0, 0, 0, 0);
+                const bool present = at != 0x7fffffff;
+                cp_async16_or_zeros(&keys.v[key][(lane % (DV / 8)) * 8], v_lane + (present ? uint64_t(unsigned(at)) * v_stride : 0), present ? 16 : 0);
             }
             cp_async_commit();
         };
@@ -316,13 +318,21 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
             }
             // one bit per score element of this lane, at s * 4 + j * 2 + e
             unsigned ordinary_bits = 0, longer_bits = 0;
+            int2 key_position[2], key_label[2], key_previous[2];  // this lane's four columns: j * 8 + 2 t + e
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                key_position[j] = *reinterpret_cast<const int2*>(&keys.position[j * 8 + 2 * t]);
+                key_label[j] = *reinterpret_cast<const int2*>(&keys.label[j * 8 + 2 * t]);
+                key_previous[j] = *reinterpret_cast<const int2*>(&keys.previous[j * 8 + 2 * t]);
+            }
 #pragma unroll
             for (int s = 0; s < 2; ++s)
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const int kind = classify(keys, s, j * 8 + 2 * t + e);
+                        const int kind = classify(s, e ? key_position[j].y : key_position[j].x, e ? key_label[j].y : key_label[j].x,
+                                                  e ? key_previous[j].y : key_previous[j].x);
                         ordinary_bits |= unsigned(kind == 1) << (s * 4 + j * 2 + e);
                         longer_bits |= unsigned(kind == 2) << (s * 4 + j * 2 + e);
                     }
@@ -336,14 +346,14 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
 #pragma unroll
                     for (int s = 0; s < 2; ++s) {
                         unsigned waiting = __ballot_sync(FULL, holder && ((longer_bits >> (s * 4 + j * 2 + e)) & 1u));  // lanes = rows g + 8 s, ascending
+                        // the pair's score is an element of the tile just multiplied: the holder lane's register
+                        const float element = j ? (e ? score[1][2 * s + 1] : score[1][2 * s]) : (e ? score[0][2 * s + 1] : score[0][2 * s]);
                         for (; waiting; waiting &= waiting - 1) {
-                            const int row = ((__ffs(waiting) - 1) >> 2) + 8 * s;
+                            const int source_lane = __ffs(waiting) - 1, row = (source_lane >> 2) + 8 * s;
                             const int qi = mine.position[row], kj = keys.position[column];
                             const int length = run_length(iq, ik, boundary, a.n, qi, kj, lane, mine.begin[row]);
-                            const float x = __ldg(lut + length);
-                            float product = 0.f;
-                            if (lane < R) product = bf2f(a.sq[(vec0 + int64_t(qi) * a.heads) * R + lane]) * bf2f(keys.sk[column][lane]);
-                            const float value_score = warp_sum(product);
+                            const float x = length == 2 ? weight_two : __ldg(lut + length);
+                            const float value_score = __shfl_sync(FULL, element, source_lane);
                             if (g == (row & 7)) {  // the four lanes that hold this row
                                 if (x > maximum[s]) raise(s, x);
                                 const float p = ex2(x - maximum[s]);
