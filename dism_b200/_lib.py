@@ -21,7 +21,7 @@ SIGNATURES = {
     'dism_hard_readout_static': (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     'dism_hard_readout_static_error': (_c.c_char_p, []),
     'dism_hard_backward_workspace': (_Z, [_I, _I, _I, _I]),
-    'dism_hard_backward': (_I, [_P] * 9 + [_I, _P, _I, _P] + [_I] * 6 + [_P, _P, _P, _P, _P, _Z, _P]),
+    'dism_hard_backward': (_I, [_P] * 9 + [_I, _P, _I, _P] + [_I] * 6 + [_P, _P, _P, _P, _P, _Z, _P, _P]),
     'dism_longest_match_workspace': (_Z, [_I, _I]),
     'dism_profile_enable': (_I, [_I]),
     'dism_profile_count': (_I, []),

@@ -85,7 +85,7 @@ int dism_profile_read(int index, char* name, int capacity, float* milliseconds) 
 }
 
 const char* dism_last_error(void) { return last_error; }
-int dism_abi_version(void) { return 4; }
+int dism_abi_version(void) { return 5; }
 
 int dism_labels(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t* labels, void* stream) {
@@ -183,7 +183,7 @@ int dism_hard_backward(const void* sq, const void* sk, const void* v, const void
                        int hard_rows, const float* lut, int lut_stride, const float* lse2, int batch, int n, int heads,
                        int r, int dv, int ctas,
                        float* dsq, void* dsk, void* dv_out, float* dtau, void* workspace, size_t workspace_bytes,
-                       void* stream) {
+                       const void* readout_workspace, void* stream) {
     if (int status = check_shape(batch, heads, n)) return status;
     if (int status = check_dims(r, dv)) return status;
     if (!sq || !sk || !v || !dout || !iq || !ik || !hard || !lut || !lse2 || !dsq || !dsk || !dv_out || !dtau ||
@@ -194,6 +194,7 @@ int dism_hard_backward(const void* sq, const void* sk, const void* v, const void
     if (int status = check_documents(documents, hard_rows, boundary, batch, n)) return status;
     if (workspace_bytes < dism::hard_backward_workspace_bytes(batch, heads, n, lut_stride) || !aligned(workspace, 256))
         return fail(DISM_EINVAL, "workspace too small or misaligned (see dism_hard_backward_workspace)");
+    if (readout_workspace && !aligned(readout_workspace, 256)) return fail(DISM_EINVAL, "readout workspace misaligned");
     if (!aligned(sq, 16) || !aligned(sk, 16) || !aligned(v, 16) || !aligned(dout, 16) || !aligned(dsq, 16) ||
         !aligned(dsk, 16) || !aligned(dv_out, 16))
         return fail(DISM_EINVAL, "vector tensors must be 16-byte aligned");
@@ -204,7 +205,7 @@ int dism_hard_backward(const void* sq, const void* sk, const void* v, const void
                                                   hard, boundary, reinterpret_cast<const int2*>(documents), hard_rows, lut,
                                                   lut_stride, lse2, ctas, dsq,
                                                   static_cast<bf*>(dsk), static_cast<bf*>(dv_out), dtau, workspace,
-                                                  static_cast<cudaStream_t>(stream)), "hard_backward");
+                                                  readout_workspace, static_cast<cudaStream_t>(stream)), "hard_backward");
 }
 
 size_t dism_longest_match_workspace(int batch, int n) {

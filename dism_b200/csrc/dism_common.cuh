@@ -162,7 +162,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
                                  const __nv_bfloat16* v, const __nv_bfloat16* dout, const int* iq, const int* ik,
                                  const uint8_t* hard, const int* boundary, const int2* documents, int hard_rows,
                                  const float* lut, int lut_stride, const float* lse2, int ctas, float* dsq,
-                                 __nv_bfloat16* dsk, __nv_bfloat16* dv, float* dtau, void* workspace,
+                                 __nv_bfloat16* dsk, __nv_bfloat16* dv, float* dtau, void* workspace, const void* readout_workspace,
                                  cudaStream_t stream);
 
 }  // namespace dism

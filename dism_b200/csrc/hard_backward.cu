@@ -85,11 +85,17 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
                                  const uint8_t* hard, const int* boundary, const int2* documents, int hard_rows,
                                  const float* lut, int lut_stride, const float* lse2, int ctas, float* dsq,
                                  __nv_bfloat16* dsk, __nv_bfloat16* dv, float* dtau, void* workspace,
-                                 cudaStream_t stream) {
+                                 const void* readout_workspace, cudaStream_t stream) {
     const int batch_heads = shape.batch * shape.heads;
-    cudaError_t status = launch_build_index_pair(ik, iq, batch_heads, shape.n, workspace, stream);
-    if (status != cudaSuccess) return status;
-    const SideIndex keys = side_index(workspace, batch_heads, shape.n, 0, 2), queries = side_index(workspace, batch_heads, shape.n, 1, 2);
+    cudaError_t status = cudaSuccess;
+    // the forward's workspace starts with the same two-sided index (keys first): reuse it when the caller kept it
+    void* index = const_cast<void*>(readout_workspace);
+    if (!index) {
+        index = workspace;
+        status = launch_build_index_pair(ik, iq, batch_heads, shape.n, workspace, stream);
+        if (status != cudaSuccess) return status;
+    }
+    const SideIndex keys = side_index(index, batch_heads, shape.n, 0, 2), queries = side_index(index, batch_heads, shape.n, 1, 2);
     char* cursor = static_cast<char*>(workspace) + index_bytes(batch_heads, shape.n, 2);
     const int capacity = tile_capacity_for(shape.n);
     int4* tiles[2];

@@ -269,6 +269,34 @@ def _layout_arguments(table, hard, boundary, lut, b, h, n, device):
     return _document_table(spans, n, device).data_ptr(), hard.size(0)
 
 
+# The readout's workspace starts with the position index of both label tensors; the backward of the same
+# step can reuse it.  One entry per device: the two label tensors themselves (kept alive, so their memory
+# cannot be handed to other labels), their version counters (bumped by any in-place write) and the
+# workspace.  share_index(False) switches the reuse off and drops the entries.
+_shared_index = {}
+_share_index = True
+
+
+def share_index(enabled):
+    """Let hard_backward reuse the position index that hard_readout built for the same label tensors."""
+    global _share_index
+    _share_index = bool(enabled)
+    if not _share_index:
+        _shared_index.clear()
+
+
+def _remember_index(iq, ik, workspace):
+    if _share_index:
+        _shared_index[iq.device.index] = (iq, ik, iq._version, ik._version, workspace)
+
+
+def _recall_index(iq, ik):
+    entry = _shared_index.get(iq.device.index) if _share_index else None
+    if entry is not None and entry[0] is iq and entry[1] is ik and entry[2] == iq._version and entry[3] == ik._version:
+        return entry[4]
+    return None
+
+
 def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
     """x = (sq, sk, v, query labels, key labels, hard) -> (bf16 [B,N,H,DV], FP32 log2 normaliser [B,H,N])."""
     _no_table(None, choice)
@@ -295,6 +323,7 @@ def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
                                           hard.data_ptr(), boundary_ptr, documents_ptr, rows, lut.data_ptr(),
                                           lut.size(1), b, n, h, r, dv, int(ctas), out.data_ptr(), norm.data_ptr(),
                                           workspace.data_ptr(), size, _stream(sq)))
+        _remember_index(iq, ik, workspace)
     return out, norm
 
 
@@ -326,12 +355,14 @@ def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None)
         dtau = torch.empty((h,), dtype=torch.float32, device=sq.device)
         size = _abi.dism_hard_backward_workspace(b, h, n, lut.size(1))
         workspace = torch.empty((size,), dtype=torch.uint8, device=sq.device)
+        index = _recall_index(iq, ik)
         _lib.check(_abi.dism_hard_backward(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), dout.data_ptr(),
                                            iq.data_ptr(), ik.data_ptr(), hard.data_ptr(), boundary_ptr,
                                            documents_ptr, rows, lut.data_ptr(), lut.size(1), normalizer.data_ptr(),
                                            b, n, h, r, dv,
                                            int(ctas), dsq.data_ptr(), dsk.data_ptr(), dv_out.data_ptr(),
-                                           dtau.data_ptr(), workspace.data_ptr(), size, _stream(sq)))
+                                           dtau.data_ptr(), workspace.data_ptr(), size,
+                                           index.data_ptr() if index is not None else None, _stream(sq)))
     return [dsq, dsk, dv_out, dtau]
 
 

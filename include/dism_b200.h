@@ -93,13 +93,16 @@ size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride)
 /* Hard backward: dsq float [B,N,H,R], dsk bf16 [B,N,H,R], dv bf16 [B,N,H,DV], dtau float [H]
  * (gradient of the natural-log coefficient).  lse2 is the normaliser the forward returned;
  * `boundary` may be NULL; `documents`/`hard_rows` as in dism_hard_readout; `workspace` is caller-owned scratch of dism_hard_backward_workspace bytes.
+ * `readout_workspace` is NULL, or the workspace a dism_hard_readout call filled for the same labels, batch,
+ * heads and n and that nothing has written since: its position index is then reused instead of rebuilt
+ * (the reference's backward likewise consumes state its forward saved).
  * Stands in for cu_flash_dism.hard_backward (dism_v3/src/host/hard_backward.cpp:13-141). */
 int dism_hard_backward(const void *sq, const void *sk, const void *v, const void *dout, const int32_t *iq,
                        const int32_t *ik, const uint8_t *hard, const int32_t *boundary,
                        const int32_t *documents, int hard_rows, const float *lut, int lut_stride,
                        const float *lse2, int batch, int n, int heads, int r, int dv, int ctas, float *dsq,
                        void *dsk, void *dv_out, float *dtau, void *workspace, size_t workspace_bytes,
-                       void *stream);
+                       const void *readout_workspace, void *stream);
 
 /* Single longest earlier match of symbol streams int32 [B,N] (labels of queries and keys are
  * the same stream): for every i the most recent j < i with the longest run L(i,j), its length,

@@ -84,3 +84,36 @@ def test_long_context_with_planted_runs(oracle):
     torch.testing.assert_close(out.double().cpu(), torch.from_numpy(expected), atol=.008, rtol=.025)
     torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
     assert lse2.max() > 30  # the planted runs dominate their rows' normalisers
+
+
+def test_full_size_discretiser(oracle):
+    """The tcgen05 discretiser at the benchmark shape: the oracle on three (batch, head) slices; over the whole
+    tensor, agreement with an fp32 arg-max up to near ties, and three exact properties: the same labels
+    on a second call, under scaling of x by a power of two (every logit scales exactly in both summation
+    orders), and under a permutation of the codebook (labels map through the permutation)."""
+    import ctypes
+    import dism_b200
+    dism_b200.install_dropin()
+    import cu_flash_dism as cu
+    from dism_b200 import _lib
+    b, n, h, d, v = 8, 8192, 16, 64, 512
+    g = torch.Generator(device='cuda').manual_seed(3)
+    x = torch.randn(b, n, h, d, generator=g, device='cuda').bfloat16()
+    e = torch.nn.functional.silu(torch.randn(h, v, d, generator=g, device='cuda')).bfloat16()
+    got = cu.labels(x, e)
+    code = ctypes.c_int(-1)
+    _lib.check(_lib.load().dism_labels_fault(ctypes.byref(code)))
+    assert code.value == 0
+    for bi, hi in ((0, 0), (7, 15), (3, 9)):
+        want = oracle.labels(x[bi:bi + 1, :, hi:hi + 1].float().cpu().numpy(), e[hi:hi + 1].float().cpu().numpy())
+        assert np.array_equal(got[bi:bi + 1, hi:hi + 1].cpu().numpy(), want)
+    mismatches = 0
+    for bi in range(b):
+        reference = torch.argmax(torch.einsum('nhd,hvd->hnv', x[bi].float(), e.float()), -1)
+        mismatches += int((reference != got[bi]).sum())
+    assert mismatches < 1e-3 * got.numel()
+    assert torch.equal(cu.labels(x, e), got)
+    assert torch.equal(cu.labels((x.float() * 4).bfloat16(), e), got)
+    permutation = torch.randperm(v, generator=torch.Generator().manual_seed(4)).cuda()
+    permuted = cu.labels(x, e[:, permutation].contiguous())
+    assert int((permutation[permuted.long()] != got).sum()) <= 2  # exact ties between two codes may resolve differently

@@ -223,6 +223,42 @@ def test_backward_all_soft_is_zero(api):
     assert all(not t.count_nonzero() for t in got)
 
 
+def test_backward_reuses_the_forward_index(api):
+    """The backward takes the position index from the readout of the same label tensors: same bits as a
+    rebuilt index; labels written in place, or other label tensors, are not served from the cache."""
+    b, n, h, r, dv = 2, 1024, 3, 32, 64
+    sq, sk, v, dout = (t.cuda() for t in vectors(5, b, n, h, r, dv))
+    g = torch.Generator().manual_seed(6)
+    iq, ik = (torch.randint(0, 40, (b, h, n), generator=g, dtype=torch.int32).cuda() for _ in range(2))
+    hard = torch.ones(b, h, dtype=torch.bool, device='cuda')
+    tau = torch.full((h,), .3, device='cuda')
+    cu = api['cu']
+
+    def both(iq, ik):
+        out, norm = api['fwd'].forward_hard(sq, sk, v, iq, ik, hard, tau)
+        lut = api['fwd'].hard_log_weights(tau, n)
+        return norm, api['bwd'].backward_hard(sq, sk, v, dout, iq, ik, hard, norm, dict(boundary=None, log_weights=lut))
+
+    norm, shared = both(iq, ik)
+    assert cu._recall_index(iq, ik) is not None
+    cu.share_index(False)
+    try:
+        _, rebuilt = both(iq, ik)
+        assert cu._recall_index(iq, ik) is None
+    finally:
+        cu.share_index(True)
+    assert all(torch.equal(a, e) for a, e in zip(shared, rebuilt))
+    both(iq, ik)
+    iq[0, 1, 7] += 1                       # in place: the remembered index is stale
+    assert cu._recall_index(iq, ik) is None
+    both(iq, ik)
+    assert cu._recall_index(iq.clone(), ik) is None  # another tensor, even with the same values
+    lut = api['fwd'].hard_log_weights(tau, n)
+    _, fresh = both(iq, ik)
+    again = api['bwd'].backward_hard(sq, sk, v, dout, iq.clone(), ik.clone(), hard, _, dict(boundary=None, log_weights=lut))
+    assert all(torch.equal(a, e) for a, e in zip(fresh, again))
+
+
 # ---- the CPU-runnable reference configuration --------------------------------------------------------
 def test_config1_reference_case(api, oracle):
     g = golden('config1.npz')
