@@ -193,14 +193,21 @@ __device__ __forceinline__ float chunk_max(const float (&r)[32]) {
 }
 
 // Bit i set: logit i of the chunk is above the threshold.  (s - t) * gain saturates to exactly 1
-// or 0 (see fold_product), so the two sums are exact 16-bit integers.
+// or 0 (see make_threshold), so the two sums are exact 16-bit integers.  They are built high bit
+// first, acc = 2 acc + g, for columns i and 16 + i at once with the packed FP32 FMA: half the
+// instructions of two scalar chains.
 __device__ __forceinline__ unsigned chunk_mask(const float (&r)[32], float gain, float offset) {
-    float low = 0.f, high = 0.f;
+    unsigned long long acc, two;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(two) : "f"(2.f));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(acc) : "f"(0.f));
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        low = fmaf(fma_saturate(r[i], gain, offset), float(1 << i), low);
-        high = fmaf(fma_saturate(r[16 + i], gain, offset), float(1 << i), high);
+    for (int i = 15; i >= 0; --i) {
+        unsigned long long g;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(g) : "f"(fma_saturate(r[i], gain, offset)), "f"(fma_saturate(r[16 + i], gain, offset)));
+        asm("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(acc) : "l"(two), "l"(g));
     }
+    float low, high;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(low), "=f"(high) : "l"(acc));
     return unsigned(low) | (unsigned(high) << 16);
 }
 
