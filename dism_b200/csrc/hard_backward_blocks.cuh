@@ -268,7 +268,8 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                 other_previous[j] = *reinterpret_cast<const int2*>(&partners.previous[j * 8 + 2 * t]);
             }
 #pragma unroll
-            for (int s = 0; s < 2; ++s)
+            for (int s = 0; s < 2; ++s) {
+                if (s == 1 && owners <= 8) continue;  // a tile of at most eight rows has no second half
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -278,6 +279,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                         ordinary_bits |= unsigned(kind == 1) << (s * 4 + j * 2 + e);
                         longer_bits |= unsigned(kind == 2) << (s * 4 + j * 2 + e);
                     }
+            }
 
             // pairs with longer runs: one at a time, partners ascending
             if (__ballot_sync(FULL, longer_bits != 0)) {

@@ -326,7 +326,8 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
                 key_previous[j] = *reinterpret_cast<const int2*>(&keys.previous[j * 8 + 2 * t]);
             }
 #pragma unroll
-            for (int s = 0; s < 2; ++s)
+            for (int s = 0; s < 2; ++s) {
+                if (s == 1 && queries <= 8) continue;  // a tile of at most eight rows has no second half
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -336,6 +337,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
                         ordinary_bits |= unsigned(kind == 1) << (s * 4 + j * 2 + e);
                         longer_bits |= unsigned(kind == 2) << (s * 4 + j * 2 + e);
                     }
+            }
             int ordinary[2] = {__popc(ordinary_bits & 15u), __popc(ordinary_bits >> 4)};
             // pairs with longer runs: one at a time, keys ascending, so a row always sees them in the same order
             if (__ballot_sync(FULL, longer_bits != 0)) {
