@@ -7,19 +7,21 @@
 // One persistent CTA per SM walks a contiguous range of (head, 128-row tile) pairs:
 //   producer warp   TMA: the head's whole codebook once (128-byte swizzled, K-major), then one
 //                   128 x D tile of x per step into a ring;
-//   MMA warp        one thread issues tcgen05.mma (M=128, N=256, K=16) for each 256-code slice of the
-//                   codebook into one of two FP32 accumulators: all of tensor memory;
-//   norm warp       squared norms of the tile's rows (the margin below scales with them);
+//   MMA warp        one elected lane issues tcgen05.mma (M=128, N=256, K=16) for each 256-code slice of
+//                   the codebook into one of two FP32 accumulators: all of tensor memory;
+//   norm warp       largest squared code norm of the head (the margin below scales with it);
 //   two finishing   put the column ranges of a row together: label, pair list or crowded list;
 //   warps
 //   sixteen         read the accumulators with tcgen05.ld (row = tensor-memory lane = thread; a warp
 //   epilogue warps  owns 32 rows and a quarter of the columns of every accumulator) and keep, per row,
-//                   the largest logit and the columns of all logits within a safety margin of it.
+//                   the largest logit and the columns of all logits within a safety margin of it; a tile
+//                   ahead, each of their threads also sums a quarter of a row's squares (the margin
+//                   scales with the row norm too).
 //
 // The epilogue is the instruction bound of the kernel, and min/max/logic instructions issue at half
 // the FMA rate.  So the half-rate pipe only finds the maximum of each 32-column chunk (three-input
 // max: half an instruction per logit); the full-rate pipe marks the logits above the threshold with
-// a saturating FMA, g = sat((s - t) * gain), and a second FMA adds g * 2^column into a bit mask.
+// a saturating FMA, g = sat((s - t) * gain), and a packed FMA shifts two g at a time into bit masks.
 // gain is a power of two chosen from the exponent of t so that g is exactly 0 or 1 for every float s.
 // The masks are folded into the row's candidates once per 64 columns.
 //
