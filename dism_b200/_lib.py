@@ -13,6 +13,7 @@ SIGNATURES = {
     'dism_abi_version': (_I, []),
     'dism_labels': (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _P]),
     'dism_labels_fault': (_I, [_P]),
+    'dism_labels_wait_selftest': (_I, [_I, _P, _P]),
     'dism_hard_summary': (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P]),
     'dism_hard_chunk': (_I, [_P, _P, _I, _I, _P]),
     'dism_hard_log_weights': (_I, [_P, _I, _I, _P, _P]),

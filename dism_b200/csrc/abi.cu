@@ -104,6 +104,11 @@ int dism_labels_fault(int* code) {
     return cuda_status(dism::read_labels_fault(code), "labels fault code");
 }
 
+int dism_labels_wait_selftest(int code, int* outcome, void* stream) {
+    if (!outcome || code <= 0) return fail(DISM_EINVAL, "outcome array and a positive code required");
+    return cuda_status(dism::run_wait_selftest(code, outcome, static_cast<cudaStream_t>(stream)), "wait self-test");
+}
+
 int dism_hard_summary(const int32_t* iq, const int32_t* ik, const uint8_t* hard, int batch, int heads, int n,
                       int ctas, int32_t* summary, void* stream) {
     if (int status = check_shape(batch, heads, n)) return status;

@@ -133,6 +133,7 @@ bool labels_tcgen05_covers(const void* x, const void* codebook, int batch, int n
 cudaError_t launch_labels_tcgen05(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int batch, int n, int heads,
                                   int d, int vocab, int* labels, cudaStream_t stream);
 cudaError_t read_labels_fault(int* code);
+cudaError_t run_wait_selftest(int code, int* outcome, cudaStream_t stream);
 cudaError_t launch_hard_summary(const int* iq, const int* ik, const uint8_t* hard, int batch, int heads, int n,
                                 int ctas, int* summary, cudaStream_t stream);
 cudaError_t launch_hard_chunk(const int* summary, int* boundary, int batch_heads, int n, cudaStream_t stream);

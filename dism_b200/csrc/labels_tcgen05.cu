@@ -746,6 +746,45 @@ cudaError_t launch_labels_tcgen05(const __nv_bfloat16* x, const __nv_bfloat16* c
 }
 
 // First bounded wait that ran out in any earlier launch on this device (0: none).  Synchronises the device.
-cudaError_t read_labels_fault(int* code) { return cudaMemcpyFromSymbol(code, labels_fault_code, sizeof(int)); }
+cudaError_t read_labels_fault(int* code) {
+    const cudaError_t status = cudaMemcpyFromSymbol(code, labels_fault_code, sizeof(int));
+    if (status != cudaSuccess) return status;
+    const int none = 0;
+    return cudaMemcpyToSymbol(labels_fault_code, &none, sizeof(int));  // read and clear
+}
+
+namespace {
+// A wait that nothing ever satisfies, through the same bounded-wait code as the pipeline: two warps wait on
+// one barrier; the first to run out records `code` and raises the flag that releases the other.
+__global__ void wait_selftest_kernel(int code, int* outcome) {
+    __shared__ Control control;
+    if (threadIdx.x == 0) {
+        barrier_init(&control.drain, 1);
+        control.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool passed = barrier_wait(&control.drain, 0, control, code);
+    if ((threadIdx.x & 31) == 0) outcome[threadIdx.x >> 5] = passed ? 1 : 0;
+}
+}  // namespace
+
+// Runs the self-test on `stream` and waits for it.  outcome[0..1]: 1 if the wait of warp 0 / warp 1 came
+// back satisfied (it must not).  The recorded fault code is read with read_labels_fault.
+cudaError_t run_wait_selftest(int code, int* outcome, cudaStream_t stream) {
+    int* device = nullptr;
+    cudaError_t status = cudaMalloc(&device, 2 * sizeof(int));
+    if (status != cudaSuccess) return status;
+    const int unset[2] = {-1, -1};
+    status = cudaMemcpyAsync(device, unset, sizeof(unset), cudaMemcpyHostToDevice, stream);
+    if (status == cudaSuccess) {
+        wait_selftest_kernel<<<1, 64, 0, stream>>>(code, device);
+        status = cudaGetLastError();
+    }
+    if (status == cudaSuccess) status = cudaMemcpyAsync(outcome, device, 2 * sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (status == cudaSuccess) status = cudaStreamSynchronize(stream);
+    cudaFree(device);
+    return status;
+}
 
 }  // namespace dism

@@ -33,9 +33,17 @@ int dism_abi_version(void);
 int dism_labels(const void *x, const void *codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t *labels, void *stream);
 /* The discretiser's tensor-memory pipeline bounds every wait of its roles on one another; *code is
- * the first wait that ran out in any earlier dism_labels launch on the current device (0: none, the
- * only value a correct run produces).  Synchronises the device.  No counterpart in the reference. */
+ * the first wait that ran out in any dism_labels launch on the current device since the last call
+ * (0: none, the only value a correct run produces); the call clears it.  Synchronises the device.
+ * No counterpart in the reference. */
 int dism_labels_fault(int *code);
+/* Exercises that bounded wait without the pipeline: one tiny kernel whose two warps wait (through the
+ * pipeline's own wait routine) on a barrier that nothing ever completes.  The first to run out, after
+ * about a second at most, records `code` (> 0) as the fault and releases the other.
+ * outcome[0..1] (host memory) receive 1 if a wait came back satisfied, 0 if it gave up — both must be 0;
+ * dism_labels_fault then returns `code`.  The call allocates 8 bytes, synchronises `stream`, and leaves the
+ * context usable.  No counterpart in the reference. */
+int dism_labels_wait_selftest(int code, int *outcome, void *stream);
 
 /* Strip summaries: summary int32 [B,H,(N-1)/32,N]; non-causal and soft entries are -1.
  * Stands in for cu_flash_dism.hard_summary (dism_v3/src/frontend.cpp:309-312,

@@ -341,6 +341,23 @@ def test_labels_tensor_memory_pipeline_all_ties(api):
     assert (got != reference).float().mean() < .02
 
 
+def test_bounded_wait_gives_up_and_reports(api):
+    """A wait that nothing satisfies runs out, reports its code, and leaves the context usable."""
+    import ctypes
+    from dism_b200 import _lib
+    lib = _lib.load()
+    assert labels_fault() == 0
+    outcome = (ctypes.c_int * 2)(-1, -1)
+    _lib.check(lib.dism_labels_wait_selftest(77, outcome, None))
+    assert list(outcome) == [0, 0]
+    assert labels_fault() == 77
+    assert labels_fault() == 0  # reading clears it
+    x = torch.randn(1, 256, 2, 64).bfloat16().cuda()
+    e = torch.randn(2, 256, 64).bfloat16().cuda()
+    reference = torch.argmax(torch.einsum('bnhd,hvd->bnhv', x.float(), e.float()), -1).transpose(1, 2)
+    assert (api['cu'].labels(x, e) != reference).float().mean() < 1e-2 and labels_fault() == 0
+
+
 # ---- symbol streams: single longest earlier match -----------------------------------------------------
 def symbol_streams(batch, n, vocab, seed):
     rng = np.random.default_rng(seed)
