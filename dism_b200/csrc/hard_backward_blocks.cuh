@@ -155,7 +155,20 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                 partner_begin = lower_bound_position(partner_entries, partner_begin, partner_end, first);
             }
         } else {
-            partner_begin = lower_bound_position(partner_entries, partner_begin, partner_end, mine.position[0]);
+            // First query at or after the tile's first key.  The bucket's queries are probed 32 at a time by the
+            // whole warp (one coalesced read each) before a binary search takes over: most buckets hold fewer.
+            {
+                const int bound = mine.position[0];
+                int probed = 0;
+                for (; probed < 64 && partner_begin < partner_end; probed += 32) {
+                    const int at = partner_begin + lane;
+                    const bool before = at < partner_end && __ldg(partner_entries + at).x < bound;
+                    const unsigned mask = __ballot_sync(FULL, before);
+                    partner_begin += __popc(mask);
+                    if (mask != FULL) break;
+                }
+                if (probed >= 64) partner_begin = lower_bound_position(partner_entries, partner_begin, partner_end, bound);
+            }
             if (a.documents) {
                 int last = mine.end[0];
                 for (int r = 1; r < owners; ++r) last = max(last, mine.end[r]);
