@@ -215,19 +215,17 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
             if (lane < KT) {
                 int2 entry = make_int2(QUERY_MAJOR ? 0x7fffffff : -1, 0);
                 int before = 0;
-                float normaliser = 0.f;
                 if (k0 + lane < partner_end) {
                     entry = __ldg(partner_entries + k0 + lane);
                     before = __ldg(partner_previous + k0 + lane);
                     other = entry.x;
-                    if (!QUERY_MAJOR) normaliser = __ldg(lse2 + entry.x);
                 }
                 partners.position[lane] = entry.x;
                 partners.label[lane] = entry.y;
                 partners.previous[lane] = before;
-                partners.norm[lane] = normaliser;
-                partners.common[lane] = ex2(weight_one - normaliser);
             }
+            float normaliser = 0.f;  // key-major: read now, stored after the rows are on their way
+            if (!QUERY_MAJOR && other != 0x7fffffff) normaliser = __ldg(lse2 + other);
             constexpr int A_ROWS = 32 / (R / 8), B_ROWS = 32 / (DV / 8);  // rows a warp covers per round
 #pragma unroll
             for (int row = lane / (R / 8); row < KT; row += A_ROWS) {
@@ -242,6 +240,10 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                 cp_async16_or_zeros(&partners.b[row][(lane % (DV / 8)) * 8], b_lane + (present ? uint64_t(unsigned(at)) * b_stride : 0), present ? 16 : 0);
             }
             cp_async_commit();
+            if (lane < KT) {
+                partners.norm[lane] = normaliser;
+                partners.common[lane] = ex2(weight_one - normaliser);
+            }
         };
 
         if (partner_begin < partner_end) stage_partners(mine.stage[0], partner_begin);
