@@ -140,8 +140,8 @@ def run_ours(args):
                               dict(boundary=None, log_weights=lut))
         mark()
         # labels x2; readout: log weights, index, tiles, forward; log weights; backward: their derivative,
-        # tiles x2, query-major, key-major, tau reduction (the index is the readout's)
-        launches[0] += 2 + 4 + 1 + 6
+        # tiles (both plans in one launch), query-major, key-major, tau reduction (the index is the readout's)
+        launches[0] += 2 + 4 + 1 + 5
         return out, norm, grads
 
     def _event():

@@ -35,8 +35,10 @@ __global__ __launch_bounds__(1024) void tau_reduce_kernel(const float* __restric
                                                           int batch, int heads, int n) {
     const int head = blockIdx.x;
     float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
     for (int b = 0; b < batch; ++b) {
         const float4* source = reinterpret_cast<const float4*>(rows + (int64_t(b) * heads + head) * n);
+#pragma unroll 2
         for (int e = threadIdx.x; e < n / 4; e += blockDim.x) {
             const float4 x = __ldg(source + e);
             sum[0] += x.x; sum[1] += x.y; sum[2] += x.z; sum[3] += x.w;
@@ -113,10 +115,9 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     }
     {
         KernelTimer timer("plan_tiles", stream);
-        plan_query_tiles_kernel<<<batch_heads, 1024, 0, stream>>>(queries.starts, keys.starts, tile_starts[0], tiles[0],
-                                                                  tile_starts[0] + size_t(batch_heads) * (BUCKETS + 1), capacity);
-        plan_query_tiles_kernel<<<batch_heads, 1024, 0, stream>>>(keys.starts, queries.starts, tile_starts[1], tiles[1],
-                                                                  tile_starts[1] + size_t(batch_heads) * (BUCKETS + 1), capacity);
+        const TilePlan by_query{queries.starts, keys.starts, tile_starts[0], tiles[0], tile_starts[0] + size_t(batch_heads) * (BUCKETS + 1)};
+        const TilePlan by_key{keys.starts, queries.starts, tile_starts[1], tiles[1], tile_starts[1] + size_t(batch_heads) * (BUCKETS + 1)};
+        plan_tile_pair_kernel<<<dim3(batch_heads, 2), 1024, 0, stream>>>(by_query, by_key, capacity);
     }
     BackwardBlockArgs args{};
     args.sq = sq; args.sk = sk; args.v = v; args.dout = dout;

@@ -78,10 +78,9 @@ struct BlockArgs {
 __host__ __device__ inline int tile_capacity_for(int n) { return n / QT + BUCKETS; }
 
 // tile_starts[b] = number of 16-query tiles in the buckets before b, and one descriptor per tile.
-static __global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int* __restrict__ query_starts,
-                                                                const int* __restrict__ key_starts,
-                                                                int* __restrict__ tile_starts, int4* __restrict__ tiles,
-                                                                int* __restrict__ next_tile, int tile_capacity) {
+__device__ __forceinline__ void plan_query_tiles(const int* __restrict__ query_starts, const int* __restrict__ key_starts,
+                                                 int* __restrict__ tile_starts, int4* __restrict__ tiles,
+                                                 int* __restrict__ next_tile, int tile_capacity) {
     constexpr int PER = BUCKETS / 1024;
     __shared__ int warp_total[32];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -127,6 +126,24 @@ static __global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int
         tile_starts[BUCKETS] = before + sum;
         next_tile[blockIdx.x] = 0;
     }
+}
+
+static __global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int* query_starts, const int* key_starts,
+                                                                       int* tile_starts, int4* tiles, int* next_tile,
+                                                                       int tile_capacity) {
+    plan_query_tiles(query_starts, key_starts, tile_starts, tiles, next_tile, tile_capacity);
+}
+
+// Two plans in one launch (the backward's query-major and key-major tiles): blockIdx.y picks the plan.
+struct TilePlan {
+    const int *owner_starts, *partner_starts;
+    int* tile_starts;
+    int4* tiles;
+    int* next_tile;
+};
+static __global__ __launch_bounds__(1024) void plan_tile_pair_kernel(const TilePlan first, const TilePlan second, int tile_capacity) {
+    const TilePlan& plan = blockIdx.y ? second : first;
+    plan_query_tiles(plan.owner_starts, plan.partner_starts, plan.tile_starts, plan.tiles, plan.next_tile, tile_capacity);
 }
 
 template <int R, int DV>
