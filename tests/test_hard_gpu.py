@@ -141,6 +141,40 @@ def test_forward_backward_dimensions(api, oracle, r, dv):
     torch.testing.assert_close(got[3].double().cpu(), torch.from_numpy(want[3]), atol=.003, rtol=.01)
 
 
+@pytest.mark.parametrize('seed', range(12))
+def test_random_shapes_against_oracle(api, oracle, seed):
+    """Seeded random shapes, label densities (2 to 600 symbols: dense buckets with many key steps and long
+    runs, down to buckets of one position), hard flags and tau signs: forward and backward against the oracle,
+    with and without the reference's boundary rectangle."""
+    rng = np.random.default_rng(1000 + seed)
+    b, h = int(rng.integers(1, 4)), int(rng.integers(1, 5))
+    n = int(rng.choice([256, 512, 768]))
+    r, dv = int(rng.choice([16, 32])), int(rng.choice([32, 64, 128]))
+    symbols = int(rng.choice([2, 5, 40, 600]))
+    q = rng.integers(0, symbols, (b, h, n)).astype(np.int32)
+    k = rng.integers(0, symbols, (b, h, n)).astype(np.int32)
+    start = int(rng.integers(0, n // 2))
+    k[:, :, start:start + n // 4] = q[:, :, start + 3:start + 3 + n // 4]  # a planted run of n/4
+    hard = rng.random((b, h)) < .8
+    hard[0, 0] = True
+    sq, sk, v, dout = vectors(2000 + seed, b, n, h, r, dv)
+    tau = torch.from_numpy(rng.uniform(-.6, .6, h).astype(np.float32))
+    x = [sq.cuda(), sk.cuda(), v.cuda(), dev(q), dev(k), dev(hard)]
+    save = bool(seed % 2)
+    result = api['fwd'].forward_hard(*x, tau.cuda(), ctas=int(rng.choice([0, 1, 7])), save_state=save)
+    out, norm = result[0], result[1]
+    state = result[2] if save else dict(boundary=None, log_weights=api['fwd'].hard_log_weights(tau.cuda(), n))
+    f = lambda t: t.float().numpy()
+    expected, lse2 = oracle.forward(f(sq), f(sk), f(v), q, k, hard, tau.numpy())
+    assert_vectors(out, expected)
+    torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
+    got = api['bwd'].backward_hard(*x[:3], dout.cuda(), *x[3:], norm, state)
+    want = oracle.backward(f(sq), f(sk), f(v), f(dout), q, k, hard, tau.numpy())
+    for a, e in zip(got[:3], want[:3]):
+        assert_vectors(a, e)
+    torch.testing.assert_close(got[3].double().cpu(), torch.from_numpy(want[3]), atol=.003, rtol=.01)
+
+
 def test_forward_exactness_properties(api):
     g = golden('pattern_boundary.npz')
     x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
