@@ -25,6 +25,7 @@ namespace dism {
 constexpr int QT = 16;  // queries per tile (the m of m16n8k16)
 constexpr int KT = 16;  // keys per step: two n8 score tiles, one k16 step of the value product
 constexpr int BLOCK_WARPS = 8;
+constexpr int WALK_CAP = 8;  // run lengths up to this are found by the lane that holds the pair
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -356,8 +357,65 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
                     }
             }
             int ordinary[2] = {__popc(ordinary_bits & 15u), __popc(ordinary_bits >> 4)};
-            // pairs with longer runs: one at a time, keys ascending, so a row always sees them in the same order
-            if (__ballot_sync(FULL, longer_bits != 0)) {
+            const bool any_longer = __ballot_sync(FULL, longer_bits != 0) != 0;
+            if (any_longer) {
+                // A lane walks the diagonals of its own pairs with longer runs, a few cells at most: nearly all such
+                // runs are short, and all of them are then weighted and multiplied on the tensor cores together
+                // with the ordinary pairs, each element with its own table entry.
+                float x[8];  // log2 weight of element slot s * 4 + j * 2 + e
+                unsigned tensor_bits = ordinary_bits, unresolved = 0;
+#pragma unroll
+                for (int slot = 0; slot < 8; ++slot) {
+                    const int s = slot >> 2, j = (slot >> 1) & 1, e = slot & 1;
+                    x[slot] = weight_one;
+                    if ((longer_bits >> slot) & 1u) {
+                        const int qi = position[s], kj = e ? key_position[j].y : key_position[j].x;
+                        int length = 2;  // the pair and its diagonal predecessor match
+                        while (length <= WALK_CAP && kj - length >= begin[s] && __ldg(iq + qi - length) == __ldg(ik + kj - length)) ++length;
+                        if (length <= WALK_CAP) {
+                            tensor_bits |= 1u << slot;
+                            x[slot] = length == 2 ? weight_two : __ldg(lut + length);
+                        } else {
+                            unresolved |= 1u << slot;
+                        }
+                    }
+                }
+                float p[8], sum[2] = {0.f, 0.f};
+#pragma unroll
+                for (int s = 0; s < 2; ++s) {
+                    float top = -INFINITY;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if ((tensor_bits >> (s * 4 + q)) & 1u) top = fmaxf(top, x[s * 4 + q]);
+                    top = fmaxf(top, __shfl_xor_sync(FULL, top, 1));
+                    top = fmaxf(top, __shfl_xor_sync(FULL, top, 2));
+                    if (top > maximum[s]) raise(s, top);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        p[s * 4 + q] = (tensor_bits >> (s * 4 + q)) & 1u ? ex2(x[s * 4 + q] - maximum[s]) : 0.f;
+                        sum[s] += p[s * 4 + q];
+                    }
+                    sum[s] += __shfl_xor_sync(FULL, sum[s], 1);
+                    sum[s] += __shfl_xor_sync(FULL, sum[s], 2);
+                    denominator[s] += sum[s];
+                }
+                unsigned weights[4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int s = 0; s < 2; ++s)
+                        weights[2 * j + s] = pack_bf16(p[s * 4 + j * 2] * score[j][2 * s], p[s * 4 + j * 2 + 1] * score[j][2 * s + 1]);
+#pragma unroll
+                for (int c = 0; c < VTILES; ++c) {
+                    unsigned b0, b1;
+                    ldmatrix_x2_trans(b0, b1, &keys.v[lane & 15][c * 8]);
+                    mma_bf16_16816(acc[c], weights, b0, b1);
+                }
+                longer_bits = unresolved;
+                ordinary[0] = ordinary[1] = 0;  // done above
+            }
+            // pairs whose run is longer than a lane walks: one at a time by the whole warp, keys ascending
+            if (any_longer && __ballot_sync(FULL, longer_bits != 0)) {
 #pragma unroll 1
                 for (int column = 0; column < KT; ++column) {
                     const int j = column >> 3, e = column & 1;
