@@ -13,6 +13,8 @@
 // Every output row belongs to one warp and is accumulated in a fixed order: no atomics, and the
 // same bits for every grid size.
 #pragma once
+#include <type_traits>
+
 #include "hard_forward_blocks.cuh"
 
 namespace dism {
@@ -23,7 +25,7 @@ struct alignas(16) PartnerStage {
     __nv_bfloat16 a[KT][R + 8];
     __nv_bfloat16 b[KT][DV + 8];
     int position[KT], label[KT], previous[KT];
-    float common[KT], norm[KT];  // key-major only: the query's c_i and log2 normaliser
+    float common[KT], common_two[KT], norm[KT];  // key-major only: the query's weights of run lengths 1 and 2, and its log2 normaliser
 };
 
 template <int R, int DV>
@@ -131,7 +133,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
         __syncwarp();
         int position[2], label[2], previous[2], begin[2], end[2];
         bool active[2];
-        float norm[2], center[2], common_row[2];
+        float norm[2], center[2], common_row[2], common_two_row[2];
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
             const int r = g + 8 * s;
@@ -143,7 +145,8 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
             active[s] = mine.active[r] != 0;
             norm[s] = mine.norm[r];
             center[s] = mine.center[r];
-            common_row[s] = active[s] ? ex2(weight_one - norm[s]) : 0.f;  // query-major: c_i of the row
+            common_row[s] = active[s] ? ex2(weight_one - norm[s]) : 0.f;  // query-major: weight of an ordinary pair of the row
+            common_two_row[s] = active[s] ? ex2(weight_two - norm[s]) : 0.f;  // and of a pair of run length 2
         }
         // partner range inside the bucket: keys from the earliest document start to the last query, or
         // queries from the first key to the latest document end
@@ -202,6 +205,8 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
         for (int c = 0; c < (QUERY_MAJOR ? 1 : VTILES); ++c) grad_b[c][0] = grad_b[c][1] = grad_b[c][2] = grad_b[c][3] = 0.f;
         float sum_se[2] = {0.f, 0.f}, u[2] = {0.f, 0.f}, v[2] = {0.f, 0.f}, w[2] = {0.f, 0.f}, z[2] = {0.f, 0.f};
         int ordinary_total[2] = {0, 0};
+        float sum_se_two[2] = {0.f, 0.f};  // the same two sums over the pairs of run length 2
+        int two_total[2] = {0, 0};
 
         auto classify = [&](int s, int other, int other_label, int other_previous) {
             bool pair = active[s] && other_label == label[s];
@@ -243,6 +248,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
             if (lane < KT) {
                 partners.norm[lane] = normaliser;
                 partners.common[lane] = ex2(weight_one - normaliser);
+                partners.common_two[lane] = ex2(weight_two - normaliser);
             }
         };
 
@@ -296,8 +302,27 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                     }
             }
 
-            // pairs with longer runs: one at a time, partners ascending
-            if (__ballot_sync(FULL, longer_bits != 0)) {
+            // A pair with a longer run is nearly always of length 2: the lane that holds it looks one cell further up
+            // the diagonal, and such pairs join the ordinary ones on the tensor cores with the table's second entry.
+            unsigned two_bits = 0;
+            const bool any_longer = __ballot_sync(FULL, longer_bits != 0) != 0;
+            if (any_longer) {
+                unsigned unresolved = 0;
+#pragma unroll
+                for (int slot = 0; slot < 8; ++slot) {
+                    if ((longer_bits >> slot) & 1u) {
+                        const int s = slot >> 2, j = (slot >> 1) & 1, e = slot & 1;
+                        const int other = e ? other_position[j].y : other_position[j].x;
+                        const int qi = QUERY_MAJOR ? position[s] : other, kj = QUERY_MAJOR ? other : position[s];
+                        const bool ends = kj - 2 < begin[s] || __ldg(iq + qi - 2) != __ldg(ik + kj - 2);
+                        if (ends) two_bits |= 1u << slot;
+                        else unresolved |= 1u << slot;
+                    }
+                }
+                longer_bits = unresolved;
+            }
+            // the rest: one at a time, partners ascending
+            if (any_longer && __ballot_sync(FULL, longer_bits != 0)) {
 #pragma unroll 1
                 for (int column = 0; column < KT; ++column) {
                     const int j = column >> 3, e = column & 1;
@@ -351,9 +376,11 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                 }
             }
 
-            // ordinary pairs on tensor cores
-            if (__ballot_sync(FULL, ordinary_bits != 0)) {
+            // ordinary pairs and pairs of run length 2 on tensor cores
+            if (__ballot_sync(FULL, (ordinary_bits | two_bits) != 0)) {
                 unsigned coefficient_e[4], remainder_e[4], coefficient_s[4], remainder_s[4];
+                // two instances of the element loop: the common one knows that no pair of run length 2 is in the step
+                auto coefficients = [&](auto with_two) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -362,18 +389,27 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
                             const bool on = (ordinary_bits >> (s * 4 + j * 2 + e)) & 1u;
-                            const float c = QUERY_MAJOR ? common_row[s] : partners.common[j * 8 + 2 * t + e];
+                            const bool two = decltype(with_two)::value && ((two_bits >> (s * 4 + j * 2 + e)) & 1u);
+                            float c = on ? (QUERY_MAJOR ? common_row[s] : partners.common[j * 8 + 2 * t + e]) : 0.f;
+                            if (decltype(with_two)::value && two) c = QUERY_MAJOR ? common_two_row[s] : partners.common_two[j * 8 + 2 * t + e];
                             const float score = s_tile[j][2 * s + e], slope = e_tile[j][2 * s + e];
-                            pe[e] = on ? c * slope : 0.f;
-                            ps[e] = on ? c * score : 0.f;
+                            pe[e] = c * slope;
+                            ps[e] = c * score;
                             if (QUERY_MAJOR && on) {
                                 sum_se[s] = fmaf(score, slope, sum_se[s]);
                                 ++ordinary_total[s];
+                            }
+                            if (QUERY_MAJOR && two) {
+                                sum_se_two[s] = fmaf(score, slope, sum_se_two[s]);
+                                ++two_total[s];
                             }
                         }
                         split_bf16(pe[0], pe[1], coefficient_e[2 * j + s], remainder_e[2 * j + s]);
                         if (!QUERY_MAJOR) split_bf16(ps[0], ps[1], coefficient_s[2 * j + s], remainder_s[2 * j + s]);
                     }
+                };
+                if (__ballot_sync(FULL, two_bits != 0)) coefficients(std::true_type{});
+                else coefficients(std::false_type{});
                 // (c o E) times the partners' R-vectors: dSQ (query-major) or dSK (key-major)
 #pragma unroll
                 for (int c = 0; c < RTILES; ++c) {
@@ -405,6 +441,10 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                 sum_se[s] += __shfl_xor_sync(FULL, sum_se[s], 2);
                 ordinary_total[s] += __shfl_xor_sync(FULL, ordinary_total[s], 1);
                 ordinary_total[s] += __shfl_xor_sync(FULL, ordinary_total[s], 2);
+                sum_se_two[s] += __shfl_xor_sync(FULL, sum_se_two[s], 1);
+                sum_se_two[s] += __shfl_xor_sync(FULL, sum_se_two[s], 2);
+                two_total[s] += __shfl_xor_sync(FULL, two_total[s], 1);
+                two_total[s] += __shfl_xor_sync(FULL, two_total[s], 2);
             }
         }
 #pragma unroll
@@ -417,8 +457,11 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                     // moments: ordinary pairs share weight c_i and the derivative of length 1
                     const float gap = derivative_one - center[s], mass = common_row[s] * float(ordinary_total[s]);
                     const float pse = common_row[s] * sum_se[s];
-                    const float total_u = u[s] + pse, total_z = z[s] + mass;
-                    const float total_v = fmaf(mass, gap, v[s]), total_w = fmaf(pse, gap, w[s]);
+                    const float gap_two = derivative_two - center[s], mass_two = common_two_row[s] * float(two_total[s]);
+                    const float pse_two = common_two_row[s] * sum_se_two[s];
+                    const float total_u = u[s] + pse + pse_two, total_z = z[s] + mass + mass_two;
+                    const float total_v = fmaf(mass_two, gap_two, fmaf(mass, gap, v[s]));
+                    const float total_w = fmaf(pse_two, gap_two, fmaf(pse, gap, w[s]));
                     // centred four-moment form: the fallback has unit weight and zero derivative
                     const float fallback = ex2(-norm[s]), inverse = __fdividef(1.f, total_z + fallback);
                     const float mean = fmaf(-fallback, center[s], total_v) * inverse;
