@@ -484,7 +484,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
             if (g + 8 * s >= queries) continue;
-            const float inverse = active[s] ? 1.f / denominator[s] : 0.f;
+            const float inverse = active[s] ? __frcp_rn(denominator[s]) : 0.f;
             __nv_bfloat16* out = a.out + (vec0 + int64_t(position[s]) * a.heads) * DV + 2 * t;
 #pragma unroll
             for (int c = 0; c < VTILES; ++c)
