@@ -67,9 +67,9 @@ size_t hard_backward_workspace_bytes(int batch, int heads, int n, int lut_stride
            sizeof(float) * (size_t(heads) * lut_stride + size_t(batch) * heads * n);
 }
 
-template <bool QUERY_MAJOR, int R, int DV>
-static cudaError_t launch_backward_blocks(const BackwardBlockArgs& args, int ctas, cudaStream_t stream) {
-    auto kernel = hard_backward_blocks_kernel<QUERY_MAJOR, R, DV>;
+template <bool QUERY_MAJOR, bool PACKED, int R, int DV>
+static cudaError_t launch_backward_variant(const BackwardBlockArgs& args, int ctas, cudaStream_t stream) {
+    auto kernel = hard_backward_blocks_kernel<QUERY_MAJOR, PACKED, R, DV>;
     const int shared = sizeof(BackwardWarpShared<R, DV>) * BLOCK_WARPS;
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
     if (status != cudaSuccess) return status;
@@ -80,6 +80,12 @@ static cudaError_t launch_backward_blocks(const BackwardBlockArgs& args, int cta
     KernelTimer timer(QUERY_MAJOR ? "hard_backward_query" : "hard_backward_key", stream);
     kernel<<<dim3(per_head, batch_heads), BLOCK_WARPS * 32, shared, stream>>>(args);
     return cudaGetLastError();
+}
+
+template <bool QUERY_MAJOR, int R, int DV>
+static cudaError_t launch_backward_blocks(const BackwardBlockArgs& args, int ctas, cudaStream_t stream) {
+    return args.documents ? launch_backward_variant<QUERY_MAJOR, true, R, DV>(args, ctas, stream)
+                          : launch_backward_variant<QUERY_MAJOR, false, R, DV>(args, ctas, stream);
 }
 
 cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,

@@ -59,7 +59,9 @@ __device__ __forceinline__ void split_bf16(float x, float y, unsigned& high, uns
     low = pack_bf16(x - back.x, y - back.y);
 }
 
-template <bool QUERY_MAJOR, int R, int DV>
+// PACKED: rows carry document limits (a.documents is set); otherwise every row's document is the whole sequence
+// and the limits are constants the compiler folds away.
+template <bool QUERY_MAJOR, bool PACKED, int R, int DV>
 __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kernel(const BackwardBlockArgs a) {
     constexpr int KSTEPS = R / 16, VSTEPS = DV / 16, RTILES = R / 8, VTILES = DV / 8;
     extern __shared__ __align__(16) unsigned char storage[];
@@ -109,7 +111,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                 entry = __ldg(owner_entries + first_owner + lane);
                 previous = __ldg(owner_previous + first_owner + lane);
                 int hard_row = b;
-                if (a.documents) {
+                if (PACKED) {
                     const int2 document = __ldg(a.documents + entry.x / 256);
                     begin = document.x;
                     end = document.y;
@@ -140,8 +142,8 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
             position[s] = mine.position[r];
             label[s] = mine.label[r];
             previous[s] = mine.previous[r];
-            begin[s] = mine.begin[r];
-            end[s] = mine.end[r];
+            begin[s] = PACKED ? mine.begin[r] : 0;
+            end[s] = PACKED ? mine.end[r] : a.n;
             active[s] = mine.active[r] != 0;
             norm[s] = mine.norm[r];
             center[s] = mine.center[r];
@@ -152,7 +154,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
         // queries from the first key to the latest document end
         int partner_begin = plan.z, partner_end = plan.w;
         if (QUERY_MAJOR) {
-            if (a.documents) {
+            if (PACKED) {
                 int first = mine.begin[0];
                 for (int r = 1; r < owners; ++r) first = min(first, mine.begin[r]);
                 partner_begin = lower_bound_position(partner_entries, partner_begin, partner_end, first);
@@ -172,7 +174,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                 }
                 if (probed >= 64) partner_begin = lower_bound_position(partner_entries, partner_begin, partner_end, bound);
             }
-            if (a.documents) {
+            if (PACKED) {
                 int last = mine.end[0];
                 for (int r = 1; r < owners; ++r) last = max(last, mine.end[r]);
                 partner_end = lower_bound_position(partner_entries, partner_begin, partner_end, last);
@@ -337,7 +339,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
                             const int source_lane = __ffs(waiting) - 1, row = (source_lane >> 2) + 8 * s;
                             const int owner_position = mine.position[row], other = partners.position[column];
                             const int qi = QUERY_MAJOR ? owner_position : other, kj = QUERY_MAJOR ? other : owner_position;
-                            const int length = run_length(iq, ik, boundary, a.n, qi, kj, lane, mine.begin[row]);
+                            const int length = run_length(iq, ik, boundary, a.n, qi, kj, lane, PACKED ? mine.begin[row] : 0);
                             const float x = length == 2 ? weight_two : __ldg(lut + length);
                             const float p = ex2(x - (QUERY_MAJOR ? mine.norm[row] : partners.norm[column]));
                             const float score = __shfl_sync(FULL, element_s, source_lane), slope = __shfl_sync(FULL, element_e, source_lane);
