@@ -48,9 +48,9 @@ size_t hard_forward_workspace_bytes(int batch, int heads, int n) {
            batch_heads * (BUCKETS + 2) * sizeof(int);
 }
 
-template <int R, int DV>
-static cudaError_t launch_blocks_variant(const BlockArgs& args, int ctas, cudaStream_t stream) {
-    auto kernel = hard_forward_blocks_kernel<R, DV>;
+template <bool PACKED, int R, int DV>
+static cudaError_t launch_blocks_layout(const BlockArgs& args, int ctas, cudaStream_t stream) {
+    auto kernel = hard_forward_blocks_kernel<PACKED, R, DV>;
     const int shared = sizeof(BlockWarpShared<R, DV>) * BLOCK_WARPS;
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
     if (status != cudaSuccess) return status;
@@ -62,6 +62,11 @@ static cudaError_t launch_blocks_variant(const BlockArgs& args, int ctas, cudaSt
     KernelTimer timer("hard_forward", stream);
     kernel<<<dim3(per_head, batch_heads), BLOCK_WARPS * 32, shared, stream>>>(args);
     return cudaGetLastError();
+}
+
+template <int R, int DV>
+static cudaError_t launch_blocks_variant(const BlockArgs& args, int ctas, cudaStream_t stream) {
+    return args.documents ? launch_blocks_layout<true, R, DV>(args, ctas, stream) : launch_blocks_layout<false, R, DV>(args, ctas, stream);
 }
 
 cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,

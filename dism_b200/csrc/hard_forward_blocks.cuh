@@ -147,7 +147,9 @@ static __global__ __launch_bounds__(1024) void plan_tile_pair_kernel(const TileP
     plan_query_tiles(plan.owner_starts, plan.partner_starts, plan.tile_starts, plan.tiles, plan.next_tile, tile_capacity);
 }
 
-template <int R, int DV>
+// PACKED: rows carry document limits (a.documents is set); otherwise every row's document is the whole sequence
+// and the limits are constants the compiler folds away.
+template <bool PACKED, int R, int DV>
 __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(const BlockArgs a) {
     constexpr int KSTEPS = R / 16, VTILES = DV / 8;
     extern __shared__ __align__(16) unsigned char storage[];
@@ -177,7 +179,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
     // chain runs ahead of the arithmetic: while tile i is worked on, the index entries of tile i+1, the
     // descriptor of tile i+2 and the number of tile i+3 are in flight.  A warp may claim up to three
     // numbers past the end; they are ignored.
-    const int fixed_active = a.documents ? 0 : a.hard[b * a.heads + h];
+    const int fixed_active = PACKED ? 0 : a.hard[b * a.heads + h];
     auto claim = [&]() { return lane == 0 ? atomicAdd(a.next_tile + bh, 1) : 0; };  // lane 0 holds the number
     auto descriptor = [&](int tile) { return tile < tile_count ? __ldg(tiles + tile) : make_int4(0, 0, 0, 0); };
     struct Entries {
@@ -217,7 +219,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
             int begin = 0, active = 0;
             if (lane < queries) {
                 active = fixed_active;
-                if (a.documents) {
+                if (PACKED) {
                     begin = __ldg(a.documents + entry.x / 256).x;
                     active = a.hard[entry.x / (a.n / a.hard_rows) * a.heads + h];
                 }
@@ -237,13 +239,13 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
             position[s] = mine.position[r];
             label[s] = mine.label[r];
             previous[s] = mine.previous[r];
-            begin[s] = mine.begin[r];
+            begin[s] = PACKED ? mine.begin[r] : 0;
             active[s] = mine.active[r] != 0;
         }
         const int last_query = mine.position[queries - 1];
         int key_begin = plan.z;
         const int key_end = plan.w;
-        if (a.documents) {  // packed: the bucket also holds keys of earlier documents
+        if (PACKED) {  // the bucket also holds keys of earlier documents
             int first_begin = mine.begin[0];
             for (int r = 1; r < queries; ++r) first_begin = min(first_begin, mine.begin[r]);
             key_begin = lower_bound_position(key_entries, key_begin, key_end, first_begin);
@@ -311,7 +313,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
         };
 
         if (key_begin < key_end) {
-            if (a.documents) stage_keys(mine.stage[0], key_begin);  // the first step moved with the documents
+            if (PACKED) stage_keys(mine.stage[0], key_begin);  // the first step moved with the documents
             else stage_entries(mine.stage[0], fetched.key, fetched.key_previous);
         }
         int buffer = 0;
@@ -428,7 +430,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
                         for (; waiting; waiting &= waiting - 1) {
                             const int source_lane = __ffs(waiting) - 1, row = (source_lane >> 2) + 8 * s;
                             const int qi = mine.position[row], kj = keys.position[column];
-                            const int length = run_length(iq, ik, boundary, a.n, qi, kj, lane, mine.begin[row]);
+                            const int length = run_length(iq, ik, boundary, a.n, qi, kj, lane, PACKED ? mine.begin[row] : 0);
                             const float x = length == 2 ? weight_two : __ldg(lut + length);
                             const float value_score = __shfl_sync(FULL, element, source_lane);
                             if (g == (row & 7)) {  // the four lanes that hold this row
