@@ -5,8 +5,8 @@
 One step = one pass of the whole path over one batch of the training shape (B8 H16 N8192 D64 R32
 DV64, 512 symbols per head): the discretiser for q and k, the fused hard forward, and the hard
 backward.  Metric: query positions per second, whole job.  With N > 1 (torchrun, one rank per GPU)
-every rank runs the same shape on its own 16 heads (heads are independent: no collective on the
-data path, weak scaling) and the time is the maximum over ranks.
+the SAME problem is split over the ranks by heads (16 / N heads per GPU: heads are independent, so
+there is no collective on the data path; strong scaling) and the time is the maximum over ranks.
 
 `value` is timed with the inputs resident in HBM; `e2e` times the same step through the drop-in
 Python API with pinned host inputs copied in and results copied out inside the timed region.
@@ -28,19 +28,25 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SHAPE = dict(batch=8, heads=16, n=8192, d=64, r=32, dv=64, vocab=512)
+WORKLOAD = 'training shape B{batch} H16 N8192 D64 R32 DV64 V512, all rows hard, tau 0.5: labels(q), labels(k), hard forward, hard backward'
 # Algorithmic bytes per query position of each kernel launch (inputs read once, outputs written once).
 KERNEL_BYTES = {
-    'labels': 132,               # one bf16 row of 64 read, one label written (one launch per tensor)
+    'labels_pair': 264,          # q and k in one launch: two bf16 rows of 64 read, two labels written
     'hard_forward': 396,         # labels 8, sq+sk 128, v 128 read; out 128, lse2 4 written
     'hard_backward_query': 524,  # sq,sk 128, v,dO 256, labels 8, lse2 4 read; dsq (f32) 128 written
     'hard_backward_key': 588,    # the same reads; dsk 64, dv 128 written
 }
-# dram__bytes_read.sum + dram__bytes_write.sum per launch at the full shape, from the ncu captures
-# summarised under profiles/ (captured at batch 2 and scaled by 4: traffic grows with the rows).  At
-# batch 2 part of the outputs stays in the 126 MB L2, which is why three of the figures are below the
-# algorithmic bytes.
-TRAFFIC = {'labels': 138.7e6, 'hard_forward': 338.7e6, 'hard_backward_query': 529.0e6, 'hard_backward_key': 535.5e6}
 STEP_BYTES = 2 * 132 + 396 + 716  # whole path: two label launches, forward, backward (inputs counted once)
+
+
+def measured_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch at the benchmark batch on one GPU, as captured with
+    ncu (profiles/traffic_B8.json, with the command that made it); None for kernels without a capture."""
+    path = os.path.join(ROOT, 'profiles', 'traffic_B8.json')
+    if not os.path.exists(path):
+        return {}
+    with open(path) as f:
+        return json.load(f).get('bytes_per_launch', {})
 
 
 def measured_peak():
@@ -90,7 +96,10 @@ class ClockSampler:
                     reasons=sorted(self.reasons))
 
 
-def make_inputs(seed, device):
+def make_inputs(seed, device, rank=0, world=1):
+    """Host (pinned) and device operands of this rank: the whole problem is drawn from one seed on every
+    rank, then cut to the rank's contiguous slice of heads (dism_b200/sharding.py)."""
+    from dism_b200.sharding import shard_operands
     s = SHAPE
     g = torch.Generator().manual_seed(seed)
     shape = (s['batch'], s['n'], s['heads'])
@@ -104,8 +113,9 @@ def make_inputs(seed, device):
     host['dout'] = torch.randn(*shape, s['dv'], generator=g).bfloat16()
     params['tau'] = torch.full((s['heads'],), .5)
     params['hard'] = torch.ones(s['batch'], s['heads'], dtype=torch.bool)
-    host = {k: v.pin_memory() for k, v in host.items()}
-    return host, {k: v.to(device) for k, v in params.items()}
+    mine = shard_operands({**host, **params}, rank, world)
+    host = {k: mine[k].pin_memory() for k in host}
+    return host, {k: mine[k].to(device) for k in params}
 
 
 def run_ours(args):
@@ -123,15 +133,19 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group('nccl', device_id=device)
     s = SHAPE
-    positions = s['batch'] * s['heads'] * s['n']
-    host, params = make_inputs(rank, device)
+    if s['heads'] % world:
+        raise SystemExit(f"{s['heads']} heads do not split evenly over {world} GPUs")
+    heads_here = s['heads'] // world
+    total_positions = s['batch'] * s['heads'] * s['n']  # the whole job, over all ranks
+    positions = s['batch'] * heads_here * s['n']        # this rank's share
+    host, params = make_inputs(0, device, rank, world)
     resident = {k: v.to(device) for k, v in host.items()}
     launches = [0]
 
     def step(x, stage_events=None):
         mark = (lambda: None) if stage_events is None else (lambda: stage_events.append(_event()))
         mark()
-        iq, ik = cu.labels(x['q'], params['eq']), cu.labels(x['k'], params['ek'])
+        iq, ik = cu.labels_pair(x['q'], params['eq'], x['k'], params['ek'])
         mark()
         out, norm = forward_hard(x['sq'], x['sk'], x['v'], iq, ik, params['hard'], params['tau'])
         mark()
@@ -139,9 +153,9 @@ def run_ours(args):
         grads = backward_hard(x['sq'], x['sk'], x['v'], x['dout'], iq, ik, params['hard'], norm,
                               dict(boundary=None, log_weights=lut))
         mark()
-        # labels x2; readout: log weights, index, tiles, forward; log weights; backward: their derivative,
-        # tiles (both plans in one launch), query-major, key-major, tau reduction (the index is the readout's)
-        launches[0] += 2 + 4 + 1 + 5
+        # labels of q and k (one launch); readout: log weights, index, tiles, forward; log weights; backward: their
+        # derivative, tiles (both plans in one launch), query-major, key-major, tau reduction (the index is the readout's)
+        launches[0] += 1 + 4 + 1 + 5
         return out, norm, grads
 
     def _event():
@@ -155,6 +169,11 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # A rank's inputs of one step must not sit in the 126 MB L2 when the step starts.  With few heads per GPU they
+    # would: then a 256 MB write flushes L2 before every step and the steps are timed one by one (the flush is not
+    # part of any step's time).
+    flush = sum(v.numel() * v.element_size() for v in resident.values()) < 2 * 126e6
+    scrub = torch.empty(256 << 20, dtype=torch.uint8, device=device) if flush else None
     for _ in range(args.warmup):
         step(resident)
     barrier()
@@ -162,13 +181,15 @@ def run_ours(args):
     stages = []
     with ClockSampler(local) as clocks:
         start = _event()
-        for _ in range(args.steps):
+        for index in range(args.steps):
+            if flush:
+                scrub.fill_(index & 255)
             events = []
             step(resident, events)
             stages.append(events)
         stop = _event()
         barrier()
-        elapsed_ms = start.elapsed_time(stop)
+        elapsed_ms = sum(e[0].elapsed_time(e[-1]) for e in stages) if flush else start.elapsed_time(stop)
         kernel_launches = launches[0]
         stage_ms = np.array([[a.elapsed_time(b) for a, b in zip(e, e[1:])] for e in stages]).mean(0)
 
@@ -247,40 +268,118 @@ def run_ours(args):
         e2e_ms = e2e_start.elapsed_time(e2e_stop)
         d2h = d2h[0]
 
-    times = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
+    flip_rate = label_flip_rate(cu, resident, params)
+    long_context = long_context_record(cu, forward_hard, device, rank, world, args)
+    times = torch.tensor([elapsed_ms, e2e_ms, long_context['ms_labels'] + long_context['ms_forward']], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = times.tolist()
+    elapsed_ms, e2e_ms, long_ms = times.tolist()
+    long_context['value'] = long_context['positions_per_gpu'] * world / (long_ms * 1e-3)  # all ranks' heads over the slowest rank's time
     if rank == 0:
         peak, peak_kind = measured_peak()
         ms_per_step = elapsed_ms / args.steps
         dominant = max(KERNEL_BYTES, key=lambda name: kernel_ms.get(name, 0.))
         achieved = KERNEL_BYTES[dominant] * positions / (kernel_ms[dominant] * 1e-3) / 1e9
+        traffic = measured_traffic().get(dominant) if world == 1 and s['batch'] == 8 else None
         line = {
             'metric': 'DISM fwd+bwd query-positions/s (labels + hard forward + hard backward)',
-            'value': positions * world / (ms_per_step * 1e-3), 'unit': 'positions/s', 'n_gpus': world,
+            'value': total_positions / (ms_per_step * 1e-3), 'unit': 'positions/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True,
-            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16 vectors, int32 labels, f32 accumulate',
+            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'bf16 vectors, int32 labels, f32 accumulate',
             'data': 'synthetic (seeded N(0,1) q,k,v,dO; silu(N(0,1)) codebooks and readout features)',
-            'config': {'workload': f"training shape B{s['batch']} H16 N8192 D64 R32 DV64 V512 per GPU, all rows hard, tau 0.5",
-                       'parallelism': f'heads sharded, 16 heads per GPU x {world}, no collective',
-                       'l2': 'inputs per step (671 MB) exceed L2'},
+            'config': {'workload': WORKLOAD.format(batch=s['batch']),
+                       'parallelism': f'16 heads / {world} = {heads_here} heads per GPU, one problem, no collective',
+                       'l2': f'inputs per step and GPU ({sum(v.numel() * v.element_size() for v in host.values()) / 1e6:.0f} MB) '
+                             + ('exceed L2' if heads_here >= 4 else 'are flushed from L2 by a 256 MB write between steps')},
             'stage_ms': {'labels': float(stage_ms[0]), 'forward': float(stage_ms[1]), 'backward': float(stage_ms[2])},
             'kernel_ms': kernel_ms,
             'per_gpu_value': positions / (ms_per_step * 1e-3),
-            'e2e': {'value': positions * world / (e2e_ms / e2e_steps * 1e-3), 'unit': 'positions/s',
+            'e2e': {'value': total_positions / (e2e_ms / e2e_steps * 1e-3), 'unit': 'positions/s',
                     'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'steps': e2e_steps},
             'gpu_launches': kernel_launches,
             'clocks': clocks.summary(),
             'roofline': {'bound': 'hbm', 'kernel': dominant, 'achieved': achieved, 'peak': peak,
-                         'unit': 'GB/s', 'frac': achieved / peak, 'peak_kind': peak_kind, 'traffic': TRAFFIC.get(dominant),
+                         'unit': 'GB/s', 'frac': achieved / peak, 'peak_kind': peak_kind, 'traffic': traffic,
                          'algorithmic_bytes_per_launch': KERNEL_BYTES[dominant] * positions,
                          'whole_step_frac': STEP_BYTES * positions / (ms_per_step * 1e-3) / 1e9 / peak},
+            'label_flip_rate': flip_rate,
+            'long_context': long_context,
             'cpu_baseline': cpu_baseline() if world == 1 else None,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def label_flip_rate(cu, x, params):
+    """Share of this rank's labels (q and k, benchmark data) that differ from torch.argmax of the FP32 einsum: the
+    kernel's labels are defined by a pinned FP32 summation order, the einsum's by cuBLAS; only near ties can differ."""
+    differing, total = 0, 0
+    for rows, codes in ((x['q'], params['eq']), (x['k'], params['ek'])):
+        mine = cu.labels(rows, codes)
+        for head in range(codes.size(0)):
+            logits = torch.einsum('bnd,vd->bnv', rows[:, :, head].float(), codes[head].float())
+            differing += int((logits.argmax(-1).int() != mine[:, head]).sum())
+            total += mine[:, head].numel()
+    return differing / total
+
+
+def long_context_record(cu, forward_hard, device, rank, world, args):
+    """The long-context workload on this rank: forward only on 4 heads of B1 H32 N131072 D64 R32 DV64 (with 8 ranks
+    that is the whole workload; with fewer, each rank still takes 4 heads).  Every 4096 positions the q rows of a
+    random 1024-long window repeat the k rows of an earlier window, which forces 1024-long label runs.  Rank 0
+    checks one head against the reference's own native CPU forward (oracle/_ref), all 131072 rows."""
+    from dism_b200 import _lib
+    b, h, n, d, r, dv, vocab = 1, 4, 131072, 64, 32, 64, 512
+    g = torch.Generator(device=device).manual_seed(100 + rank)
+    k = torch.randn(b, n, h, d, generator=g, device=device).bfloat16()
+    q = torch.randn(b, n, h, d, generator=g, device=device).bfloat16()
+    rng = np.random.default_rng(100 + rank)
+    for start in range(4096, n, 4096):
+        target = start + int(rng.integers(0, 3072))
+        source = int(rng.integers(0, target - 1024))
+        q[:, target:target + 1024] = k[:, source:source + 1024]
+    codebook = torch.nn.functional.silu(torch.randn(h, vocab, d, generator=g, device=device)).bfloat16()
+    sq, sk = [(torch.nn.functional.silu(torch.randn(b, n, h, r, generator=g, device=device)) * .4).bfloat16() for _ in range(2)]
+    v = torch.randn(b, n, h, dv, generator=g, device=device).bfloat16()
+    hard, tau = torch.ones(b, h, dtype=torch.bool, device=device), torch.full((h,), .05, device=device)
+
+    def timed(fn):
+        for _ in range(max(1, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / args.steps
+
+    iq, ik = cu.labels_pair(q, codebook, k, codebook)  # one shared codebook, so repeated rows get equal labels
+    ms_labels = timed(lambda: cu.labels_pair(q, codebook, k, codebook))
+    ms_forward = timed(lambda: forward_hard(sq, sk, v, iq, ik, hard, tau))
+    _lib.load().dism_profile_enable(1)
+    out, norm = forward_hard(sq, sk, v, iq, ik, hard, tau)
+    torch.cuda.synchronize()
+    kernel_ms = dict(_lib.kernel_timings())
+    _lib.load().dism_profile_enable(0)
+    record = {'workload': 'long context forward: 4 heads per GPU of B1 H32 N131072 D64 R32 DV64 V512, planted 1024-long runs, tau 0.05',
+              'metric': 'query positions/s (labels + hard forward)', 'positions_per_gpu': b * h * n, 'ms_labels': ms_labels,
+              'ms_forward': ms_forward, 'kernel_ms': kernel_ms, 'max_log2_normaliser': float(norm.max()), 'parity': None}
+    if rank == 0:
+        from oracle import dism_oracle
+        if dism_oracle.reference_lib() is None:
+            record['parity'] = 'not checked: oracle/_ref (the reference native CPU forward) was not built'
+        else:
+            f = lambda t: t[0, :, 0].float().cpu().numpy()
+            want = dism_oracle.reference_forward_many(f(sq)[None], f(sk)[None], f(v)[None], iq[0, 0].cpu().numpy()[None],
+                                                      ik[0, 0].cpu().numpy()[None], np.full(1, .05), threads=1)[0]
+            error = np.abs(out[0, :, 0].float().cpu().numpy() - want)
+            bound = .008 + .025 * np.abs(want)  # the forward tests' tolerance
+            record['parity'] = {'against': 'reference native CPU forward (Builder + execute<float>), head 0, all 131072 rows',
+                                'max_abs_error': float(error.max()), 'rows_outside_tolerance': int((error > bound).any(-1).sum())}
+    return record
 
 
 def cpu_inputs(heads, seed=0):
@@ -301,7 +400,9 @@ def cpu_inputs(heads, seed=0):
 
 
 def cpu_sample(x, threads):
-    """Time the CPU port on prepared operands; returns seconds per stage (inputs are not timed)."""
+    """Time the CPU path on prepared operands; returns seconds per stage (inputs are not timed).  The forward leg runs
+    the reference's own native CPU forward (its planner and executor in float32, one (batch, head) sequence per task
+    on `threads` host threads) when oracle/_ref was built, else the C port; labels and backward are the port."""
     from oracle import dism_oracle as o
     # the discretiser on the CPU side is a plain fp32 GEMM + argmax (what the reference's torch path does)
     t0 = time.perf_counter()
@@ -310,28 +411,35 @@ def cpu_sample(x, threads):
     ik = torch.argmax(torch.einsum('bnhd,hvd->bnhv', torch.from_numpy(x['k']), torch.from_numpy(x['ek'])), -1)
     iq, ik = [t.transpose(1, 2).contiguous().int().numpy() for t in (iq, ik)]
     t1 = time.perf_counter()
-    o.forward(x['sq'], x['sk'], x['v'], iq, ik, x['hard'], x['tau'], threads=threads)
+    native = o.reference_lib() is not None
+    if native:
+        per_head = lambda a: np.ascontiguousarray(a[0].transpose(1, 0, 2))  # [N,H,C] -> [H,N,C]
+        o.reference_forward_many(per_head(x['sq']), per_head(x['sk']), per_head(x['v']), iq[0], ik[0],
+                                 x['tau'].astype(np.float64), threads=threads)
+    else:
+        o.forward(x['sq'], x['sk'], x['v'], iq, ik, x['hard'], x['tau'], threads=threads)
     t2 = time.perf_counter()
     o.backward(x['sq'], x['sk'], x['v'], x['dout'], iq, ik, x['hard'], x['tau'], threads=threads)
     t3 = time.perf_counter()
-    native = None
-    if o.reference_lib() is not None:
-        t = time.perf_counter()
-        o.reference_forward(x['sq'][0, :, 0], x['sk'][0, :, 0], x['v'][0, :, 0], iq[0, 0], ik[0, 0], .5)
-        native = time.perf_counter() - t
-    return dict(labels=t1 - t0, forward=t2 - t1, backward=t3 - t2, native_forward_one_head=native)
+    return dict(labels=t1 - t0, forward=t2 - t1, backward=t3 - t2), native
+
+
+def cpu_legs(native):
+    return {'labels': 'port (torch fp32 GEMM + argmax)',
+            'forward': 'reference (native planner + execute<float>)' if native else 'port (C restatement of the dense recurrence)',
+            'backward': 'port (C restatement of the dense recurrence; the reference has no native CPU backward)'}
 
 
 def cpu_baseline(heads=None):
     cores = os.cpu_count() or 1
-    heads = heads or max(cores, 8)
+    heads = heads or min(128, 4 * max(cores, 8))
     cpu_sample(cpu_inputs(2), cores)  # warm caches and the thread pool
-    t = cpu_sample(cpu_inputs(heads), cores)
+    t, native = cpu_sample(cpu_inputs(heads), cores)
     total = t['labels'] + t['forward'] + t['backward']
-    return {'value': heads * SHAPE['n'] / total, 'unit': 'positions/s', 'cores': cores, 'kind': 'port',
-            'sample': f'{heads} of the 128 (batch, head) slices at N=8192, all {cores} host threads, '
-                      f'oracle C port (dense L recurrence, weights only where labels match) + torch fp32 argmax for labels',
-            'seconds': {k: v for k, v in t.items() if v is not None}}
+    return {'value': heads * SHAPE['n'] / total, 'unit': 'positions/s', 'cores': cores, 'kind': 'reference' if native else 'port',
+            'legs': cpu_legs(native),
+            'sample': f'{heads} of the 128 (batch, head) slices at N=8192, one slice per task on all {cores} host threads',
+            'seconds': t}
 
 
 def run_reference(args):
@@ -339,26 +447,26 @@ def run_reference(args):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    heads = max(cores, 8)
+    heads = min(128, 4 * max(cores, 8))
     small, inputs = cpu_inputs(2), cpu_inputs(heads)
     for _ in range(args.warmup):
         cpu_sample(small, cores)
-    native, elapsed = [], 0.
+    elapsed, native, seconds = 0., False, {}
     for step in range(args.steps):
-        t = cpu_sample(inputs, cores)
+        t, native = cpu_sample(inputs, cores)
         elapsed += t['labels'] + t['forward'] + t['backward']
-        native.append(t['native_forward_one_head'])
+        seconds = {k: seconds.get(k, 0.) + v / args.steps for k, v in t.items()}
     value = heads * SHAPE['n'] * args.steps / elapsed
-    base = {'value': value, 'unit': 'positions/s', 'cores': cores, 'kind': 'port',
-            'sample': f'each step = {heads} of the 128 (batch, head) slices at N=8192 on all {cores} host threads; '
-                      'C port of the reference dense recurrence (fwd+bwd) + torch fp32 argmax labels',
-            'reference_native_forward_one_head_s': float(np.median([x for x in native if x])) if any(native) else None}
+    base = {'value': value, 'unit': 'positions/s', 'cores': cores, 'kind': 'reference' if native else 'port', 'legs': cpu_legs(native),
+            'sample': f'each step = {heads} of the 128 (batch, head) slices at N=8192, one slice per task on all {cores} host threads',
+            'seconds': seconds}
     print(json.dumps({
         'impl': 'reference', 'metric': 'DISM fwd+bwd query-positions/s (labels + hard forward + hard backward)',
         'value': value, 'unit': 'positions/s', 'n_gpus': int(os.environ.get('WORLD_SIZE', 1)), 'steps': args.steps,
-        'warmup': args.warmup, 'ms_per_step': elapsed / args.steps * 1e3, 'higher_is_better': True, 'scaling': 'weak',
-        'vs_baseline': None, 'dtype': 'f64 accumulate over bf16-rounded f32 inputs', 'data': 'synthetic',
-        'config': {'workload': 'training shape B8 H16 N8192 D64 R32 DV64 V512, bounded sample of (batch, head) slices'},
+        'warmup': args.warmup, 'ms_per_step': elapsed / args.steps * 1e3, 'higher_is_better': True, 'scaling': 'strong',
+        'vs_baseline': None, 'dtype': 'f32 (reference forward), f64 accumulate over bf16-rounded f32 inputs (port)', 'data': 'synthetic',
+        'config': {'workload': WORKLOAD.format(batch=SHAPE['batch']),
+                   'sample': f'{heads} of the 128 (batch, head) slices per step on the host cores'},
         'cpu_baseline': base,
         'e2e': {'value': value, 'unit': 'positions/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
 

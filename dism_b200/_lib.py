@@ -12,17 +12,18 @@ SIGNATURES = {
     'dism_last_error': (_c.c_char_p, []),
     'dism_abi_version': (_I, []),
     'dism_labels': (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _P]),
+    'dism_labels_pair': (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     'dism_labels_fault': (_I, [_P]),
     'dism_labels_wait_selftest': (_I, [_I, _P, _P]),
     'dism_hard_summary': (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P]),
     'dism_hard_chunk': (_I, [_P, _P, _I, _I, _P]),
     'dism_hard_log_weights': (_I, [_P, _I, _I, _P, _P]),
     'dism_hard_readout_workspace': (_Z, [_I, _I, _I]),
-    'dism_hard_readout': (_I, [_P] * 8 + [_I, _P] + [_I] * 7 + [_P, _P, _P, _Z, _P]),
+    'dism_hard_readout': (_I, [_P] * 8 + [_I, _I, _P] + [_I] * 7 + [_P, _P, _P, _Z, _P]),
     'dism_hard_readout_static': (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     'dism_hard_readout_static_error': (_c.c_char_p, []),
     'dism_hard_backward_workspace': (_Z, [_I, _I, _I, _I]),
-    'dism_hard_backward': (_I, [_P] * 9 + [_I, _P, _I, _P] + [_I] * 6 + [_P, _P, _P, _P, _P, _Z, _P, _P]),
+    'dism_hard_backward': (_I, [_P] * 9 + [_I, _I, _P, _I, _P] + [_I] * 6 + [_P, _P, _P, _P, _P, _Z, _P, _P]),
     'dism_longest_match_workspace': (_Z, [_I, _I]),
     'dism_profile_enable': (_I, [_I]),
     'dism_profile_count': (_I, []),

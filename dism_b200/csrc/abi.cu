@@ -25,8 +25,10 @@ int cuda_status(cudaError_t status, const char* what) {
 bool aligned(const void* p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) & (bytes - 1)) == 0; }
 
 int check_shape(int batch, int heads, int n) {
-    if (batch <= 0 || heads <= 0 || int64_t(batch) * heads > INT_MAX || n <= 0 || n > INT_MAX - 256 || n % 256)
+    if (batch <= 0 || heads <= 0 || n <= 0 || n > INT_MAX - 256 || n % 256)
         return fail(DISM_EINVAL, "positive dimensions and 256-aligned sequence length required");
+    if (int64_t(batch) * heads > 65535)  // (batch, head) slices are one grid dimension of every kernel
+        return fail(DISM_EINVAL, "batch * heads must not exceed 65535");
     return DISM_OK;
 }
 int check_dims(int r, int dv) {
@@ -85,7 +87,7 @@ int dism_profile_read(int index, char* name, int capacity, float* milliseconds) 
 }
 
 const char* dism_last_error(void) { return last_error; }
-int dism_abi_version(void) { return 5; }
+int dism_abi_version(void) { return 6; }
 
 int dism_labels(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t* labels, void* stream) {
@@ -93,10 +95,24 @@ int dism_labels(const void* x, const void* codebook, int batch, int n, int heads
     if (batch <= 0 || n <= 0 || heads <= 0 || vocab <= 0 || int64_t(batch) * heads > 65535)
         return fail(DISM_EINVAL, "positive dimensions required (batch*heads <= 65535)");
     if (d != 32 && d != 64 && d != 128) return fail(DISM_EUNSUPPORTED, "unsupported label width D=%d", d);
-    if (!aligned(x, 16)) return fail(DISM_EINVAL, "x must be 16-byte aligned");
+    if (!aligned(x, 16) || !aligned(codebook, 16)) return fail(DISM_EINVAL, "x and codebook must be 16-byte aligned");
     return cuda_status(dism::launch_labels(static_cast<const __nv_bfloat16*>(x),
                                            static_cast<const __nv_bfloat16*>(codebook), batch, n, heads, d, vocab,
                                            labels, static_cast<cudaStream_t>(stream)), "labels");
+}
+
+int dism_labels_pair(const void* x0, const void* codebook0, int32_t* labels0, const void* x1, const void* codebook1,
+                     int32_t* labels1, int batch, int n, int heads, int d, int vocab, void* stream) {
+    if (!x0 || !codebook0 || !labels0 || !x1 || !codebook1 || !labels1) return fail(DISM_EINVAL, "null pointer");
+    if (batch <= 0 || n <= 0 || heads <= 0 || vocab <= 0 || int64_t(batch) * heads > 65535)
+        return fail(DISM_EINVAL, "positive dimensions required (batch*heads <= 65535)");
+    if (d != 32 && d != 64 && d != 128) return fail(DISM_EUNSUPPORTED, "unsupported label width D=%d", d);
+    if (!aligned(x0, 16) || !aligned(codebook0, 16) || !aligned(x1, 16) || !aligned(codebook1, 16))
+        return fail(DISM_EINVAL, "x and codebook must be 16-byte aligned");
+    using bf = __nv_bfloat16;
+    return cuda_status(dism::launch_labels_pair(static_cast<const bf*>(x0), static_cast<const bf*>(codebook0), labels0,
+                                                static_cast<const bf*>(x1), static_cast<const bf*>(codebook1), labels1, batch, n, heads,
+                                                d, vocab, static_cast<cudaStream_t>(stream)), "labels");
 }
 
 int dism_labels_fault(int* code) {
@@ -135,11 +151,17 @@ int dism_hard_log_weights(const float* tau, int heads, int n, float* lut, void* 
                        "hard_log_weights");
 }
 
-static int check_documents(const int32_t* documents, int hard_rows, const int32_t* boundary, int batch, int n) {
+static int check_documents(const int32_t* documents, int hard_rows, int longest_document, int lut_stride, const int32_t* boundary,
+                           int batch, int n) {
     if (!documents) {
         if (hard_rows != batch) return fail(DISM_EINVAL, "fixed hard must be [B,H]");
+        if (lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
         return DISM_OK;
     }
+    // the kernels index the tables with run lengths up to the longest document
+    if (longest_document <= 0 || longest_document > n || longest_document % 256)
+        return fail(DISM_EINVAL, "longest document must be a positive 256-aligned length within the pack");
+    if (lut_stride <= longest_document) return fail(DISM_EINVAL, "hard log-weight table is too short for the longest document");
     if (batch != 1) return fail(DISM_EINVAL, "packed labels/layout length mismatch: packed layouts use one batch row");
     if (boundary) return fail(DISM_EUNSUPPORTED, "the boundary rectangle is not used with packed layouts; pass NULL");
     if (hard_rows <= 0 || n % hard_rows || (n / hard_rows) % 256)
@@ -150,15 +172,14 @@ static int check_documents(const int32_t* documents, int hard_rows, const int32_
 
 int dism_hard_readout(const void* sq, const void* sk, const void* v, const int32_t* iq, const int32_t* ik,
                       const uint8_t* hard, const int32_t* boundary, const int32_t* documents, int hard_rows,
-                      const float* lut, int lut_stride, int batch,
+                      int longest_document, const float* lut, int lut_stride, int batch,
                       int n, int heads, int r, int dv, int ctas, void* out, float* lse2, void* workspace,
                       size_t workspace_bytes, void* stream) {
     if (int status = check_shape(batch, heads, n)) return status;
     if (int status = check_dims(r, dv)) return status;
     if (!sq || !sk || !v || !iq || !ik || !hard || !lut || !out || !lse2) return fail(DISM_EINVAL, "null pointer");
     if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
-    if (!documents && lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
-    if (int status = check_documents(documents, hard_rows, boundary, batch, n)) return status;
+    if (int status = check_documents(documents, hard_rows, longest_document, lut_stride, boundary, batch, n)) return status;
     if (!aligned(sq, 16) || !aligned(sk, 16) || !aligned(v, 16) || !aligned(out, 16))
         return fail(DISM_EINVAL, "vector tensors must be 16-byte aligned");
     if (!workspace || workspace_bytes < dism::hard_forward_workspace_bytes(batch, heads, n) || !aligned(workspace, 256))
@@ -185,7 +206,7 @@ size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride)
 
 int dism_hard_backward(const void* sq, const void* sk, const void* v, const void* dout, const int32_t* iq,
                        const int32_t* ik, const uint8_t* hard, const int32_t* boundary, const int32_t* documents,
-                       int hard_rows, const float* lut, int lut_stride, const float* lse2, int batch, int n, int heads,
+                       int hard_rows, int longest_document, const float* lut, int lut_stride, const float* lse2, int batch, int n, int heads,
                        int r, int dv, int ctas,
                        float* dsq, void* dsk, void* dv_out, float* dtau, void* workspace, size_t workspace_bytes,
                        const void* readout_workspace, void* stream) {
@@ -195,8 +216,7 @@ int dism_hard_backward(const void* sq, const void* sk, const void* v, const void
         !workspace)
         return fail(DISM_EINVAL, "null pointer");
     if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
-    if (!documents && lut_stride <= n) return fail(DISM_EINVAL, "hard log-weight table is too short");
-    if (int status = check_documents(documents, hard_rows, boundary, batch, n)) return status;
+    if (int status = check_documents(documents, hard_rows, longest_document, lut_stride, boundary, batch, n)) return status;
     if (workspace_bytes < dism::hard_backward_workspace_bytes(batch, heads, n, lut_stride) || !aligned(workspace, 256))
         return fail(DISM_EINVAL, "workspace too small or misaligned (see dism_hard_backward_workspace)");
     if (readout_workspace && !aligned(readout_workspace, 256)) return fail(DISM_EINVAL, "readout workspace misaligned");

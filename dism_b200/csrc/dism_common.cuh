@@ -130,8 +130,12 @@ cudaError_t launch_labels(const __nv_bfloat16* x, const __nv_bfloat16* codebook,
                           int d, int vocab, int* labels, cudaStream_t stream);
 // Tensor-memory pipeline for the shapes it covers (labels_tcgen05.cu); launch_labels picks it when it can.
 bool labels_tcgen05_covers(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab);
-cudaError_t launch_labels_tcgen05(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int batch, int n, int heads,
-                                  int d, int vocab, int* labels, cudaStream_t stream);
+cudaError_t launch_labels_tcgen05(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int* labels, const __nv_bfloat16* x1,
+                                  const __nv_bfloat16* codebook1, int* labels1, int batch, int n, int heads, int d, int vocab,
+                                  cudaStream_t stream);
+cudaError_t launch_labels_pair(const __nv_bfloat16* x0, const __nv_bfloat16* codebook0, int* labels0, const __nv_bfloat16* x1,
+                               const __nv_bfloat16* codebook1, int* labels1, int batch, int n, int heads, int d, int vocab,
+                               cudaStream_t stream);
 cudaError_t read_labels_fault(int* code);
 cudaError_t run_wait_selftest(int code, int* outcome, cudaStream_t stream);
 cudaError_t launch_hard_summary(const int* iq, const int* ik, const uint8_t* hard, int batch, int heads, int n,

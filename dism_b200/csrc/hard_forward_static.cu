@@ -66,7 +66,7 @@ int dism_hard_readout_static(const void* sq, const void* sk, const void* v, cons
         snprintf(static_error, sizeof(static_error), "built-in scratch unavailable: %s", cudaGetErrorString(status));
         return DISM_ECUDA;
     }
-    const int code = dism_hard_readout(sq, sk, v, iq, ik, hard, boundary, nullptr, batch, lut, lut_stride, batch, n, heads, r, dv, ctas,
+    const int code = dism_hard_readout(sq, sk, v, iq, ik, hard, boundary, nullptr, batch, n, lut, lut_stride, batch, n, heads, r, dv, ctas,
                                        out, lse2, device_address[device], size_t(DISM_READOUT_STATIC_BYTES), stream);
     if (code) snprintf(static_error, sizeof(static_error), "%s", dism_last_error());
     return code;

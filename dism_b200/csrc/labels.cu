@@ -216,7 +216,7 @@ __global__ __launch_bounds__(LABEL_ROWS) void labels_kernel(const __nv_bfloat16*
 cudaError_t launch_labels(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int batch, int n, int heads,
                           int d, int vocab, int* labels, cudaStream_t stream) {
     if (labels_tcgen05_covers(x, codebook, batch, n, heads, d, vocab))
-        return launch_labels_tcgen05(x, codebook, batch, n, heads, d, vocab, labels, stream);
+        return launch_labels_tcgen05(x, codebook, labels, nullptr, nullptr, nullptr, batch, n, heads, d, vocab, stream);
     dim3 grid((n + LABEL_ROWS - 1) / LABEL_ROWS, batch * heads);
     KernelTimer timer("labels", stream);
     if (d == 32) labels_kernel<32><<<grid, LABEL_ROWS, 0, stream>>>(x, codebook, n, heads, vocab, labels);
@@ -224,6 +224,17 @@ cudaError_t launch_labels(const __nv_bfloat16* x, const __nv_bfloat16* codebook,
     else if (d == 128) labels_kernel<128><<<grid, LABEL_ROWS, 0, stream>>>(x, codebook, n, heads, vocab, labels);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
+}
+
+// Two tensors of the same shape (the q and the k side of a step), in one launch where the tensor-memory pipeline covers both.
+cudaError_t launch_labels_pair(const __nv_bfloat16* x0, const __nv_bfloat16* codebook0, int* labels0, const __nv_bfloat16* x1,
+                               const __nv_bfloat16* codebook1, int* labels1, int batch, int n, int heads, int d, int vocab,
+                               cudaStream_t stream) {
+    if (2 * int64_t(batch) * heads <= 65535 && labels_tcgen05_covers(x0, codebook0, batch, n, heads, d, vocab) &&
+        labels_tcgen05_covers(x1, codebook1, batch, n, heads, d, vocab))
+        return launch_labels_tcgen05(x0, codebook0, labels0, x1, codebook1, labels1, batch, n, heads, d, vocab, stream);
+    const cudaError_t status = launch_labels(x0, codebook0, batch, n, heads, d, vocab, labels0, stream);
+    return status != cudaSuccess ? status : launch_labels(x1, codebook1, batch, n, heads, d, vocab, labels1, stream);
 }
 
 }  // namespace dism

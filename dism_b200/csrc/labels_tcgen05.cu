@@ -348,13 +348,22 @@ __device__ __noinline__ float pinned_logit(const __nv_bfloat16* __restrict__ row
     return acc;
 }
 
+// The tensors of one launch: one (x, codebook, labels) triple, or two of the same shape (the q and the k side of a
+// step), which then share one pipeline fill and drain.  Tiles are numbered side by side: `heads` heads of the first
+// triple, then those of the second; a "virtual head" below is that running number.
+struct LabelSides {
+    const __nv_bfloat16* x[2];
+    const __nv_bfloat16* codebook[2];
+    int* labels[2];
+};
+
 template <int D>
-__global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map,
-                                                                    const __grid_constant__ CUtensorMap code_map,
-                                                                    const __nv_bfloat16* __restrict__ x,
-                                                                    const __nv_bfloat16* __restrict__ codebook, int n, int heads,
-                                                                    int vocab, int tiles_per_head, int total_tiles,
-                                                                    int* __restrict__ labels) {
+__global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map0,
+                                                                    const __grid_constant__ CUtensorMap code_map0,
+                                                                    const __grid_constant__ CUtensorMap x_map1,
+                                                                    const __grid_constant__ CUtensorMap code_map1,
+                                                                    const LabelSides sides, int n, int heads,
+                                                                    int vocab, int tiles_per_head, int total_tiles) {
     constexpr int KBLOCKS = D / KBLOCK, A_BYTES = KBLOCKS * BLOCK_BYTES, A_STAGES = D == 64 ? 4 : 2;
     extern __shared__ unsigned char raw[];
     unsigned char* base = raw + ((1024u - (shared_address(raw) & 1023u)) & 1023u);  // swizzled tiles: 1024-byte aligned
@@ -403,14 +412,18 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
         if (lane == 0) {
             int loaded_head = -1, code_loads = 0, step = 0;
             for (int tile = first_tile; tile < last_tile; ++tile, ++step) {
-                const int head = tile / tiles_per_head, row = (tile % tiles_per_head) * TILE_ROWS;
+                const int head = tile / tiles_per_head, row = (tile % tiles_per_head) * TILE_ROWS;  // virtual head
+                const bool second = head >= heads;
+                const int real_head = second ? head - heads : head;
+                const CUtensorMap* x_map = second ? &x_map1 : &x_map0;
+                const CUtensorMap* code_map = second ? &code_map1 : &code_map0;
                 if (head != loaded_head) {
                     // the tensor core must have finished with the previous head's codes
                     if (code_loads > 0 && !barrier_wait(&control.code_empty, (code_loads - 1) & 1, control, 1)) break;
                     barrier_expect(&control.code_full, uint32_t(code_tiles * KBLOCKS * CODE_BLOCK_BYTES));
                     for (int j = 0; j < code_tiles; ++j)
                         for (int kb = 0; kb < KBLOCKS; ++kb)
-                            tma_load(codes + (j * KBLOCKS + kb) * CODE_BLOCK_BYTES, &code_map, kb * KBLOCK, head * vocab + j * TILE_CODES,
+                            tma_load(codes + (j * KBLOCKS + kb) * CODE_BLOCK_BYTES, code_map, kb * KBLOCK, real_head * vocab + j * TILE_CODES,
                                      &control.code_full);
                     loaded_head = head;
                     ++code_loads;
@@ -419,7 +432,7 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 if (!barrier_wait(&control.a_empty[stage], ((step / A_STAGES) & 1) ^ 1, control, 2)) break;
                 barrier_expect(&control.a_full[stage], uint32_t(A_BYTES));
                 for (int kb = 0; kb < KBLOCKS; ++kb)
-                    tma_load(a_ring + stage * A_BYTES + kb * BLOCK_BYTES, &x_map, head * D + kb * KBLOCK, row, &control.a_full[stage]);
+                    tma_load(a_ring + stage * A_BYTES + kb * BLOCK_BYTES, x_map, real_head * D + kb * KBLOCK, row, &control.a_full[stage]);
             }
             if (*reinterpret_cast<volatile int*>(&control.abort)) {  // let the copies in flight land
                 if (code_loads > 0) barrier_settle(&control.code_full, (code_loads - 1) & 1);
@@ -517,7 +530,10 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
             ok = barrier_wait(&control.exchange_full[side], (step >> 1) & 1, control, 8);
             if (!ok) break;
             const float code_max = control.code_max[step % (2 * NORM_RING)];
-            const __nv_bfloat16* head_codes = codebook + int64_t(head) * vocab * D;
+            const int which = head >= heads, real_head = head - which * heads;
+            const __nv_bfloat16* x = sides.x[which];
+            int* labels = sides.labels[which];
+            const __nv_bfloat16* head_codes = sides.codebook[which] + int64_t(real_head) * vocab * D;
 #pragma unroll 1
             for (int quarter = (warp - FINISH_WARP) * 2; quarter < (warp - FINISH_WARP) * 2 + 2; ++quarter) {
                 const int row_in_tile = quarter * 32 + lane, position = tile_in_batch * TILE_ROWS + row_in_tile;
@@ -528,7 +544,7 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 Candidates all{best, 0, 0, 0};
 #pragma unroll
                 for (int g = 0; g < EPILOGUE_GROUPS; ++g) merge_candidates(all, part[g], best, delta);
-                if (all.count == 1) labels[(int64_t(batch) * heads + head) * n + position] = all.a;
+                if (all.count == 1) labels[(int64_t(batch) * heads + real_head) * n + position] = all.a;
                 const int id = tile * TILE_ROWS + row_in_tile;
                 // near ties go to the pair list while it has room, everything else to the crowded list
                 unsigned pair_mask = __ballot_sync(FULL, all.count == 2);
@@ -557,8 +573,8 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                     } else {  // list full: recompute here
                         for (unsigned rest = crowded_mask; rest; rest &= rest - 1) {
                             const int p = tile_in_batch * TILE_ROWS + quarter * 32 + __ffs(rest) - 1;
-                            const int label = pinned_label<D>(x + ((int64_t(batch) * n + p) * heads + head) * D, head_codes, vocab, lane);
-                            if (lane == 0) labels[(int64_t(batch) * heads + head) * n + p] = label;
+                            const int label = pinned_label<D>(x + ((int64_t(batch) * n + p) * heads + real_head) * D, head_codes, vocab, lane);
+                            if (lane == 0) labels[(int64_t(batch) * heads + real_head) * n + p] = label;
                         }
                     }
                 }
@@ -652,10 +668,11 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 const int count = *reinterpret_cast<volatile int*>(&control.pair_count[list]);
                 for (int entry = threadIdx.x; entry < count; entry += EPILOGUE_WARPS * 32) {
                     const int id = control.pairs[list][entry][0], a = control.pairs[list][entry][1], b = control.pairs[list][entry][2];
-                    const int tile = id / TILE_ROWS, head = tile / tiles_per_head;
+                    const int tile = id / TILE_ROWS, which = tile / tiles_per_head >= heads, head = tile / tiles_per_head - which * heads;
                     const int r = (tile % tiles_per_head) * TILE_ROWS + id % TILE_ROWS;
-                    const __nv_bfloat16* source = x + (int64_t(r) * heads + head) * D;
-                    const __nv_bfloat16* head_codes = codebook + int64_t(head) * vocab * D;
+                    const __nv_bfloat16* source = sides.x[which] + (int64_t(r) * heads + head) * D;
+                    const __nv_bfloat16* head_codes = sides.codebook[which] + int64_t(head) * vocab * D;
+                    int* labels = sides.labels[which];
                     const float logit_a = pinned_logit<D>(source, head_codes + int64_t(a) * D);
                     const float logit_b = pinned_logit<D>(source, head_codes + int64_t(b) * D);
                     const bool first_wins = logit_a > logit_b || (logit_a == logit_b && a < b);
@@ -668,9 +685,11 @@ __global__ __launch_bounds__(THREADS, 1) void labels_tcgen05_kernel(const __grid
                 for (int entry = 0; entry < count; ++entry, ++turn) {
                     if (turn % EPILOGUE_WARPS != warp) continue;
                     const int id = control.crowded[list][entry], tile = id / TILE_ROWS;
-                    const int head = tile / tiles_per_head, r = (tile % tiles_per_head) * TILE_ROWS + id % TILE_ROWS;
-                    const int label = pinned_label<D>(x + (int64_t(r) * heads + head) * D, codebook + int64_t(head) * vocab * D, vocab, lane);
-                    if (lane == 0) labels[(int64_t(r / n) * heads + head) * n + r % n] = label;
+                    const int which = tile / tiles_per_head >= heads, head = tile / tiles_per_head - which * heads;
+                    const int r = (tile % tiles_per_head) * TILE_ROWS + id % TILE_ROWS;
+                    const int label = pinned_label<D>(sides.x[which] + (int64_t(r) * heads + head) * D,
+                                                      sides.codebook[which] + int64_t(head) * vocab * D, vocab, lane);
+                    if (lane == 0) sides.labels[which][(int64_t(r / n) * heads + head) * n + r % n] = label;
                 }
             }
         }
@@ -715,13 +734,14 @@ int shared_bytes(int d, int vocab) { return vocab * d * 2 + (d == 64 ? 4 : 2) * 
 constexpr int SHARED_LIMIT = 227 * 1024;
 
 template <int D>
-cudaError_t launch(const CUtensorMap& x_map, const CUtensorMap& code_map, const __nv_bfloat16* x, const __nv_bfloat16* codebook,
-                   int n, int heads, int vocab, int tiles_per_head, int total_tiles, int* labels, cudaStream_t stream) {
+cudaError_t launch(const CUtensorMap (&x_map)[2], const CUtensorMap (&code_map)[2], const LabelSides& sides, int n, int heads, int vocab,
+                   int tiles_per_head, int total_tiles, cudaStream_t stream) {
     const int bytes = shared_bytes(D, vocab);
     const cudaError_t status = cudaFuncSetAttribute(labels_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (status != cudaSuccess) return status;
     const int grid = total_tiles < device_sm_count() ? total_tiles : device_sm_count();
-    labels_tcgen05_kernel<D><<<grid, THREADS, bytes, stream>>>(x_map, code_map, x, codebook, n, heads, vocab, tiles_per_head, total_tiles, labels);
+    labels_tcgen05_kernel<D><<<grid, THREADS, bytes, stream>>>(x_map[0], code_map[0], x_map[1], code_map[1], sides, n, heads, vocab,
+                                                               tiles_per_head, total_tiles);
     return cudaGetLastError();
 }
 
@@ -733,16 +753,21 @@ bool labels_tcgen05_covers(const void* x, const void* codebook, int batch, int n
            reinterpret_cast<uintptr_t>(codebook) % 16 == 0 && encode_tiled() != nullptr;
 }
 
-cudaError_t launch_labels_tcgen05(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int batch, int n, int heads, int d,
-                                  int vocab, int* labels, cudaStream_t stream) {
-    CUtensorMap x_map, code_map;
-    if (!make_map(&x_map, x, uint64_t(batch) * n, uint64_t(heads) * d, uint64_t(heads) * d, TILE_ROWS) ||
-        !make_map(&code_map, codebook, uint64_t(heads) * vocab, uint64_t(d), uint64_t(d), TILE_CODES))
-        return cudaErrorInvalidValue;
-    const int tiles_per_head = int(int64_t(batch) * n / TILE_ROWS), total_tiles = tiles_per_head * heads;
-    KernelTimer timer("labels", stream);
-    if (d == 64) return launch<64>(x_map, code_map, x, codebook, n, heads, vocab, tiles_per_head, total_tiles, labels, stream);
-    return launch<128>(x_map, code_map, x, codebook, n, heads, vocab, tiles_per_head, total_tiles, labels, stream);
+// One triple (x1 == nullptr) or two triples of the same shape in one launch.
+cudaError_t launch_labels_tcgen05(const __nv_bfloat16* x, const __nv_bfloat16* codebook, int* labels, const __nv_bfloat16* x1,
+                                  const __nv_bfloat16* codebook1, int* labels1, int batch, int n, int heads, int d, int vocab,
+                                  cudaStream_t stream) {
+    const int count = x1 ? 2 : 1;
+    const LabelSides sides{{x, x1 ? x1 : x}, {codebook, x1 ? codebook1 : codebook}, {labels, x1 ? labels1 : labels}};
+    CUtensorMap x_map[2], code_map[2];
+    for (int side = 0; side < 2; ++side)
+        if (!make_map(&x_map[side], sides.x[side], uint64_t(batch) * n, uint64_t(heads) * d, uint64_t(heads) * d, TILE_ROWS) ||
+            !make_map(&code_map[side], sides.codebook[side], uint64_t(heads) * vocab, uint64_t(d), uint64_t(d), TILE_CODES))
+            return cudaErrorInvalidValue;
+    const int tiles_per_head = int(int64_t(batch) * n / TILE_ROWS), total_tiles = tiles_per_head * heads * count;
+    KernelTimer timer(count == 2 ? "labels_pair" : "labels", stream);
+    if (d == 64) return launch<64>(x_map, code_map, sides, n, heads, vocab, tiles_per_head, total_tiles, stream);
+    return launch<128>(x_map, code_map, sides, n, heads, vocab, tiles_per_head, total_tiles, stream);
 }
 
 // First bounded wait that ran out in any earlier launch on this device (0: none).  Synchronises the device.

@@ -254,26 +254,29 @@ def _check_lut(lut, h, n, device):
 
 def _layout_arguments(table, hard, boundary, lut, b, h, n, device):
     """Validates hard flags and LUT for the fixed or the packed layout; returns the document-table
-    pointer (0 = fixed) and the number of hard rows."""
+    pointer (0 = fixed), the number of hard rows and the longest document."""
     if table is None:
         _check_hard(hard, device, b, h)
         _check_lut(lut, h, n, device)
-        return 0, b
+        return 0, b, n
     _packed_hard(hard, device, h)
     if b != 1:
         _fail('packed labels/layout length mismatch')
     spans = _documents(table, n, hard.size(0))
     if boundary is not None:
         raise NotImplementedError('packed layouts take boundary=None (run lengths come from the labels)')
-    _check_lut(lut, h, max([m for _, m in spans], default=0), device)
-    return _document_table(spans, n, device).data_ptr(), hard.size(0)
+    longest = max([m for _, m in spans], default=0)
+    _check_lut(lut, h, longest, device)
+    return _document_table(spans, n, device).data_ptr(), hard.size(0), max(longest, 256)
 
 
 # The readout's workspace starts with the position index of both label tensors; the backward of the same
-# step can reuse it.  One entry per device: the two label tensors themselves (kept alive, so their memory
-# cannot be handed to other labels), their version counters (bumped by any in-place write) and the
-# workspace.  share_index(False) switches the reuse off and drops the entries.
-_shared_index = {}
+# step can reuse it.  The reuse is explicit: the workspace travels on the normaliser that hard_readout
+# returns (the tensor every caller hands to hard_backward), together with the two label tensors it was built
+# from and their version counters.  hard_backward takes it only when it is given those same label tensors,
+# unmodified as far as torch can tell; a writer that goes through a raw pointer (a custom kernel filling a
+# preallocated label buffer) does not bump the counter, so such callers switch the reuse off with
+# share_index(False) or pass fresh label tensors per step.
 _share_index = True
 
 
@@ -281,17 +284,15 @@ def share_index(enabled):
     """Let hard_backward reuse the position index that hard_readout built for the same label tensors."""
     global _share_index
     _share_index = bool(enabled)
-    if not _share_index:
-        _shared_index.clear()
 
 
-def _remember_index(iq, ik, workspace):
+def _remember_index(norm, iq, ik, workspace):
     if _share_index:
-        _shared_index[iq.device.index] = (iq, ik, iq._version, ik._version, workspace)
+        norm._dism_readout = (iq, ik, iq._version, ik._version, workspace)
 
 
-def _recall_index(iq, ik):
-    entry = _shared_index.get(iq.device.index) if _share_index else None
+def _recall_index(norm, iq, ik):
+    entry = getattr(norm, '_dism_readout', None) if _share_index else None
     if entry is not None and entry[0] is iq and entry[1] is ik and entry[2] == iq._version and entry[3] == ik._version:
         return entry[4]
     return None
@@ -310,7 +311,7 @@ def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
     dv = v.size(3)
     _check(iq, torch.int32, (b, h, n), 'query labels')
     _check(ik, torch.int32, (b, h, n), 'key labels')
-    documents_ptr, rows = _layout_arguments(table, hard, boundary, lut, b, h, n, sq.device)
+    documents_ptr, rows, longest = _layout_arguments(table, hard, boundary, lut, b, h, n, sq.device)
     if ctas < 0:
         _fail('invalid CTA count')
     boundary_ptr = _check_boundary(boundary, b, h, n, sq.device)
@@ -320,10 +321,10 @@ def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
         size = _abi.dism_hard_readout_workspace(b, h, n)
         workspace = torch.empty((size,), dtype=torch.uint8, device=sq.device)
         _lib.check(_abi.dism_hard_readout(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), iq.data_ptr(), ik.data_ptr(),
-                                          hard.data_ptr(), boundary_ptr, documents_ptr, rows, lut.data_ptr(),
+                                          hard.data_ptr(), boundary_ptr, documents_ptr, rows, longest, lut.data_ptr(),
                                           lut.size(1), b, n, h, r, dv, int(ctas), out.data_ptr(), norm.data_ptr(),
                                           workspace.data_ptr(), size, _stream(sq)))
-        _remember_index(iq, ik, workspace)
+        _remember_index(norm, iq, ik, workspace)
     return out, norm
 
 
@@ -345,7 +346,7 @@ def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None)
     if table is None and not (torch.is_tensor(hard) and hard.dtype == torch.bool and tuple(hard.shape) == (b, h)
                               and hard.is_contiguous() and hard.device == sq.device):
         _fail('sequence hard flags: invalid device, dtype, shape or stride')
-    documents_ptr, rows = _layout_arguments(table, hard, boundary, lut, b, h, n, sq.device)
+    documents_ptr, rows, longest = _layout_arguments(table, hard, boundary, lut, b, h, n, sq.device)
     if ctas < 0:
         _fail('invalid CTA count')
     boundary_ptr = _check_boundary(boundary, b, h, n, sq.device)
@@ -355,10 +356,12 @@ def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None)
         dtau = torch.empty((h,), dtype=torch.float32, device=sq.device)
         size = _abi.dism_hard_backward_workspace(b, h, n, lut.size(1))
         workspace = torch.empty((size,), dtype=torch.uint8, device=sq.device)
-        index = _recall_index(iq, ik)
+        index = _recall_index(normalizer, iq, ik)
+        if index is not None:
+            index.record_stream(torch.cuda.current_stream(sq.device))  # read by this stream's kernels
         _lib.check(_abi.dism_hard_backward(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), dout.data_ptr(),
                                            iq.data_ptr(), ik.data_ptr(), hard.data_ptr(), boundary_ptr,
-                                           documents_ptr, rows, lut.data_ptr(), lut.size(1), normalizer.data_ptr(),
+                                           documents_ptr, rows, longest, lut.data_ptr(), lut.size(1), normalizer.data_ptr(),
                                            b, n, h, r, dv,
                                            int(ctas), dsq.data_ptr(), dsk.data_ptr(), dv_out.data_ptr(),
                                            dtau.data_ptr(), workspace.data_ptr(), size,
@@ -380,6 +383,24 @@ def labels(x, codebook):
         _lib.check(_abi.dism_labels(x.data_ptr(), codebook.data_ptr(), b, n, h, d, codebook.size(1), out.data_ptr(),
                                     _stream(x)))
     return out
+
+
+def labels_pair(x0, codebook0, x1, codebook1):
+    """labels(x0, codebook0) and labels(x1, codebook1) for two tensors of one shape (the q and k side of a step) in one launch."""
+    for x, codebook in ((x0, codebook0), (x1, codebook1)):
+        _check(x, torch.bfloat16, None, 'x')
+        _check(codebook, torch.bfloat16, None, 'codebook')
+    if x0.dim() != 4 or x1.shape != x0.shape or x1.device != x0.device:
+        _fail('both x must be [B,N,H,D] on one device')
+    b, n, h, d = x0.shape
+    if (codebook0.dim() != 3 or codebook0.size(0) != h or codebook0.size(2) != d or codebook1.shape != codebook0.shape
+            or codebook0.device != x0.device or codebook1.device != x0.device):
+        _fail('both codebooks must be [H,V,D] on the device of x')
+    with torch.cuda.device(x0.device):
+        out0, out1 = (torch.empty((b, h, n), dtype=torch.int32, device=x0.device) for _ in range(2))
+        _lib.check(_abi.dism_labels_pair(x0.data_ptr(), codebook0.data_ptr(), out0.data_ptr(), x1.data_ptr(), codebook1.data_ptr(),
+                                         out1.data_ptr(), b, n, h, d, codebook0.size(1), _stream(x0)))
+    return out0, out1
 
 
 def longest_match(streams):

@@ -32,6 +32,11 @@ int dism_abi_version(void);
  * 155-189) and of kernels/interp_true.py:8-65. */
 int dism_labels(const void *x, const void *codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t *labels, void *stream);
+/* The same for two tensors of one shape in one launch: the q and the k side of a step, each with its own codebook
+ * and label output.  The reference discretises q and k with two launches of the same kernel
+ * (dism_v3/python/flash_dism/kernels/interp_true.py:51-65); here they share one pipeline fill and drain. */
+int dism_labels_pair(const void *x0, const void *codebook0, int32_t *labels0, const void *x1, const void *codebook1,
+                     int32_t *labels1, int batch, int n, int heads, int d, int vocab, void *stream);
 /* The discretiser's tensor-memory pipeline bounds every wait of its roles on one another; *code is
  * the first wait that ran out in any dism_labels launch on the current device since the last call
  * (0: none, the only value a correct run produces); the call clears it.  Synchronises the device.
@@ -67,15 +72,16 @@ size_t dism_hard_readout_workspace(int batch, int heads, int n);
  * longest document).  Packed layout (the reference's `table` argument, dism_v3/src/host/hard_forward.cpp:
  * 56-85): batch 1, `documents` is a device int32 [N/256, 2] table giving, for every 256-position
  * block, the [begin, end) of the 256-aligned document that contains it, and `hard` is
- * [hard_rows, H] over equal training rows of N / hard_rows positions; fixed layout: documents NULL,
- * hard_rows = batch.
+ * [hard_rows, H] over equal training rows of N / hard_rows positions, and `longest_document` is the
+ * length of the longest document (the host knows it when it builds the table; lut_stride must exceed it);
+ * fixed layout: documents NULL, hard_rows = batch, longest_document ignored.
  * out bf16 [B,N,H,DV], lse2 float [B,H,N]; soft (batch, head) rows are written as zeros.
  * R in {16,32}, DV in {32,64,128}; vectors 16-byte aligned.  `workspace` is caller-owned scratch of
  * dism_hard_readout_workspace bytes, 256-byte aligned; its contents are dead after the call.
  * Stands in for cu_flash_dism.hard_readout (dism_v3/src/host/hard_forward.cpp:25-113). */
 int dism_hard_readout(const void *sq, const void *sk, const void *v, const int32_t *iq, const int32_t *ik,
                       const uint8_t *hard, const int32_t *boundary, const int32_t *documents, int hard_rows,
-                      const float *lut, int lut_stride, int batch, int n, int heads, int r, int dv, int ctas,
+                      int longest_document, const float *lut, int lut_stride, int batch, int n, int heads, int r, int dv, int ctas,
                       void *out, float *lse2, void *workspace, size_t workspace_bytes, void *stream);
 
 /* The same readout for callers that cannot supply scratch memory (an operator hook that only gets its
@@ -100,14 +106,14 @@ size_t dism_hard_backward_workspace(int batch, int heads, int n, int lut_stride)
 
 /* Hard backward: dsq float [B,N,H,R], dsk bf16 [B,N,H,R], dv bf16 [B,N,H,DV], dtau float [H]
  * (gradient of the natural-log coefficient).  lse2 is the normaliser the forward returned;
- * `boundary` may be NULL; `documents`/`hard_rows` as in dism_hard_readout; `workspace` is caller-owned scratch of dism_hard_backward_workspace bytes.
+ * `boundary` may be NULL; `documents`/`hard_rows`/`longest_document` as in dism_hard_readout; `workspace` is caller-owned scratch of dism_hard_backward_workspace bytes.
  * `readout_workspace` is NULL, or the workspace a dism_hard_readout call filled for the same labels, batch,
  * heads and n and that nothing has written since: its position index is then reused instead of rebuilt
  * (the reference's backward likewise consumes state its forward saved).
  * Stands in for cu_flash_dism.hard_backward (dism_v3/src/host/hard_backward.cpp:13-141). */
 int dism_hard_backward(const void *sq, const void *sk, const void *v, const void *dout, const int32_t *iq,
                        const int32_t *ik, const uint8_t *hard, const int32_t *boundary,
-                       const int32_t *documents, int hard_rows, const float *lut, int lut_stride,
+                       const int32_t *documents, int hard_rows, int longest_document, const float *lut, int lut_stride,
                        const float *lse2, int batch, int n, int heads, int r, int dv, int ctas, float *dsq,
                        void *dsk, void *dv_out, float *dtau, void *workspace, size_t workspace_bytes,
                        const void *readout_workspace, void *stream);

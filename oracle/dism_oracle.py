@@ -158,6 +158,26 @@ def reference_forward(sq, sk, v, iq, ik, tau):
     return out, logden / np.log(2.)
 
 
+def reference_forward_many(sq, sk, v, iq, ik, tau, threads=1):
+    """Many (batch, head) sequences through the reference's native planner + executor in float32, on `threads`
+    host threads.  sq, sk [S,N,R], v [S,N,DV], labels [S,N], tau [S] -> out float32 [S,N,DV]."""
+    ref = reference_lib()
+    if ref is None:
+        raise RuntimeError('oracle/_ref/libdism_ref.so was not built')
+    sq, sk, v, iq, ik = _f32(sq), _f32(sk), _f32(v), _i32(iq), _i32(ik)
+    tau = np.ascontiguousarray(tau, dtype=np.float64)
+    s, n, r = sq.shape
+    dv = v.shape[2]
+    out = np.empty((s, n, dv), np.float32)
+    ref.dism_ref_forward_f32_many.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                              ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_void_p, ctypes.c_int]
+    if ref.dism_ref_forward_f32_many(_ptr(iq), _ptr(ik), s, n, _ptr(tau), _ptr(sq), _ptr(sk), _ptr(v), r, dv, _ptr(out),
+                                     int(threads)):
+        raise RuntimeError('reference planner rejected an input')
+    return out
+
+
 # ---- numpy restatements of the integer stages (independent of the C file) -------------------
 def summary_numpy(iq, ik, hard):
     """Row-major recurrence restarted at every 32-row strip (dism_v3/tests/test_hard_summary.py:37-49)."""

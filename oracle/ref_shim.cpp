@@ -5,7 +5,10 @@
 //   execute<T> (:603-625).  The build recipe is oracle/Makefile; the output goes to oracle/_ref/.
 // One call plans and executes one (batch, head) sequence: labels -> Program -> output rows.
 #include "prefill.hpp"
+#include <atomic>
 #include <cstring>
+#include <thread>
+#include <vector>
 
 extern "C" {
 // iq, ik: int32 [n]; sq, sk: [n,r]; v: [n,dv]; out: [n,dv]; logden: [n] natural log of 1+sum W.
@@ -20,6 +23,25 @@ int dism_ref_forward_f32(const int *iq, const int *ik, int n, double tau, const 
         if (logden) std::memcpy(logden, program.logden.data(), sizeof(double) * n);
         return 0;
     } catch (...) { return 1; }
+}
+// `heads` independent (batch, head) sequences, each laid out as above and stored one after the other, worked off by
+// `threads` host threads that take sequences from a shared counter (the pattern of the reference's own planning
+// workers, planning_workers.hpp:14-85).  tau: one value per sequence.  Returns the number of rejected sequences.
+int dism_ref_forward_f32_many(const int *iq, const int *ik, int heads, int n, const double *tau, const float *sq,
+                              const float *sk, const float *v, int r, int dv, float *out, int threads) {
+    std::atomic<int> next{0}, failed{0};
+    auto work = [&] {
+        for (int head = next.fetch_add(1); head < heads; head = next.fetch_add(1)) {
+            const size_t at = size_t(head) * n;
+            failed += dism_ref_forward_f32(iq + at, ik + at, n, tau[head], sq + at * r, sk + at * r, v + at * dv, r, dv,
+                                           out + at * dv, nullptr);
+        }
+    };
+    std::vector<std::thread> pool;
+    for (int t = 1; t < threads; ++t) pool.emplace_back(work);
+    work();
+    for (auto &t : pool) t.join();
+    return failed.load();
 }
 int dism_ref_forward_f64(const int *iq, const int *ik, int n, double tau, const double *sq,
                          const double *sk, const double *v, int r, int dv, double *out,

@@ -29,7 +29,7 @@ def test_every_declared_symbol_is_exported_and_typed(lib):
     for name in names:
         assert hasattr(lib, name), f'{name} is declared in include/dism_b200.h but not exported'
         assert name in _lib.SIGNATURES, f'{name} has no ctypes signature'
-    assert lib.dism_abi_version() >= 5
+    assert lib.dism_abi_version() >= 6
 
 
 def test_library_has_no_torch_dependency(lib):
@@ -47,20 +47,32 @@ def test_argument_checks_run_without_a_device(lib):
     assert lib.dism_hard_log_weights(p, 4, 100, p, None) == 1 and '256-aligned' in message(lib)
     assert lib.dism_hard_summary(p, p, p, 1, 2, 300, 0, p, None) == 1 and '256-aligned' in message(lib)
     assert lib.dism_hard_summary(p, p, p, 1, 2, 512, -1, p, None) == 1 and 'CTA' in message(lib)
-    assert lib.dism_hard_readout(p, p, p, p, p, p, None, None, 1, p, 512, 1, 512, 2, 32, 64, 0, p, p, p, 1 << 30, None) == 1
+    assert lib.dism_hard_readout(p, p, p, p, p, p, None, None, 1, 0, p, 512, 1, 512, 2, 32, 64, 0, p, p, p, 1 << 30, None) == 1
     assert 'too short' in message(lib)
-    assert lib.dism_hard_readout(p, p, p, p, p, p, None, None, 1, p, 513, 1, 512, 2, 24, 64, 0, p, p, p, 1 << 30, None) == 2
+    assert lib.dism_hard_readout(p, p, p, p, p, p, None, None, 1, 0, p, 513, 1, 512, 2, 24, 64, 0, p, p, p, 1 << 30, None) == 2
     assert 'unsupported' in message(lib)
-    assert lib.dism_hard_readout(p, p, p, p, p, p, None, None, 1, p, 513, 1, 512, 2, 32, 64, 0, p, p, p, 16, None) == 1
+    assert lib.dism_hard_readout(p, p, p, p, p, p, None, None, 1, 0, p, 513, 1, 512, 2, 32, 64, 0, p, p, p, 16, None) == 1
     assert 'workspace' in message(lib)
-    assert lib.dism_hard_readout(p, p, p, p, p, p, None, p, 3, p, 513, 1, 1024, 2, 32, 64, 0, p, p, p, 1 << 30, None) == 1
+    assert lib.dism_hard_readout(p, p, p, p, p, p, None, p, 3, 256, p, 513, 1, 1024, 2, 32, 64, 0, p, p, p, 1 << 30, None) == 1
     assert 'training rows' in message(lib)
-    assert lib.dism_hard_readout(p, p, p, p, p, p, None, p, 1, p, 513, 2, 1024, 2, 32, 64, 0, p, p, p, 1 << 30, None) == 1
+    assert lib.dism_hard_readout(p, p, p, p, p, p, None, p, 1, 256, p, 513, 2, 1024, 2, 32, 64, 0, p, p, p, 1 << 30, None) == 1
     assert 'packed' in message(lib)
-    assert lib.dism_hard_backward(p, p, p, p, p, p, p, None, None, 1, p, 513, p, 1, 512, 2, 32, 64, 0, p, p, p, p, p, 16,
+    assert lib.dism_hard_backward(p, p, p, p, p, p, p, None, None, 1, 0, p, 513, p, 1, 512, 2, 32, 64, 0, p, p, p, p, p, 16,
                                   None, None) == 1
     assert 'workspace' in message(lib)
+    # packed layouts: the tables are indexed up to the longest document, which the caller states
+    assert lib.dism_hard_readout(p, p, p, p, p, p, None, p, 1, 1024, p, 513, 1, 1024, 2, 32, 64, 0, p, p, p, 1 << 30, None) == 1
+    assert 'too short' in message(lib) and 'longest document' in message(lib)
+    assert lib.dism_hard_readout(p, p, p, p, p, p, None, p, 1, 0, p, 2049, 1, 1024, 2, 32, 64, 0, p, p, p, 1 << 30, None) == 1
+    assert 'longest document' in message(lib)
+    assert lib.dism_hard_backward(p, p, p, p, p, p, p, None, p, 1, 768, p, 513, p, 1, 1024, 2, 32, 64, 0, p, p, p, p, p, 1 << 30,
+                                  None, None) == 1
+    assert 'too short' in message(lib)
+    # (batch, head) slices are a grid dimension
+    assert lib.dism_hard_readout(p, p, p, p, p, p, None, None, 4096, 0, p, 513, 4096, 512, 32, 32, 64, 0, p, p, p, 1 << 40, None) == 1
+    assert '65535' in message(lib)
     assert lib.dism_labels(p, p, 1, 16, 2, 48, 512, p, None) == 2 and 'unsupported' in message(lib)
+    assert lib.dism_labels(p, ctypes.c_void_p(4104), 1, 16, 2, 64, 512, p, None) == 1 and '16-byte aligned' in message(lib)
     assert lib.dism_longest_match(p, 1, 13, p, p, p, p, 1 << 20, None) == 1
     assert lib.dism_hard_readout_workspace(8, 16, 8192) > 8 * 16 * 8192 * 8
     assert lib.dism_hard_backward_workspace(8, 16, 8192, 8193) > 2 * 8 * 16 * 8192 * 8

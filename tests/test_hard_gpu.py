@@ -258,8 +258,9 @@ def test_backward_all_soft_is_zero(api):
 
 
 def test_backward_reuses_the_forward_index(api):
-    """The backward takes the position index from the readout of the same label tensors: same bits as a
-    rebuilt index; labels written in place, or other label tensors, are not served from the cache."""
+    """The backward takes the position index that travels on the normaliser of the readout of the same label
+    tensors: same bits as a rebuilt index; labels written in place, other label tensors or another forward's
+    normaliser are not served."""
     b, n, h, r, dv = 2, 1024, 3, 32, 64
     sq, sk, v, dout = (t.cuda() for t in vectors(5, b, n, h, r, dv))
     g = torch.Generator().manual_seed(6)
@@ -274,19 +275,20 @@ def test_backward_reuses_the_forward_index(api):
         return norm, api['bwd'].backward_hard(sq, sk, v, dout, iq, ik, hard, norm, dict(boundary=None, log_weights=lut))
 
     norm, shared = both(iq, ik)
-    assert cu._recall_index(iq, ik) is not None
+    assert cu._recall_index(norm, iq, ik) is not None
     cu.share_index(False)
     try:
-        _, rebuilt = both(iq, ik)
-        assert cu._recall_index(iq, ik) is None
+        unshared_norm, rebuilt = both(iq, ik)
+        assert cu._recall_index(unshared_norm, iq, ik) is None
     finally:
         cu.share_index(True)
     assert all(torch.equal(a, e) for a, e in zip(shared, rebuilt))
-    both(iq, ik)
-    iq[0, 1, 7] += 1                       # in place: the remembered index is stale
-    assert cu._recall_index(iq, ik) is None
-    both(iq, ik)
-    assert cu._recall_index(iq.clone(), ik) is None  # another tensor, even with the same values
+    norm, _ = both(iq, ik)
+    assert cu._recall_index(norm.clone(), iq, ik) is None  # the index belongs to one readout's normaliser
+    iq[0, 1, 7] += 1                       # in place: the index that travelled with the normaliser is stale
+    assert cu._recall_index(norm, iq, ik) is None
+    norm, _ = both(iq, ik)
+    assert cu._recall_index(norm, iq.clone(), ik) is None  # another tensor, even with the same values
     lut = api['fwd'].hard_log_weights(tau, n)
     _, fresh = both(iq, ik)
     again = api['bwd'].backward_hard(sq, sk, v, dout, iq.clone(), ik.clone(), hard, _, dict(boundary=None, log_weights=lut))
@@ -360,6 +362,22 @@ def test_labels_tensor_memory_pipeline(api, oracle, shape):
     assert np.array_equal(got.cpu().numpy(), oracle.labels(x.float().numpy(), e.float().numpy()))
     again = api['cu'].labels(x.cuda(), e.cuda())
     assert torch.equal(got, again)
+
+
+@pytest.mark.parametrize('shape', [(2, 1024, 4, 64, 512), (1, 256, 2, 128, 256), (3, 128, 5, 64, 128), (1, 384, 3, 64, 512)])
+def test_labels_pair_equals_two_calls(api, oracle, shape):
+    """Two tensors of one shape in one launch (q with its codebook, k with its own): the bits of two single calls,
+    on shapes the tensor-memory pipeline covers and on one it hands to the mma.sync kernel."""
+    b, n, h, d, v = shape
+    g = torch.Generator().manual_seed(b * 77 + n + v)
+    xq, xk = (torch.randn(b, n, h, d, generator=g).bfloat16().cuda() for _ in range(2))
+    eq, ek = (torch.nn.functional.silu(torch.randn(h, v, d, generator=g)).bfloat16().cuda() for _ in range(2))
+    xk[0, 3] = 0                    # all logits equal: label 0
+    ek[:, v - 1] = ek[:, 1]         # exact duplicate: the lower index wins
+    iq, ik = api['cu'].labels_pair(xq, eq, xk, ek)
+    assert labels_fault() == 0
+    assert torch.equal(iq, api['cu'].labels(xq, eq)) and torch.equal(ik, api['cu'].labels(xk, ek))
+    assert np.array_equal(ik.cpu().numpy(), oracle.labels(xk.float().cpu().numpy(), ek.float().cpu().numpy()))
 
 
 def test_labels_tensor_memory_pipeline_all_ties(api):

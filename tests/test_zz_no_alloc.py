@@ -40,18 +40,28 @@ def test_static_readout_matches_workspace_readout_twice():
         size = lib.dism_hard_readout_workspace(b, h, n)
         workspace = torch.empty(size, dtype=torch.uint8, device='cuda')
         _lib.check(lib.dism_hard_readout(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), iq.data_ptr(), ik.data_ptr(),
-                                         hard.data_ptr(), None, None, b, lut.data_ptr(), n + 1, b, n, h, r, dv, 0,
+                                         hard.data_ptr(), None, None, b, n, lut.data_ptr(), n + 1, b, n, h, r, dv, 0,
                                          want.data_ptr(), want_norm.data_ptr(), workspace.data_ptr(), size, stream))
         got, got_norm = torch.full_like(want, float('nan')), torch.full_like(want_norm, float('nan'))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0] if call else None  # the first call on a device may load the array
         status = lib.dism_hard_readout_static(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), iq.data_ptr(), ik.data_ptr(),
                                               hard.data_ptr(), None, lut.data_ptr(), n + 1, b, n, h, r, dv, 0,
                                               got.data_ptr(), got_norm.data_ptr(), stream)
         assert status == 0, lib.dism_hard_readout_static_error().decode()
         torch.cuda.synchronize()
+        if call:  # a later call leaves the device's free memory exactly as it found it
+            assert torch.cuda.mem_get_info()[0] == free_before
         # the same kernels on the same inputs: the hard-path tests compare such runs bit for bit
         assert torch.equal(got, want), f'call {call}: output differs'
         assert torch.equal(got_norm, want_norm), f'call {call}: normaliser differs'
         assert got.count_nonzero() and not got[0, :, 1].count_nonzero()
+        # and against the CPU oracle, at the tolerances of the forward tests
+        from oracle import dism_oracle
+        f = lambda t: t.float().cpu().numpy()
+        expected, lse2 = dism_oracle.forward(f(sq), f(sk), f(v), iq.cpu().numpy(), ik.cpu().numpy(), hard.cpu().numpy(), f(tau))
+        torch.testing.assert_close(got.double().cpu(), torch.from_numpy(expected), atol=.008, rtol=.025)
+        torch.testing.assert_close(got_norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
 
 
 def test_static_readout_rejects_shapes_beyond_its_scratch():
