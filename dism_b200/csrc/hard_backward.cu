@@ -74,7 +74,13 @@ static cudaError_t launch_backward_variant(const BackwardBlockArgs& args, int ct
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
     if (status != cudaSuccess) return status;
     const int batch_heads = args.batch * args.heads;
+    // about eight full tiles per warp (partial tiles of small buckets come on top), and with few (batch, head) slices at
+    // least four CTAs per SM over the whole grid: warps take tiles from a counter, so any grid covers the work;
+    // `ctas` caps the whole grid
     int per_head = args.n / (QT * BLOCK_WARPS * 8);
+    const int fill = (4 * device_sm_count() + batch_heads - 1) / batch_heads;
+    if (per_head < fill) per_head = fill;
+    if (per_head > (args.n + QT * BLOCK_WARPS - 1) / (QT * BLOCK_WARPS)) per_head = (args.n + QT * BLOCK_WARPS - 1) / (QT * BLOCK_WARPS);
     if (per_head < 1) per_head = 1;
     if (ctas) per_head = ctas / batch_heads > 0 ? ctas / batch_heads : 1;
     KernelTimer timer(QUERY_MAJOR ? "hard_backward_query" : "hard_backward_key", stream);

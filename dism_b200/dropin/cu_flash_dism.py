@@ -7,9 +7,9 @@ forwards plain pointers to the C ABI of libdism_b200.so on the current CUDA stre
 compute of its own and has no fallback: without the library, importing it fails.
 
 Differences a caller can see: `hard_readout` and `hard_backward` accept `boundary=None` (run
-lengths are then derived from the labels inside the kernel, nothing quadratic is stored) and, with
-a packed `table`, only `boundary=None`; the packed `hard_summary` / `hard_chunk` run document by
-document through the fixed-length kernels; the soft path (`core_forward`, `core_backward`) is not
+lengths are then derived from the labels inside the kernel, nothing quadratic is stored); with a
+packed `table` a boundary is checked for shape and otherwise left unread (same bits either way);
+the packed `hard_summary` / `hard_chunk` run document by document through the fixed-length kernels; the soft path (`core_forward`, `core_backward`) is not
 built and raises NotImplementedError; the `choice` device word of the reference's CUDA-graph
 router is accepted only as None.
 """
@@ -264,7 +264,13 @@ def _layout_arguments(table, hard, boundary, lut, b, h, n, device):
         _fail('packed labels/layout length mismatch')
     spans = _documents(table, n, hard.size(0))
     if boundary is not None:
-        raise NotImplementedError('packed layouts take boundary=None (run lengths come from the labels)')
+        # The reference's forward_hard always hands over the packed rectangle (the documents' [H,(m-1)//32,m] regions,
+        # flattened).  It is checked for shape and then left unread: with a packed layout the kernels take run lengths
+        # from the labels alone, which gives the same bits.
+        expected = sum(h * ((m - 1) // 32) * m for _, m in spans)
+        if not (torch.is_tensor(boundary) and boundary.device == device and boundary.dtype == torch.int32
+                and boundary.is_contiguous() and boundary.dim() == 1 and boundary.numel() == expected):
+            _fail('hard boundary: invalid device, dtype, shape or stride')
     longest = max([m for _, m in spans], default=0)
     _check_lut(lut, h, longest, device)
     return _document_table(spans, n, device).data_ptr(), hard.size(0), max(longest, 256)
@@ -314,7 +320,7 @@ def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
     documents_ptr, rows, longest = _layout_arguments(table, hard, boundary, lut, b, h, n, sq.device)
     if ctas < 0:
         _fail('invalid CTA count')
-    boundary_ptr = _check_boundary(boundary, b, h, n, sq.device)
+    boundary_ptr = _check_boundary(boundary, b, h, n, sq.device) if table is None else 0
     with torch.cuda.device(sq.device):
         out = torch.empty((b, n, h, dv), dtype=torch.bfloat16, device=sq.device)
         norm = torch.empty((b, h, n), dtype=torch.float32, device=sq.device)
@@ -349,7 +355,7 @@ def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None)
     documents_ptr, rows, longest = _layout_arguments(table, hard, boundary, lut, b, h, n, sq.device)
     if ctas < 0:
         _fail('invalid CTA count')
-    boundary_ptr = _check_boundary(boundary, b, h, n, sq.device)
+    boundary_ptr = _check_boundary(boundary, b, h, n, sq.device) if table is None else 0
     with torch.cuda.device(sq.device):
         dsq = torch.empty((b, n, h, r), dtype=torch.float32, device=sq.device)
         dsk, dv_out = torch.empty_like(sk), torch.empty_like(v)

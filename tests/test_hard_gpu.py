@@ -507,6 +507,21 @@ def test_packed_documents_match_fixed_length(api, oracle, pattern):
     assert torch.equal(changed[:, 256:], out[:, 256:]) and torch.equal(changed_norm, norm)
 
 
+def test_packed_saved_state_gives_the_same_bits(api):
+    """forward_hard(save_state=True) with a layout returns the packed rectangle (what the reference's forward always
+    builds); readout and backward accept it and give the bits of the label-only route."""
+    x, dout, layout, spans = packed_case(api, 'periodic')
+    out, norm = api['fwd'].forward_hard(*x, layout=layout)
+    out2, norm2, state = api['fwd'].forward_hard(*x, layout=layout, save_state=True)
+    assert torch.equal(out, out2) and torch.equal(norm, norm2)
+    assert state['boundary'].dim() == 1 and state['boundary'].numel() == sum(2 * ((z - a - 1) // 32) * (z - a) for a, z in spans)
+    plain = api['bwd'].backward_hard(*x[:3], dout, *x[3:6], norm, dict(boundary=None, log_weights=state['log_weights']), layout=layout)
+    saved = api['bwd'].backward_hard(*x[:3], dout, *x[3:6], norm2, state, layout=layout)
+    assert all(torch.equal(a, e) for a, e in zip(plain, saved))
+    with pytest.raises(RuntimeError, match='boundary'):
+        api['fwd'].hard_readout(*x[:6], state['boundary'][:-1].contiguous(), state['log_weights'], layout=layout)
+
+
 def test_packed_summary_chunk_and_errors(api, oracle):
     x, dout, layout, spans = packed_case(api, 'boundary')
     summary = api['summary'].summarize_hard(x[3], x[4], x[5], layout=layout)
