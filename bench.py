@@ -543,6 +543,78 @@ def run_other_workload(args):
                           'steps': args.steps, 'warmup': args.warmup}))
 
 
+def run_model(args):
+    """The nanochat-shaped model with DISM layers (dism_b200/model.py): depth 20, width 1280, 10 heads of 128, vocabulary
+    65536, bf16 weights, sequences of 2048 uniform-random tokens, batch 16 per GPU.  One step = forward, backward, the
+    data-parallel gradient sum over NCCL (dism_b200/data_parallel.py) and an AdamW update; metric: tokens/s over all
+    ranks, time = the slowest rank's."""
+    import torch.distributed as dist
+    import dism_b200
+    dism_b200.install_dropin()
+    from dism_b200.model import DismLM
+    from dism_b200.data_parallel import sum_gradients
+    rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
+    local = int(os.environ.get('LOCAL_RANK', 0))
+    torch.cuda.set_device(local)
+    device = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    torch.manual_seed(0)  # the same initial weights on every rank
+    depth, width, heads, head_dim, vocab, batch, seq = 20, 1280, 10, 128, 65536, args.model_batch, 2048
+    model = DismLM(depth, width, heads, head_dim, vocab).to(device).bfloat16()
+    optimizer = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+    parameters = [p for p in model.parameters()]
+    generator = torch.Generator().manual_seed(1 + rank)
+    host = [torch.randint(0, vocab, (batch, seq + 1), generator=generator, dtype=torch.int32).pin_memory() for _ in range(4)]
+
+    def step(index):
+        tokens = host[index % len(host)].to(device, non_blocking=True).long()
+        loss = model(tokens[:, :-1], tokens[:, 1:])
+        loss.backward()
+        if world > 1:
+            sum_gradients(parameters)
+            torch._foreach_div_([p.grad for p in parameters if p.grad is not None], world)
+        optimizer.step()
+        optimizer.zero_grad(set_to_none=True)
+        return loss
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for index in range(args.warmup):
+        step(index)
+    barrier()
+    with ClockSampler(local) as clocks:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for index in range(args.steps):
+            loss = step(index)
+        value = loss.item()  # the step's result read back on the host, inside the timed region
+        stop.record()
+        barrier()
+    elapsed = torch.tensor([start.elapsed_time(stop)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = float(elapsed) / args.steps
+        tokens_per_second = world * batch * seq / (ms * 1e-3)
+        count = sum(p.numel() for p in parameters)
+        print(json.dumps({
+            'metric': 'training tokens/s, nanochat-shaped model with DISM layers (fwd + bwd + gradient all-reduce + AdamW)',
+            'value': tokens_per_second, 'unit': 'tokens/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms,
+            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic (uniform random tokens, random-init weights)',
+            'config': {'workload': f'depth {depth}, width {width}, {heads} heads x {head_dim}, vocabulary {vocab}, sequence {seq}, batch {batch} per GPU',
+                       'parallelism': f'dp{world}: replicas, bucketed NCCL all_reduce(SUM) of the gradients', 'parameters': count},
+            'loss': value, 'per_gpu_value': tokens_per_second / world,
+            'e2e': {'value': tokens_per_second, 'unit': 'tokens/s', 'h2d_bytes_per_step': batch * (seq + 1) * 4, 'd2h_bytes_per_step': 4},
+            'clocks': clocks.summary()}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument('--gpus', type=int, default=1)
@@ -552,11 +624,14 @@ def main():
     # profiling aids (ncu captures want a small case and no host-side work); not for reported numbers
     parser.add_argument('--batch', type=int, default=SHAPE['batch'])
     parser.add_argument('--kernels-only', action='store_true', help='skip the end-to-end and CPU-baseline legs')
-    parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams'],
+    parser.add_argument('--model-batch', type=int, default=16, help='sequences per GPU of the model workload')
+    parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams', 'model'],
                         help='side workloads print their own line; the benchmark contract is the training shape')
     args = parser.parse_args()
     SHAPE['batch'] = args.batch
-    if args.workload != 'training':
+    if args.workload == 'model':
+        run_model(args)
+    elif args.workload != 'training':
         run_other_workload(args)
     elif args.impl == 'reference':
         run_reference(args)
