@@ -135,10 +135,11 @@ def run_ours(args):
     s = SHAPE
     if s['heads'] % world:
         raise SystemExit(f"{s['heads']} heads do not split evenly over {world} GPUs")
-    heads_here = s['heads'] // world
+    split = args.share if args.kernels_only and args.share else world  # --share: rank 0's slice of a wider split, alone
+    heads_here = s['heads'] // split
     total_positions = s['batch'] * s['heads'] * s['n']  # the whole job, over all ranks
     positions = s['batch'] * heads_here * s['n']        # this rank's share
-    host, params = make_inputs(0, device, rank, world)
+    host, params = make_inputs(0, device, rank, split)
     resident = {k: v.to(device) for k, v in host.items()}
     launches = [0]
 
@@ -624,6 +625,7 @@ def main():
     # profiling aids (ncu captures want a small case and no host-side work); not for reported numbers
     parser.add_argument('--batch', type=int, default=SHAPE['batch'])
     parser.add_argument('--kernels-only', action='store_true', help='skip the end-to-end and CPU-baseline legs')
+    parser.add_argument('--share', type=int, default=0, help='with --kernels-only: time the head slice one of this many GPUs would get')
     parser.add_argument('--model-batch', type=int, default=16, help='sequences per GPU of the model workload')
     parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams', 'model'],
                         help='side workloads print their own line; the benchmark contract is the training shape')

@@ -89,12 +89,12 @@ int dism_hard_readout(const void *sq, const void *sk, const void *v, const int32
  * serialises the device and may fail).  It has no counterpart in the reference.  The position index
  * lives in a fixed array inside the library (DISM_READOUT_STATIC_BYTES, held on every GPU that loads
  * the library until the process exits); the call allocates nothing.  Limits: the shape's scratch
- * (dism_hard_readout_workspace: about 41 bytes per position plus 112 KiB per (batch, head)) must fit,
+ * (dism_hard_readout_workspace: about 49 bytes per position plus 112 KiB per (batch, head)) must fit,
  * otherwise DISM_EINVAL; all calls on a
  * device share the array, so calls that overlap on the GPU race and must be serialised by the caller;
  * the first call on each device resolves the array's address and should be made before any stream
  * capture starts.  The message of a failing call is in dism_hard_readout_static_error(). */
-#define DISM_READOUT_STATIC_BYTES 8388608 /* 8 MiB: e.g. 18 (batch x head) rows of 8192 positions */
+#define DISM_READOUT_STATIC_BYTES 8388608 /* 8 MiB: e.g. 16 (batch x head) rows of 8192 positions */
 int dism_hard_readout_static(const void *sq, const void *sk, const void *v, const int32_t *iq,
                              const int32_t *ik, const uint8_t *hard, const int32_t *boundary,
                              const float *lut, int lut_stride, int batch, int n, int heads, int r, int dv,
