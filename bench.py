@@ -508,8 +508,8 @@ def run_other_workload(args):
                   for _ in range(2)]
         v = torch.randn(b, n, h, dv, generator=g, device='cuda').bfloat16()
         hard, tau = torch.ones(b, h, dtype=torch.bool, device='cuda'), torch.full((h,), .05, device='cuda')
-        iq, ik = cu.labels(q, codebook), cu.labels(k, codebook)  # one shared codebook, so copied rows match
-        ms_labels = timed(lambda: (cu.labels(q, codebook), cu.labels(k, codebook)))
+        iq, ik = cu.labels_pair(q, codebook, k, codebook)  # one shared codebook, so copied rows match
+        ms_labels = timed(lambda: cu.labels_pair(q, codebook, k, codebook))
         ms_forward = timed(lambda: forward_hard(sq, sk, v, iq, ik, hard, tau))
         from dism_b200 import _lib
         _lib.load().dism_profile_enable(1)

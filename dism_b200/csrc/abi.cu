@@ -87,7 +87,7 @@ int dism_profile_read(int index, char* name, int capacity, float* milliseconds) 
 }
 
 const char* dism_last_error(void) { return last_error; }
-int dism_abi_version(void) { return 6; }
+int dism_abi_version(void) { return 7; }
 
 int dism_labels(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t* labels, void* stream) {
@@ -149,6 +149,14 @@ int dism_hard_log_weights(const float* tau, int heads, int n, float* lut, void* 
         return fail(DISM_EINVAL, "LUT maximum length must be positive and 256-aligned");
     return cuda_status(dism::launch_log_weights(tau, heads, n, lut, static_cast<cudaStream_t>(stream)),
                        "hard_log_weights");
+}
+
+int dism_hard_dlog_weights(const float* lut, int heads, int lut_stride, float* out, void* stream) {
+    if (!lut || !out) return fail(DISM_EINVAL, "null pointer");
+    if (heads <= 0 || heads > 65535) return fail(DISM_EINVAL, "the table must hold 1..65535 heads");
+    if (lut_stride < 2) return fail(DISM_EINVAL, "the table must hold lengths 0 and 1 at least");
+    return cuda_status(dism::launch_dlog_weights(lut, heads, lut_stride, out, static_cast<cudaStream_t>(stream)),
+                       "hard_dlog_weights");
 }
 
 static int check_documents(const int32_t* documents, int hard_rows, int longest_document, int lut_stride, const int32_t* boundary,

@@ -4,9 +4,10 @@
 // when its labels are equal, so the kernels never visit the N^2/2 pairs.  A small prepass sorts
 // the positions of one side by (label bucket, position); the owner of a row then reads only the
 // bucket of its own label (with 4096 buckets, almost always exactly the positions with that label), keeps the entries with the same label on the
-// causal side, and gets its matching partners already in ascending order.  Eight lane groups of
-// a warp each own one row and work through their queued partners together, so the per-pair
-// arithmetic (run length, table lookup, two short dot products, one axpy) runs eight pairs wide.
+// causal side, and gets its matching partners already in ascending order.  Because both sides are
+// sorted the same way, the causal pair set is a union of small dense blocks (the queries of a
+// bucket against the keys of the same bucket); a warp works through one such block sixteen rows
+// by sixteen partners at a time on the tensor cores (hard_forward_blocks.cuh, hard_backward_blocks.cuh).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -156,6 +157,8 @@ size_t longest_match_workspace_bytes(int batch, int n);
 cudaError_t launch_longest_match(const int* streams, int batch, int n, int* end, int* length, int* next,
                                  void* workspace, cudaStream_t stream);
 cudaError_t launch_log_weights(const float* tau, int heads, int n, float* lut, cudaStream_t stream);
+// g[h, l] = d ln W_l / d tau from the log2 table lut [heads, lut_stride]; out has the same shape.
+cudaError_t launch_dlog_weights(const float* lut, int heads, int lut_stride, float* out, cudaStream_t stream);
 size_t hard_forward_workspace_bytes(int batch, int heads, int n);
 cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,
                                 const __nv_bfloat16* v, const int* iq, const int* ik, const uint8_t* hard,

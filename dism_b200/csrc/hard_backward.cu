@@ -6,7 +6,7 @@
 // dism_v3/docs/HARD_BACKWARD_QUADRATIC.md:60-97).  Where the reference runs one key-major kernel
 // and adds dSQ and four per-query moments across CTAs with FP32 atomics, this design walks the
 // matched pairs twice, once owned by queries and once owned by keys: every gradient row is then
-// accumulated by exactly one lane group in ascending partner order, with no atomics, no
+// accumulated by exactly one warp, tile by tile in ascending partner order, with no atomics, no
 // zero-filled accumulators and bit-identical results for any grid size.  Pair coefficients stay
 // in FP32 (the reference rounds them to BF16 to feed its tensor-core tiles).
 #include "hard_backward_blocks.cuh"
@@ -27,6 +27,12 @@ __global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __rest
         g = t > 0 ? length + 1.f - negative : negative;
     }
     out[int64_t(head) * stride + l] = g;
+}
+
+cudaError_t launch_dlog_weights(const float* lut, int heads, int lut_stride, float* out, cudaStream_t stream) {
+    KernelTimer timer("dlog_weights", stream);
+    dlog_weights_kernel<<<dim3((lut_stride + 255) / 256, heads), 256, 0, stream>>>(lut, out, lut_stride);
+    return cudaGetLastError();
 }
 
 // dtau[h] = sum over batch and rows of the per-row terms, in a fixed order (thread-strided partial
@@ -121,10 +127,8 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     }
     float* rows = reinterpret_cast<float*>(cursor);
     float* dlut = rows + size_t(batch_heads) * shape.n;
-    {
-        KernelTimer timer("dlog_weights", stream);
-        dlog_weights_kernel<<<dim3((lut_stride + 255) / 256, shape.heads), 256, 0, stream>>>(lut, dlut, lut_stride);
-    }
+    status = launch_dlog_weights(lut, shape.heads, lut_stride, dlut, stream);
+    if (status != cudaSuccess) return status;
     {
         KernelTimer timer("plan_tiles", stream);
         const TilePlan by_query{queries.starts, keys.starts, tile_starts[0], tiles[0], tile_starts[0] + size_t(batch_heads) * (BUCKETS + 1)};

@@ -3,11 +3,12 @@
 // Replaces, behind the C ABI, the reference's hard_log_weights_kernel and hard_forward_kernel
 // (dism_v3/src/hard_forward.cu:9-118, dism_v3/include/forward/readout.cuh:16-100).  The design is
 // not a translation: the table entry of length 0 is -1e6, whose weight flushes to exactly 0, so
-// only pairs with equal labels contribute.  Each group of four lanes owns one query row, finds
-// its matching keys through the key-side position index, and accumulates them in ascending key
-// order with the online max / unit-fallback normalisation of the reference (maximum starts at 0,
-// denominator at 1).  A row is reduced by one group in a fixed order, so outputs do not depend on
-// the grid size.
+// only pairs with equal labels contribute.  Both sides are sorted by (label bucket, position); a
+// warp takes sixteen queries of one bucket, walks the bucket's keys sixteen at a time and
+// accumulates them in ascending key order with the online max / unit-fallback normalisation of
+// the reference (maximum starts at 0, denominator at 1).  A row is reduced by one warp in a fixed
+// order, so outputs do not depend on the grid size.  This file holds the table kernel, the
+// workspace layout and the launch; the tile kernel is in hard_forward_blocks.cuh.
 #include "hard_forward_blocks.cuh"
 
 namespace dism {

@@ -17,6 +17,7 @@
 #include "../../include/dism_b200.h"
 #include "dism_common.cuh"
 
+#include <atomic>
 #include <cstdio>
 
 namespace {
@@ -26,7 +27,7 @@ namespace {
 static __device__ __align__(256) unsigned char static_index[DISM_READOUT_STATIC_BYTES];
 
 constexpr int MAX_DEVICES = 64;
-void* device_address[MAX_DEVICES] = {};
+std::atomic<void*> device_address[MAX_DEVICES] = {};  // written once per device; threads may race to resolve the same value
 thread_local char static_error[256] = "";
 
 }  // namespace
@@ -55,19 +56,20 @@ int dism_hard_readout_static(const void* sq, const void* sk, const void* v, cons
     int device = 0;
     cudaError_t status = cudaGetDevice(&device);
     if (status == cudaSuccess && (device < 0 || device >= MAX_DEVICES)) status = cudaErrorInvalidDevice;
-    if (status == cudaSuccess && !device_address[device]) {
-        // First call on this device: resolve the array's device address.  This is a set-up step; make the
-        // first call on a device before any stream capture begins.
-        void* address = nullptr;
+    void* address = status == cudaSuccess ? device_address[device].load(std::memory_order_acquire) : nullptr;
+    if (status == cudaSuccess && !address) {
+        // First call on this device: resolve the array's device address.  This is a set-up step: it may load the
+        // library's image on the device (which takes device memory for the array), so make the first call on each
+        // device at start-up, before the host's pool takes the remaining memory and before any stream capture begins.
         status = cudaGetSymbolAddress(&address, static_index);
-        if (status == cudaSuccess) device_address[device] = address;
+        if (status == cudaSuccess) device_address[device].store(address, std::memory_order_release);
     }
     if (status != cudaSuccess) {
         snprintf(static_error, sizeof(static_error), "built-in scratch unavailable: %s", cudaGetErrorString(status));
         return DISM_ECUDA;
     }
     const int code = dism_hard_readout(sq, sk, v, iq, ik, hard, boundary, nullptr, batch, n, lut, lut_stride, batch, n, heads, r, dv, ctas,
-                                       out, lse2, device_address[device], size_t(DISM_READOUT_STATIC_BYTES), stream);
+                                       out, lse2, address, size_t(DISM_READOUT_STATIC_BYTES), stream);
     if (code) snprintf(static_error, sizeof(static_error), "%s", dism_last_error());
     return code;
 }

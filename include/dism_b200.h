@@ -64,6 +64,13 @@ int dism_hard_chunk(const int32_t *summary, int32_t *boundary, int batch_heads, 
  * Stands in for cu_flash_dism.hard_log_weights (dism_v3/src/host/hard_forward.cpp:11-23). */
 int dism_hard_log_weights(const float *tau, int heads, int n, float *lut, void *stream);
 
+/* out float [H, lut_stride]: g[h,l] = d ln W_l / d tau[h] for W_l = sum_{s=1..l} exp(s*tau[h]), with tau recovered from
+ * the table itself (lut[h,1] = tau[h] * log2 e); entry 0 is 0.  dism_hard_backward builds this table in its
+ * workspace on every call; the entry point makes it testable and reusable by itself.
+ * Stands in for hard_dlog_weights_kernel (dism_v3/src/hard_backward.cu:8-24), which the reference launches
+ * inside cu_flash_dism.hard_backward (dism_v3/src/host/hard_backward.cpp). */
+int dism_hard_dlog_weights(const float *lut, int heads, int lut_stride, float *out, void *stream);
+
 /* Bytes of scratch dism_hard_readout needs for this shape (both position indices and the tile plan). */
 size_t dism_hard_readout_workspace(int batch, int heads, int n);
 
@@ -92,8 +99,9 @@ int dism_hard_readout(const void *sq, const void *sk, const void *v, const int32
  * (dism_hard_readout_workspace: about 49 bytes per position plus 112 KiB per (batch, head)) must fit,
  * otherwise DISM_EINVAL; all calls on a
  * device share the array, so calls that overlap on the GPU race and must be serialised by the caller;
- * the first call on each device resolves the array's address and should be made before any stream
- * capture starts.  The message of a failing call is in dism_hard_readout_static_error(). */
+ * the first call on each device resolves the array's address, which may load the library image (and with it
+ * the array) onto that device: make it at start-up, before the host's pool takes the remaining memory and
+ * before any stream capture starts.  The message of a failing call is in dism_hard_readout_static_error(). */
 #define DISM_READOUT_STATIC_BYTES 8388608 /* 8 MiB: e.g. 16 (batch x head) rows of 8192 positions */
 int dism_hard_readout_static(const void *sq, const void *sk, const void *v, const int32_t *iq,
                              const int32_t *ik, const uint8_t *hard, const int32_t *boundary,

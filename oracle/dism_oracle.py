@@ -102,6 +102,19 @@ def longest(stream):
     return end, length, nxt
 
 
+def reference_longest_lengths(keys, queries, interval=64):
+    """max_j<=i L(i,j) of one sequence from the reference's decode planner (suffix automaton + tail band), int32 [N];
+    None when the reference was not built."""
+    ref = reference_lib()
+    if ref is None or not hasattr(ref, 'dism_ref_longest_lengths'):
+        return None
+    k, q = _i32(keys), _i32(queries)
+    out = np.empty(k.size, np.int32)
+    if ref.dism_ref_longest_lengths(_ptr(k), _ptr(q), k.size, int(interval), _ptr(out)):
+        raise RuntimeError('the reference planner rejected the sequence')
+    return out
+
+
 def lut(tau, n):
     tau = _f32(tau)
     out = np.empty((tau.size, n + 1), np.float32)

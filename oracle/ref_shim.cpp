@@ -2,9 +2,11 @@
 //
 // Compiled from the reference sources where they lie (never copied into this repository):
 //   dism_v3/python/flash_dism/inference/csrc/prefill.hpp  Builder (:426-515), finish (:517-599),
-//   execute<T> (:603-625).  The build recipe is oracle/Makefile; the output goes to oracle/_ref/.
+//   execute<T> (:603-625); planner.hpp  Planner::append / advance (:132-149, :253-310) for the longest match length.
+// The build recipe is oracle/Makefile; the output goes to oracle/_ref/.
 // One call plans and executes one (batch, head) sequence: labels -> Program -> output rows.
 #include "prefill.hpp"
+#include "planner.hpp"
 #include <atomic>
 #include <cstring>
 #include <thread>
@@ -52,6 +54,20 @@ int dism_ref_forward_f64(const int *iq, const int *ik, int n, double tau, const 
         auto program = builder.finish();
         dism_prefill::execute<double>(program, sq, sk, v, r, dv, out);
         if (logden) std::memcpy(logden, program.logden.data(), sizeof(double) * n);
+        return 0;
+    } catch (...) { return 1; }
+}
+// max_j<=i L(i,j) of one sequence as the reference's decode planner tracks it: Planner::append keeps
+// max_length = max(suffix-automaton match over the snapshot, diagonal band over the tail); the automaton is rebuilt
+// every `interval` positions, as the planner's caller must.  keys, queries: int32 [n]; longest: int32 [n].
+int dism_ref_longest_lengths(const int *keys, const int *queries, int n, int interval, int *longest) {
+    try {
+        dism_decode::Planner planner(1, interval, 1, 2, 0.);
+        for (int p = 0; p < n; ++p) {
+            if (planner.needs_rebuild()) planner.rebuild();
+            planner.append(keys[p], queries[p], false);
+            longest[p] = planner.max_length;
+        }
         return 0;
     } catch (...) { return 1; }
 }

@@ -410,6 +410,44 @@ def test_bounded_wait_gives_up_and_reports(api):
     assert (api['cu'].labels(x, e) != reference).float().mean() < 1e-2 and labels_fault() == 0
 
 
+# ---- the two weight tables by themselves -----------------------------------------------------------------
+@pytest.mark.parametrize('n', [256, 2048])
+def test_log_weight_table_against_the_closed_form(api, oracle, n):
+    """lut[h, l] = log2 sum_{s=1..l} exp(s tau[h]) in FP64, at the reference's tolerance for the same table
+    (dism_v3/tests/test_hard_forward.py:60-71), and against the oracle's FP32 restatement."""
+    tau = torch.tensor([-4., -.5, -1e-6, -1e-12, 0., 1e-12, 1e-6, .5, 4.])
+    table = api['fwd'].hard_log_weights(tau.cuda(), n).cpu()
+    assert table.shape == (9, n + 1) and (table[:, 0] == -1e6).all()
+    length = np.arange(1, n + 1, dtype=np.float64)
+    t = tau.double().numpy()[:, None]
+    with np.errstate(divide='ignore', invalid='ignore'):
+        expected = (np.where(t > 0, length * t, t) + np.log(-np.expm1(-length * np.abs(t))) - np.log(-np.expm1(-np.abs(t)))) / np.log(2.)
+    expected[tau.numpy() == 0] = np.log2(length)
+    np.testing.assert_allclose(table[:, 1:].double().numpy(), expected, atol=2e-5, rtol=2e-6)
+    np.testing.assert_allclose(table.numpy(), oracle.lut(tau.numpy(), n), atol=2e-5, rtol=2e-6)
+
+
+def test_dlog_weight_table_against_the_moment_sums(api):
+    """g[h, l] = d ln W_l / d tau = sum s e^{s tau} / sum e^{s tau}, summed directly in FP64 (the formula of
+    dism_v3/docs/HARD_BACKWARD_QUADRATIC.md:60-75); the table the backward builds from the log2 table."""
+    from dism_b200 import _lib
+    n = 2048
+    tau = torch.tensor([-4., -.5, -.01, -1e-4, -1e-6, 0., 1e-6, 1e-4, .01, .5, 4.])
+    table = api['fwd'].hard_log_weights(tau.cuda(), n)
+    out = torch.full_like(table, float('nan'))
+    _lib.check(_lib.load().dism_hard_dlog_weights(table.data_ptr(), tau.numel(), n + 1, out.data_ptr(),
+                                                  torch.cuda.current_stream().cuda_stream))
+    got = out.cpu().double().numpy()
+    assert (got[:, 0] == 0).all()
+    s = np.arange(1, n + 1, dtype=np.float64)
+    lower = np.tril(np.ones((n, n)))
+    for row, t in enumerate(tau.double().numpy()):
+        # weights of row l scaled by their largest (s = l for tau > 0, s = 1 otherwise): nothing overflows or vanishes
+        scaled = np.exp(np.minimum((s[None, :] - (s[:, None] if t > 0 else 1.)) * t, 0.)) * lower
+        expected = (scaled * s[None, :]).sum(1) / scaled.sum(1)
+        np.testing.assert_allclose(got[row, 1:], expected, rtol=2e-4, atol=2e-4, err_msg=f'tau {t}')
+
+
 # ---- symbol streams: single longest earlier match -----------------------------------------------------
 def symbol_streams(batch, n, vocab, seed):
     rng = np.random.default_rng(seed)

@@ -126,3 +126,24 @@ def test_edge_cases(oracle):
     out, lse2 = oracle.forward(ones, ones, np.ones((1, n, 1, 64), np.float32), q, q, np.zeros((1, 1), bool),
                                np.array([.5], np.float32))
     assert not out.any() and not lse2.any()  # soft rows are skipped
+
+
+def test_longest_match_length_against_reference_planner(oracle):
+    """The one part of the single-longest-match quantity the reference defines: max_j L(i,j), which its decode
+    planner keeps as max_length (inference/csrc/planner.hpp:132-149, :253-270: suffix-automaton match over the
+    snapshot, diagonal band over the tail).  Self-matching streams exclude j = i, so the planner gets the stream
+    delayed by one position as its keys; the two-sided form is checked against the dense L as well."""
+    rng = np.random.default_rng(11)
+    if oracle.reference_longest_lengths(np.zeros(4, np.int32), np.zeros(4, np.int32)) is None:
+        pytest.skip('the reference planner was not built in this checkout')
+    for n, vocab in ((300, 3), (2048, 4), (1000, 50), (512, 1)):
+        s = rng.integers(0, vocab, n).astype(np.int32)
+        if n == 2048:
+            s[700:1200] = s[100:600]
+        end, length, nxt = oracle.longest(s)
+        delayed = np.concatenate([[-1], s[:-1]]).astype(np.int32)
+        for interval in (16, 64):
+            np.testing.assert_array_equal(oracle.reference_longest_lengths(delayed, s, interval), length)
+        q, k = rng.integers(0, vocab, 384).astype(np.int32), rng.integers(0, vocab, 384).astype(np.int32)
+        k[200:300] = q[210:310]
+        np.testing.assert_array_equal(oracle.reference_longest_lengths(k, q, 32), oracle.lengths(q, k).max(1))
