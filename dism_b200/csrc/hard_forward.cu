@@ -9,7 +9,7 @@
 // the reference (maximum starts at 0, denominator at 1).  A row is reduced by one warp in a fixed
 // order, so outputs do not depend on the grid size.  This file holds the table kernel, the
 // workspace layout and the launch; the tile kernel is in hard_forward_blocks.cuh.
-#include "hard_forward_blocks.cuh"
+#include "hard_forward_dense.cuh"
 
 namespace dism {
 
@@ -42,11 +42,29 @@ int device_sm_count() {
 }
 
 // Workspace: both position indices, the tile descriptors [BH, N/16 + BUCKETS] (16-byte records), the
-// first-tile table [BH, BUCKETS + 1] and one tile counter per (batch, head).
+// first-tile table [BH, BUCKETS + 1], one tile counter and one route word per (batch, head), and the
+// run-length rows of the dense route.
+static size_t plan_words_bytes(size_t batch_heads) { return (batch_heads * (BUCKETS + 3) * sizeof(int) + 15) & ~size_t(15); }
 size_t hard_forward_workspace_bytes(int batch, int heads, int n) {
     const size_t batch_heads = size_t(batch) * heads;
     return index_bytes(batch * heads, n, 2) + batch_heads * tile_capacity_for(n) * sizeof(int4) +
-           batch_heads * (BUCKETS + 2) * sizeof(int);
+           plan_words_bytes(batch_heads) + dense_bytes(batch * heads, n);
+}
+
+template <int R, int DV>
+static cudaError_t launch_dense(const DenseArgs& args, cudaStream_t stream) {
+    auto kernel = hard_forward_dense_kernel<R, DV>;
+    const int shared = sizeof(DenseWarpShared<R, DV>) * DENSE_WARPS;
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+    if (status != cudaSuccess) return status;
+    const int batch_heads = args.batch * args.heads;
+    {
+        KernelTimer timer("dense_boundary", stream);
+        dense_boundary_kernel<<<dim3((args.n + 255) / 256, batch_heads), 256, 0, stream>>>(args);
+    }
+    KernelTimer timer("hard_forward_dense", stream);
+    kernel<<<dim3(args.chunks, batch_heads), DENSE_WARPS * 32, shared, stream>>>(args);
+    return cudaGetLastError();
 }
 
 template <bool PACKED, int R, int DV>
@@ -98,17 +116,33 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
     args.next_tile = tile_starts + size_t(batch_heads) * (BUCKETS + 1);
     args.out = out; args.lse2 = lse2;
     args.batch = shape.batch; args.heads = shape.heads; args.n = shape.n; args.lut_stride = lut_stride;
+    // The dense route takes whole-sequence layouts whose length its 32-column steps divide; a (batch, head) goes
+    // there when at least a sixteenth of all N^2 pairs have equal labels.
+    int* route = args.next_tile + batch_heads;
+    const bool dense_allowed = !documents && shape.n % DENSE_COLUMNS == 0 && lut_stride > shape.n;
     {
         KernelTimer timer("plan_query_tiles", stream);
         plan_query_tiles_kernel<<<batch_heads, 1024, 0, stream>>>(args.queries.starts, args.keys.starts, tile_starts, tiles,
-                                                                  args.next_tile, args.tile_capacity);
+                                                                  args.next_tile, args.tile_capacity, route,
+                                                                  dense_allowed ? (unsigned long long)(shape.n) * shape.n / 16 : ~0ull);
     }
-#define DISM_CASE(RR, VV) \
-    if (shape.r == RR && shape.dv == VV) return launch_blocks_variant<RR, VV>(args, ctas, stream);
+    DenseArgs dense{};
+    dense.sq = sq; dense.sk = sk; dense.v = v; dense.iq = iq; dense.ik = ik; dense.hard = hard; dense.lut = lut;
+    dense.route = route;
+    dense.rows = reinterpret_cast<int*>(reinterpret_cast<char*>(tile_starts) + plan_words_bytes(batch_heads));
+    dense.out = out; dense.lse2 = lse2;
+    dense.batch = shape.batch; dense.heads = shape.heads; dense.n = shape.n; dense.lut_stride = lut_stride;
+    dense.chunks = dense_chunks(batch_heads, shape.n);
+    cudaError_t status_blocks = cudaErrorInvalidValue;
+#define DISM_CASE(RR, VV)                                                                   \
+    if (shape.r == RR && shape.dv == VV) {                                                  \
+        status_blocks = launch_blocks_variant<RR, VV>(args, ctas, stream);                  \
+        if (status_blocks == cudaSuccess && dense_allowed) status_blocks = launch_dense<RR, VV>(dense, stream); \
+    }
     DISM_CASE(16, 32) DISM_CASE(16, 64) DISM_CASE(16, 128)
     DISM_CASE(32, 32) DISM_CASE(32, 64) DISM_CASE(32, 128)
 #undef DISM_CASE
-    return cudaErrorInvalidValue;
+    return status_blocks;
 }
 
 }  // namespace dism

@@ -79,21 +79,34 @@ struct BlockArgs {
 __host__ __device__ inline int tile_capacity_for(int n) { return n / QT + BUCKETS; }
 
 // tile_starts[b] = number of 16-query tiles in the buckets before b, and one descriptor per tile.
+// With `route` set, a (batch, head) whose buckets hold at least dense_pairs label-matching pairs (causal or not) is
+// marked for the dense kernel instead (route word 1) and gets no tiles here.
 __device__ __forceinline__ void plan_query_tiles(const int* __restrict__ query_starts, const int* __restrict__ key_starts,
                                                  int* __restrict__ tile_starts, int4* __restrict__ tiles,
-                                                 int* __restrict__ next_tile, int tile_capacity) {
+                                                 int* __restrict__ next_tile, int tile_capacity, int* __restrict__ route = nullptr,
+                                                 unsigned long long dense_pairs = 0) {
     constexpr int PER = BUCKETS / 1024;
     __shared__ int warp_total[32];
+    __shared__ unsigned long long warp_pairs[32];
+    __shared__ int dense;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     query_starts += int64_t(blockIdx.x) * (BUCKETS + 1);
     key_starts += int64_t(blockIdx.x) * (BUCKETS + 1);
     tile_starts += int64_t(blockIdx.x) * (BUCKETS + 1);
     tiles += int64_t(blockIdx.x) * tile_capacity;
     int local[PER], sum = 0;
+    unsigned long long pairs = 0;
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
         local[e] = sum;
-        sum += (query_starts[tid * PER + e + 1] - query_starts[tid * PER + e] + QT - 1) / QT;
+        const int queries = query_starts[tid * PER + e + 1] - query_starts[tid * PER + e];
+        sum += (queries + QT - 1) / QT;
+        pairs += (unsigned long long)(queries) * (unsigned long long)(key_starts[tid * PER + e + 1] - key_starts[tid * PER + e]);
+    }
+    if (route) {
+#pragma unroll
+        for (int s = 16; s; s >>= 1) pairs += __shfl_xor_sync(FULL, pairs, s);
+        if (lane == 0) warp_pairs[warp] = pairs;
     }
     int prefix = sum;
 #pragma unroll
@@ -103,6 +116,12 @@ __device__ __forceinline__ void plan_query_tiles(const int* __restrict__ query_s
     }
     if (lane == 31) warp_total[warp] = prefix;
     __syncthreads();
+    if (route && tid == 0) {
+        unsigned long long all = 0;
+        for (int w = 0; w < 32; ++w) all += warp_pairs[w];
+        dense = all >= dense_pairs;
+        route[blockIdx.x] = dense;
+    }
     if (warp == 0) {
         const int mine = warp_total[lane];
         int scan = mine;
@@ -124,15 +143,15 @@ __device__ __forceinline__ void plan_query_tiles(const int* __restrict__ query_s
         for (int q = q0, tile = first; q < q1; q += QT, ++tile) tiles[tile] = make_int4(q, min(QT, q1 - q), k0, k1);
     }
     if (tid == 1023) {
-        tile_starts[BUCKETS] = before + sum;
+        tile_starts[BUCKETS] = route && dense ? 0 : before + sum;  // `dense` was written before the last barrier
         next_tile[blockIdx.x] = 0;
     }
 }
 
 static __global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int* query_starts, const int* key_starts,
                                                                        int* tile_starts, int4* tiles, int* next_tile,
-                                                                       int tile_capacity) {
-    plan_query_tiles(query_starts, key_starts, tile_starts, tiles, next_tile, tile_capacity);
+                                                                       int tile_capacity, int* route, unsigned long long dense_pairs) {
+    plan_query_tiles(query_starts, key_starts, tile_starts, tiles, next_tile, tile_capacity, route, dense_pairs);
 }
 
 // Two plans in one launch (the backward's query-major and key-major tiles): blockIdx.y picks the plan.

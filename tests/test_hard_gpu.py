@@ -111,6 +111,31 @@ def test_forward_matches_oracle(api, oracle, pattern, n):
     torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
 
 
+@pytest.mark.parametrize('n,r,dv', [(1024, 32, 64), (2048, 16, 128), (4096, 32, 32)])
+def test_forward_dense_labels_take_the_consecutive_tile_kernel(api, oracle, n, r, dv):
+    """Slices where at least a sixteenth of all pairs match go to the dense kernel: all labels equal, a period of
+    seven, two symbols at random; a slice of sparse labels and a slice that is not hard sit in the same call.  The
+    reference tests these patterns for its strip stages (dism_v3/tests/test_hard_summary.py:70,
+    tests/test_hard_chunk.py:39) and benchmarks equal labels (tools/bench_hard_forward.py:24-28)."""
+    rng = np.random.default_rng(n)
+    q, k = np.empty((2, 3, n), np.int32), np.empty((2, 3, n), np.int32)
+    q[0, 0], k[0, 0] = 5, 5
+    q[0, 1] = k[0, 1] = np.arange(n) % 7
+    q[0, 2], k[0, 2] = rng.integers(0, 2, n), rng.integers(0, 2, n)
+    q[1, 0], k[1, 0] = rng.integers(0, 300, n), rng.integers(0, 300, n)   # sparse: stays with the label-block kernel
+    q[1, 1], k[1, 1] = 9, 9                                                  # dense but not hard: zeros
+    q[1, 2] = np.arange(n) % 3
+    k[1, 2] = (np.arange(n) + 1) % 3
+    hard = np.array([[True, True, True], [True, False, True]])
+    sq, sk, v, _ = vectors(n, 2, n, 3, r, dv)
+    tau = torch.tensor([-.02, .3, -.6])
+    out, norm = api['fwd'].forward_hard(sq.cuda(), sk.cuda(), v.cuda(), dev(q), dev(k), dev(hard), tau.cuda())
+    expected, lse2 = oracle.forward(sq.float().numpy(), sk.float().numpy(), v.float().numpy(), q, k, hard, tau.numpy(), threads=8)
+    assert_vectors(out, expected)
+    torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
+    assert not out[1, :, 1].count_nonzero() and not norm[1, 1].count_nonzero()
+
+
 def test_forward_long_chain_tau_sweep(api):
     g = golden('chain_equal.npz')
     x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
