@@ -154,9 +154,10 @@ def run_ours(args):
         grads = backward_hard(x['sq'], x['sk'], x['v'], x['dout'], iq, ik, params['hard'], norm,
                               dict(boundary=None, log_weights=lut))
         mark()
-        # labels of q and k (one launch); readout: log weights, index, tiles, forward; log weights; backward: their
-        # derivative, tiles (both plans in one launch), query-major, key-major, tau reduction (the index is the readout's)
-        launches[0] += 1 + 4 + 1 + 5
+        # labels of q and k (one launch); readout: log weights, index, tiles, label-block kernel, dense-route kernel (its
+        # CTAs return at once on these labels); log weights; backward: tiles of both passes with the dlog table (one
+        # launch), query-major, key-major, dense-route kernel, tau reduction (the index is the readout's)
+        launches[0] += 1 + 5 + 1 + 5
         return out, norm, grads
 
     def _event():
@@ -522,6 +523,27 @@ def run_other_workload(args):
                           'ms_labels': ms_labels, 'ms_forward': ms_forward, 'kernel_ms': kernel_ms,
                           'max_log2_normaliser': float(norm.max()),
                           'steps': args.steps, 'warmup': args.warmup}))
+    elif args.workload == 'dense_labels':
+        # the shape of the reference's own hard-forward benchmark (dism_v3/tools/bench_hard_forward.py:18: B16 N2048 H6 R32
+        # DV64, tau .5, labels uniform over 512 symbols or all equal), fixed layout: complete forward and backward
+        from flash_dism.hard_forward import hard_log_weights
+        from flash_dism.hard_backward import backward_hard
+        b, n, h, r, dv = 16, 2048, 6, 32, 64
+        sq, sk = [(torch.randn(b, n, h, r, generator=g, device='cuda') * .3).bfloat16() for _ in range(2)]
+        v, dout = [torch.randn(b, n, h, dv, generator=g, device='cuda').bfloat16() for _ in range(2)]
+        hard, tau = torch.ones(b, h, dtype=torch.bool, device='cuda'), torch.full((h,), .5, device='cuda')
+        record = {'workload': 'hard forward and backward, B16 N2048 H6 R32 DV64, labels over 512 symbols or all equal', 'ms': {}}
+        for pattern in ('random', 'equal'):
+            iq, ik = [torch.randint(0, 512, (b, h, n), generator=g, device='cuda', dtype=torch.int32) for _ in range(2)]
+            if pattern == 'equal':
+                iq.zero_(), ik.zero_()
+            _, norm = forward_hard(sq, sk, v, iq, ik, hard, tau)
+            lut = hard_log_weights(tau, n)
+            record['ms'][pattern] = {
+                'forward': timed(lambda: forward_hard(sq, sk, v, iq, ik, hard, tau)),
+                'backward': timed(lambda: backward_hard(sq, sk, v, dout, iq, ik, hard, norm, dict(boundary=None, log_weights=lut)))}
+        record.update(steps=args.steps, warmup=args.warmup)
+        print(json.dumps(record))
     else:
         batch, n = 4, 4096
         rng = np.random.default_rng(0)
@@ -627,7 +649,7 @@ def main():
     parser.add_argument('--kernels-only', action='store_true', help='skip the end-to-end and CPU-baseline legs')
     parser.add_argument('--share', type=int, default=0, help='with --kernels-only: time the head slice one of this many GPUs would get')
     parser.add_argument('--model-batch', type=int, default=16, help='sequences per GPU of the model workload')
-    parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams', 'model'],
+    parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams', 'dense_labels', 'model'],
                         help='side workloads print their own line; the benchmark contract is the training shape')
     args = parser.parse_args()
     SHAPE['batch'] = args.batch

@@ -9,15 +9,13 @@
 // accumulated by exactly one warp, tile by tile in ascending partner order, with no atomics, no
 // zero-filled accumulators and bit-identical results for any grid size.  Pair coefficients stay
 // in FP32 (the reference rounds them to BF16 to feed its tensor-core tiles).
-#include "hard_backward_blocks.cuh"
+#include "hard_backward_dense.cuh"
 
 namespace dism {
 
 // g[h,l] = d ln W_l / d tau with tau recovered from the log2 table (lut[h,1] = tau * log2 e).
-__global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __restrict__ out, int stride) {
-    int l = blockIdx.x * blockDim.x + threadIdx.x, head = blockIdx.y;
-    if (l >= stride) return;
-    float t = lut[int64_t(head) * stride + 1] * 0.6931471805599453f;
+__device__ __forceinline__ float dlog_weight(float table_one, int l) {
+    float t = table_one * 0.6931471805599453f;
     float a = fabsf(t), length = float(l), x = length * t, g = 0.f;
     if (l && fabsf(x) < .1f) {
         g = (length + 1.f) * .5f + (length * length - 1.f) * t * (1.f / 12.f - (x * x + t * t) * (1.f / 720.f));
@@ -26,7 +24,27 @@ __global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __rest
         float negative = __fdividef(1.f, -expm1f(-a)) - tail;
         g = t > 0 ? length + 1.f - negative : negative;
     }
-    out[int64_t(head) * stride + l] = g;
+    return g;
+}
+__global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __restrict__ out, int stride) {
+    int l = blockIdx.x * blockDim.x + threadIdx.x, head = blockIdx.y;
+    if (l >= stride) return;
+    out[int64_t(head) * stride + l] = dlog_weight(lut[int64_t(head) * stride + 1], l);
+}
+
+// What the backward prepares in one launch: blockIdx.y 0 and 1 plan the query-major and key-major tiles of
+// (batch, head) blockIdx.x (and choose its route); blockIdx.y 2 fills the dlog table, all CTAs of that row together.
+static __global__ __launch_bounds__(1024) void prepare_backward_kernel(const TilePlan first, const TilePlan second, int tile_capacity,
+                                                                       int* route, unsigned long long dense_pairs,
+                                                                       const float* __restrict__ lut, float* __restrict__ dlut,
+                                                                       int heads, int lut_stride) {
+    if (blockIdx.y == 2) {
+        for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < heads * lut_stride; e += gridDim.x * blockDim.x)
+            dlut[e] = dlog_weight(lut[int64_t(e / lut_stride) * lut_stride + 1], e % lut_stride);
+        return;
+    }
+    const TilePlan& plan = blockIdx.y ? second : first;
+    plan_query_tiles(plan.owner_starts, plan.partner_starts, plan.tile_starts, plan.tiles, plan.next_tile, tile_capacity, route, dense_pairs);
 }
 
 cudaError_t launch_dlog_weights(const float* lut, int heads, int lut_stride, float* out, cudaStream_t stream) {
@@ -68,9 +86,26 @@ static size_t plan_bytes(int batch_heads, int n) {
     return (bytes + 255) & ~size_t(255);
 }
 
+static size_t tables_bytes(int batch, int heads, int n, int lut_stride) {  // tau rows, dlog table, route words
+    const size_t bytes = sizeof(float) * (size_t(heads) * lut_stride + size_t(batch) * heads * n) + sizeof(int) * size_t(batch) * heads;
+    return (bytes + 15) & ~size_t(15);
+}
 size_t hard_backward_workspace_bytes(int batch, int heads, int n, int lut_stride) {
-    return index_bytes(batch * heads, n, 2) + 2 * plan_bytes(batch * heads, n) +
-           sizeof(float) * (size_t(heads) * lut_stride + size_t(batch) * heads * n);
+    return index_bytes(batch * heads, n, 2) + 2 * plan_bytes(batch * heads, n) + tables_bytes(batch, heads, n, lut_stride) +
+           dense_backward_bytes(batch * heads, n);
+}
+
+// One cooperative launch of one CTA per SM for both passes: see dense_route.cuh.
+template <int R, int DV>
+static cudaError_t launch_dense_backward(const DenseBackwardArgs& args, cudaStream_t stream) {
+    auto kernel = hard_backward_dense_kernel<R, DV>;
+    const int shared = sizeof(DenseBackwardWarpShared<R, DV>) * DENSE_WARPS;
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+    if (status != cudaSuccess) return status;
+    KernelTimer timer("hard_backward_dense", stream);
+    void* parameters[] = {const_cast<DenseBackwardArgs*>(&args)};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(device_sm_count()), dim3(DENSE_WARPS * 32), parameters,
+                                       shared, stream);
 }
 
 template <bool QUERY_MAJOR, bool PACKED, int R, int DV>
@@ -127,13 +162,17 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     }
     float* rows = reinterpret_cast<float*>(cursor);
     float* dlut = rows + size_t(batch_heads) * shape.n;
-    status = launch_dlog_weights(lut, shape.heads, lut_stride, dlut, stream);
-    if (status != cudaSuccess) return status;
+    int* route = reinterpret_cast<int*>(dlut + size_t(shape.heads) * lut_stride);
+    int* lines = reinterpret_cast<int*>(cursor + tables_bytes(shape.batch, shape.heads, shape.n, lut_stride));
+    // dense labels: the same rule as the forward (whole-sequence layout, a sixteenth of all pairs matching)
+    const bool dense_allowed = !documents && shape.n % DENSE_COLUMNS == 0 && lut_stride > shape.n;
     {
         KernelTimer timer("plan_tiles", stream);
         const TilePlan by_query{queries.starts, keys.starts, tile_starts[0], tiles[0], tile_starts[0] + size_t(batch_heads) * (BUCKETS + 1)};
         const TilePlan by_key{keys.starts, queries.starts, tile_starts[1], tiles[1], tile_starts[1] + size_t(batch_heads) * (BUCKETS + 1)};
-        plan_tile_pair_kernel<<<dim3(batch_heads, 2), 1024, 0, stream>>>(by_query, by_key, capacity);
+        prepare_backward_kernel<<<dim3(batch_heads, 3), 1024, 0, stream>>>(by_query, by_key, capacity, route,
+                                                                           dense_allowed ? (unsigned long long)(shape.n) * shape.n / 16 : ~0ull,
+                                                                           lut, dlut, shape.heads, lut_stride);
     }
     BackwardBlockArgs args{};
     args.sq = sq; args.sk = sk; args.v = v; args.dout = dout;
@@ -150,11 +189,18 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     by_key.owners = keys; by_key.partners = queries;
     by_key.tiles = tiles[1]; by_key.tile_starts = tile_starts[1];
     by_key.next_tile = tile_starts[1] + size_t(batch_heads) * (BUCKETS + 1);
+    DenseBackwardArgs dense{};
+    dense.sq = sq; dense.sk = sk; dense.v = v; dense.dout = dout; dense.iq = iq; dense.ik = ik; dense.hard = hard;
+    dense.lut = lut; dense.dlut = dlut; dense.lse2 = lse2; dense.route = route; dense.lines = lines;
+    dense.dsq = dsq; dense.dtau_rows = rows; dense.dsk = dsk; dense.dv = dv;
+    dense.batch = shape.batch; dense.heads = shape.heads; dense.n = shape.n; dense.lut_stride = lut_stride;
+    dense.chunks = dense_chunks(batch_heads, shape.n);
     status = cudaErrorInvalidValue;
 #define DISM_CASE(RR, VV)                                                                         \
     if (shape.r == RR && shape.dv == VV) {                                                        \
         status = launch_backward_blocks<true, RR, VV>(by_query, ctas, stream);                    \
         if (status == cudaSuccess) status = launch_backward_blocks<false, RR, VV>(by_key, ctas, stream); \
+        if (status == cudaSuccess && dense_allowed) status = launch_dense_backward<RR, VV>(dense, stream); \
     }
     DISM_CASE(16, 32) DISM_CASE(16, 64) DISM_CASE(16, 128)
     DISM_CASE(32, 32) DISM_CASE(32, 64) DISM_CASE(32, 128)

@@ -51,20 +51,17 @@ size_t hard_forward_workspace_bytes(int batch, int heads, int n) {
            plan_words_bytes(batch_heads) + dense_bytes(batch * heads, n);
 }
 
+// One cooperative launch of one CTA per SM (the kernel's shared memory allows no second one): see dense_route.cuh.
 template <int R, int DV>
 static cudaError_t launch_dense(const DenseArgs& args, cudaStream_t stream) {
     auto kernel = hard_forward_dense_kernel<R, DV>;
     const int shared = sizeof(DenseWarpShared<R, DV>) * DENSE_WARPS;
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
     if (status != cudaSuccess) return status;
-    const int batch_heads = args.batch * args.heads;
-    {
-        KernelTimer timer("dense_boundary", stream);
-        dense_boundary_kernel<<<dim3((args.n + 255) / 256, batch_heads), 256, 0, stream>>>(args);
-    }
     KernelTimer timer("hard_forward_dense", stream);
-    kernel<<<dim3(args.chunks, batch_heads), DENSE_WARPS * 32, shared, stream>>>(args);
-    return cudaGetLastError();
+    void* parameters[] = {const_cast<DenseArgs*>(&args)};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(device_sm_count()), dim3(DENSE_WARPS * 32), parameters,
+                                       shared, stream);
 }
 
 template <bool PACKED, int R, int DV>

@@ -18,7 +18,7 @@
 // normalisation (maximum starts at 0, denominator at 1).  Each row is reduced by one warp in a
 // fixed order: results do not depend on the grid.
 #pragma once
-#include "dism_common.cuh"
+#include "dense_route.cuh"
 
 namespace dism {
 
@@ -161,11 +161,6 @@ struct TilePlan {
     int4* tiles;
     int* next_tile;
 };
-static __global__ __launch_bounds__(1024) void plan_tile_pair_kernel(const TilePlan first, const TilePlan second, int tile_capacity) {
-    const TilePlan& plan = blockIdx.y ? second : first;
-    plan_query_tiles(plan.owner_starts, plan.partner_starts, plan.tile_starts, plan.tiles, plan.next_tile, tile_capacity);
-}
-
 // PACKED: rows carry document limits (a.documents is set); otherwise every row's document is the whole sequence
 // and the limits are constants the compiler folds away.
 template <bool PACKED, int R, int DV>

@@ -13,42 +13,19 @@
 // block of sixteen query rows follow from those of the row above it: one key column per lane, sixteen
 // steps, each taking the neighbouring lane's previous value.  A CTA owns a contiguous range of sixteen-row blocks
 // of one (batch, head) and sweeps it downwards, handing the last row's lengths to the next block
-// through a scratch row; the row above a CTA's first block comes from a prepass in which one thread
-// walks one whole diagonal.  Within a block the eight warps split the key columns into eight contiguous
+// through a scratch row; the row above a chunk's first block comes from a walk along whole
+// diagonals that the grid does before the sweeps (dense_route.cuh).  Within a block the eight warps split the key columns into eight contiguous
 // ranges and work through them thirty-two at a time: the lanes first turn their columns' run lengths
 // into log2 weights in shared memory, then the
 // warp does what a fused attention kernel does on sixteen-by-sixteen tiles (scores = SQ.SK^T,
 // online maximum from the weights, acc += (P o S).V, all bf16 mma.sync), and the warps' partial
 // rows are merged with the reference's normalisation (maximum starts at 0, denominator at 1).
 #pragma once
+#include <cooperative_groups.h>
+
 #include "hard_forward_blocks.cuh"
 
 namespace dism {
-
-constexpr int DENSE_ROWS = 16;     // query rows per block
-constexpr int DENSE_COLUMNS = 32;  // key columns per warp step: two tiles
-constexpr int DENSE_WARPS = 8;
-constexpr int DENSE_ROUTE = 1;     // route word of a (batch, head) that takes this path
-
-// Row chunks per (batch, head): enough CTAs for about two per SM of a 148-SM part, at least 128 rows each.
-__host__ __device__ inline int dense_chunks(int batch_heads, int n) {
-    int chunks = (296 + batch_heads - 1) / batch_heads;
-    if (chunks > n / 128) chunks = n / 128;
-    if (chunks > 64) chunks = 64;
-    return chunks < 1 ? 1 : chunks;
-}
-// First row block of chunk c: chunks have about equal numbers of causal pairs (rows weigh as their index).
-__host__ __device__ inline int dense_chunk_start(int chunk, int chunks, int n) {
-    const int blocks = n / DENSE_ROWS;
-    if (chunk <= 0) return 0;
-    if (chunk >= chunks) return blocks;
-    int start = int(float(blocks) * sqrtf(float(chunk) / float(chunks)));
-    return start > blocks ? blocks : start;
-}
-// Scratch of the dense route: per (batch, head) and chunk one prepass row and two sweep rows of N run lengths.
-__host__ __device__ inline size_t dense_bytes(int batch_heads, int n) {
-    return size_t(batch_heads) * dense_chunks(batch_heads, n) * 3 * size_t(n) * sizeof(int);
-}
 
 struct DenseArgs {
     const __nv_bfloat16 *sq, *sk, *v;
@@ -56,33 +33,11 @@ struct DenseArgs {
     const uint8_t* hard;
     const float* lut;
     const int* route;  // [BH]
-    int* rows;         // [BH, chunks, 3, N]: prepass row, then the two rows the sweep alternates between
+    int* rows;         // [BH, chunks, 3, N]: the row above the chunk, then the two rows the sweep alternates between
     __nv_bfloat16* out;
     float* lse2;
     int batch, heads, n, lut_stride, chunks;
 };
-
-// rows[bh][c][0][j] = L(i0 - 1, j) for the first row i0 of chunk c >= 1: thread d walks diagonal i - j = d.
-static __global__ __launch_bounds__(256) void dense_boundary_kernel(const DenseArgs a) {
-    const int bh = blockIdx.y;
-    if (a.route[bh] != DENSE_ROUTE || a.chunks < 2) return;
-    const int d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (d >= a.n) return;
-    const int* __restrict__ iq = a.iq + int64_t(bh) * a.n;
-    const int* __restrict__ ik = a.ik + int64_t(bh) * a.n;
-    int* rows = a.rows + int64_t(bh) * a.chunks * 3 * a.n;
-    int i = d, j = 0, run = 0;
-    for (int chunk = 1; chunk < a.chunks; ++chunk) {
-        const int wanted = dense_chunk_start(chunk, a.chunks, a.n) * DENSE_ROWS - 1;  // the row above the chunk's first
-        if (wanted < d) continue;  // the diagonal starts below that row
-        const int steps = wanted - i + 1;
-#pragma unroll 8
-        for (int s = 0; s < steps; ++s) run = __ldg(iq + i + s) == __ldg(ik + j + s) ? run + 1 : 0;
-        i += steps;
-        j += steps;
-        rows[int64_t(chunk) * 3 * a.n + j - 1] = run;
-    }
-}
 
 template <int R, int DV>
 struct alignas(16) DenseStage {
@@ -101,12 +56,11 @@ struct alignas(16) DenseWarpShared {
     float weight[DENSE_ROWS][DENSE_COLUMNS + 1];  // log2 weights of the current columns
 };
 
+// The sweep of one chunk of one (batch, head) by the whole CTA.
 template <int R, int DV>
-__global__ __launch_bounds__(DENSE_WARPS * 32, 1) void hard_forward_dense_kernel(const DenseArgs a) {
+__device__ __forceinline__ void hard_forward_dense_chunk(const DenseArgs& a, int bh, int chunk) {
     constexpr int KSTEPS = R / 16, VTILES = DV / 8;
     static_assert(sizeof(DenseWarpShared<R, DV>) >= sizeof(float) * DENSE_ROWS * (DV + 2), "the partial rows fit in the warp's stages");
-    const int bh = blockIdx.y, chunk = blockIdx.x;
-    if (a.route[bh] != DENSE_ROUTE) return;
     extern __shared__ __align__(16) unsigned char storage[];
     auto* shared = reinterpret_cast<DenseWarpShared<R, DV>*>(storage);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -313,6 +267,19 @@ __global__ __launch_bounds__(DENSE_WARPS * 32, 1) void hard_forward_dense_kernel
             if (lane == 0) a.lse2[int64_t(bh) * n + i0 + row] = top + log2f(total);
         }
         __syncthreads();  // the partial rows lie in the stages the next block loads into; next_row is complete
+    }
+}
+
+template <int R, int DV>
+__global__ __launch_bounds__(DENSE_WARPS * 32, 1) void hard_forward_dense_kernel(const DenseArgs a) {
+    const int batch_heads = a.batch * a.heads;
+    if (!dense_any(a.route, batch_heads)) return;
+    dense_walk_all(a.iq, a.ik, a.route, a.rows, 1, batch_heads, a.chunks, a.n);
+    __threadfence();
+    cooperative_groups::this_grid().sync();
+    for (int item = blockIdx.x; item < batch_heads * a.chunks; item += gridDim.x) {
+        const int bh = item / a.chunks;
+        if (a.route[bh] == DENSE_ROUTE) hard_forward_dense_chunk<R, DV>(a, bh, item % a.chunks);
     }
 }
 
