@@ -14,6 +14,7 @@ constexpr int DENSE_ROWS = 16;     // owners (query rows or key columns) per blo
 constexpr int DENSE_COLUMNS = 32;  // partners per warp step: two tiles
 constexpr int DENSE_WARPS = 8;
 constexpr int DENSE_ROUTE = 1;     // route word of a (batch, head) that takes the dense route
+constexpr int DENSE_SHARE = 10;    // it does when at least N^2 / DENSE_SHARE pairs (causal or not) have equal labels
 
 // Chunks per (batch, head): enough CTAs for about two per SM of a 148-SM part, at least 128 positions each.
 __host__ __device__ inline int dense_chunks(int batch_heads, int n) {

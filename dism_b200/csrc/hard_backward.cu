@@ -164,14 +164,14 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     float* dlut = rows + size_t(batch_heads) * shape.n;
     int* route = reinterpret_cast<int*>(dlut + size_t(shape.heads) * lut_stride);
     int* lines = reinterpret_cast<int*>(cursor + tables_bytes(shape.batch, shape.heads, shape.n, lut_stride));
-    // dense labels: the same rule as the forward (whole-sequence layout, a sixteenth of all pairs matching)
+    // dense labels: the same rule as the forward (whole-sequence layout, a tenth of all pairs matching)
     const bool dense_allowed = !documents && shape.n % DENSE_COLUMNS == 0 && lut_stride > shape.n;
     {
         KernelTimer timer("plan_tiles", stream);
         const TilePlan by_query{queries.starts, keys.starts, tile_starts[0], tiles[0], tile_starts[0] + size_t(batch_heads) * (BUCKETS + 1)};
         const TilePlan by_key{keys.starts, queries.starts, tile_starts[1], tiles[1], tile_starts[1] + size_t(batch_heads) * (BUCKETS + 1)};
         prepare_backward_kernel<<<dim3(batch_heads, 3), 1024, 0, stream>>>(by_query, by_key, capacity, route,
-                                                                           dense_allowed ? (unsigned long long)(shape.n) * shape.n / 16 : ~0ull,
+                                                                           dense_allowed ? (unsigned long long)(shape.n) * shape.n / DENSE_SHARE : ~0ull,
                                                                            lut, dlut, shape.heads, lut_stride);
     }
     BackwardBlockArgs args{};

@@ -114,14 +114,14 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
     args.out = out; args.lse2 = lse2;
     args.batch = shape.batch; args.heads = shape.heads; args.n = shape.n; args.lut_stride = lut_stride;
     // The dense route takes whole-sequence layouts whose length its 32-column steps divide; a (batch, head) goes
-    // there when at least a sixteenth of all N^2 pairs have equal labels.
+    // there when at least a tenth of all N^2 pairs have equal labels.
     int* route = args.next_tile + batch_heads;
     const bool dense_allowed = !documents && shape.n % DENSE_COLUMNS == 0 && lut_stride > shape.n;
     {
         KernelTimer timer("plan_query_tiles", stream);
         plan_query_tiles_kernel<<<batch_heads, 1024, 0, stream>>>(args.queries.starts, args.keys.starts, tile_starts, tiles,
                                                                   args.next_tile, args.tile_capacity, route,
-                                                                  dense_allowed ? (unsigned long long)(shape.n) * shape.n / 16 : ~0ull);
+                                                                  dense_allowed ? (unsigned long long)(shape.n) * shape.n / DENSE_SHARE : ~0ull);
     }
     DenseArgs dense{};
     dense.sq = sq; dense.sk = sk; dense.v = v; dense.iq = iq; dense.ik = ik; dense.hard = hard; dense.lut = lut;

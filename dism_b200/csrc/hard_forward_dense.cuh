@@ -6,7 +6,7 @@
 // cost when they are simply all visited, which is what the reference's tile kernel does
 // (dism_v3/src/hard_forward.cu:27-118 on the strip rectangle of hard_summary / hard_chunk).  The
 // plan kernel therefore counts the label-matching pairs of every (batch, head) from the bucket
-// sizes of the two indices and sends a slice whose count exceeds N^2/16 here; the label-block
+// sizes of the two indices and sends a slice whose count reaches N^2/10 here; the label-block
 // kernel then finds no tiles for that slice.
 //
 // Run lengths need no rectangle.  L(i, j) = 1 + L(i-1, j-1) on a match, so the run lengths of a

@@ -113,7 +113,7 @@ def test_forward_matches_oracle(api, oracle, pattern, n):
 
 @pytest.mark.parametrize('n,r,dv', [(1024, 32, 64), (2048, 16, 128), (4096, 32, 32)])
 def test_dense_labels_take_the_consecutive_tile_kernels(api, oracle, n, r, dv):
-    """Slices where at least a sixteenth of all pairs match go to the dense kernel: all labels equal, a period of
+    """Slices where at least a tenth of all pairs match go to the dense kernel: all labels equal, a period of
     seven, two symbols at random; a slice of sparse labels and a slice that is not hard sit in the same call.  The
     reference tests these patterns for its strip stages (dism_v3/tests/test_hard_summary.py:70,
     tests/test_hard_chunk.py:39) and benchmarks equal labels (tools/bench_hard_forward.py:24-28)."""
