@@ -44,8 +44,10 @@ __host__ __device__ inline size_t dense_bytes(int batch_heads, int n) {
 // line[c][0][.] of one (batch, head) and pass, for chunks c >= 1: the run lengths of the line before the chunk's
 // first owner o0: query-major L(o0 - 1, key) over keys, key-major L(query, o0 - 1) over queries.  The thread walks
 // diagonal query - key = d from its start, so one walk serves the lines of all chunks.
-static __device__ __forceinline__ void dense_walk_diagonal(const int* __restrict__ iq, const int* __restrict__ ik, int* lines,
-                                                           int chunks, int n, bool query_major, int d) {
+// With packed documents a run ends where the key would lie before the query's document, and begins at its first key.
+static __device__ __forceinline__ void dense_walk_diagonal(const int* __restrict__ iq, const int* __restrict__ ik,
+                                                           const int2* __restrict__ documents, int* lines, int chunks, int n,
+                                                           bool query_major, int d) {
     int i = d, j = 0, run = 0;
     for (int chunk = 1; chunk < chunks; ++chunk) {
         const int line = dense_owner_start(query_major, chunk, chunks, n) * DENSE_ROWS - 1;
@@ -53,21 +55,28 @@ static __device__ __forceinline__ void dense_walk_diagonal(const int* __restrict
         if (steps <= 0) continue;    // query-major: the diagonal starts below that row
         if (i + steps > n) break;    // key-major: the diagonal ends before that column
 #pragma unroll 8
-        for (int s = 0; s < steps; ++s) run = __ldg(iq + i + s) == __ldg(ik + j + s) ? run + 1 : 0;
+        for (int s = 0; s < steps; ++s) {
+            // a document's first key starts a run afresh: on the main diagonal the cell before it belongs to the
+            // previous document, elsewhere it lies outside the query's document and has ended the run already
+            const int first_key = documents ? __ldg(documents + ((i + s) >> 8)).x : 0;
+            if (j + s <= first_key) run = 0;
+            run = j + s >= first_key && __ldg(iq + i + s) == __ldg(ik + j + s) ? run + 1 : 0;
+        }
         i += steps;
         j += steps;
         lines[int64_t(chunk) * 3 * n + (query_major ? j - 1 : i - 1)] = run;
     }
 }
 // All diagonals of all dense slices, spread over the grid.  lines: [passes, BH, chunks, 3, N]; pass 0 is query-major.
-static __device__ __forceinline__ void dense_walk_all(const int* __restrict__ iq, const int* __restrict__ ik, const int* __restrict__ route,
-                                                      int* lines, int passes, int batch_heads, int chunks, int n) {
+static __device__ __forceinline__ void dense_walk_all(const int* __restrict__ iq, const int* __restrict__ ik,
+                                                      const int2* __restrict__ documents, const int* __restrict__ route, int* lines,
+                                                      int passes, int batch_heads, int chunks, int n) {
     if (chunks < 2) return;
     const int64_t total = int64_t(passes) * batch_heads * n;
     for (int64_t work = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; work < total; work += int64_t(gridDim.x) * blockDim.x) {
         const int slice = int(work / n), bh = slice % batch_heads;
         if (route[bh] != DENSE_ROUTE) continue;
-        dense_walk_diagonal(iq + int64_t(bh) * n, ik + int64_t(bh) * n, lines + int64_t(slice) * chunks * 3 * n, chunks, n,
+        dense_walk_diagonal(iq + int64_t(bh) * n, ik + int64_t(bh) * n, documents, lines + int64_t(slice) * chunks * 3 * n, chunks, n,
                             slice < batch_heads, int(work % n));
     }
 }

@@ -164,8 +164,8 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     float* dlut = rows + size_t(batch_heads) * shape.n;
     int* route = reinterpret_cast<int*>(dlut + size_t(shape.heads) * lut_stride);
     int* lines = reinterpret_cast<int*>(cursor + tables_bytes(shape.batch, shape.heads, shape.n, lut_stride));
-    // dense labels: the same rule as the forward (whole-sequence layout, a tenth of all pairs matching)
-    const bool dense_allowed = !documents && shape.n % DENSE_COLUMNS == 0 && lut_stride > shape.n;
+    // dense labels: the same rule as the forward (a tenth of all pairs matching)
+    const bool dense_allowed = shape.n % DENSE_COLUMNS == 0 && (documents || lut_stride > shape.n);  // (a pack's table length is checked by the caller)
     {
         KernelTimer timer("plan_tiles", stream);
         const TilePlan by_query{queries.starts, keys.starts, tile_starts[0], tiles[0], tile_starts[0] + size_t(batch_heads) * (BUCKETS + 1)};
@@ -190,7 +190,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     by_key.tiles = tiles[1]; by_key.tile_starts = tile_starts[1];
     by_key.next_tile = tile_starts[1] + size_t(batch_heads) * (BUCKETS + 1);
     DenseBackwardArgs dense{};
-    dense.sq = sq; dense.sk = sk; dense.v = v; dense.dout = dout; dense.iq = iq; dense.ik = ik; dense.hard = hard;
+    dense.sq = sq; dense.sk = sk; dense.v = v; dense.dout = dout; dense.iq = iq; dense.ik = ik; dense.hard = hard; dense.documents = documents; dense.hard_rows = hard_rows;
     dense.lut = lut; dense.dlut = dlut; dense.lse2 = lse2; dense.route = route; dense.lines = lines;
     dense.dsq = dsq; dense.dtau_rows = rows; dense.dsk = dsk; dense.dv = dv;
     dense.batch = shape.batch; dense.heads = shape.heads; dense.n = shape.n; dense.lut_stride = lut_stride;

@@ -25,6 +25,8 @@ struct DenseBackwardArgs {
     const __nv_bfloat16 *sq, *sk, *v, *dout;
     const int *iq, *ik;
     const uint8_t* hard;
+    const int2* documents;  // packed layouts: (first position, end) of the document of every 256-position block; else null
+    int hard_rows;          // packed layouts: training rows the hard flags are given for
     const float *lut, *dlut, *lse2;
     const int* route;  // [BH]
     int* lines;        // [2 passes, BH, chunks, 3, N]: the vector before the chunk, then the two vectors the sweep alternates between
@@ -79,22 +81,6 @@ __device__ __forceinline__ void hard_backward_dense_chunk(const DenseBackwardArg
     const char* a_lane = reinterpret_cast<const char*>(other_a + vec0 * R) + (lane % (R / 8)) * 16;
     const char* b_lane = reinterpret_cast<const char*>(other_b + vec0 * DV) + (lane % (DV / 8)) * 16;
 
-    if (!a.hard[b * a.heads + h]) {  // rows that are not hard have zero gradients
-        const int rows = (last_block - first_block) * DENSE_ROWS;
-        for (int e = threadIdx.x; e < rows * 32; e += blockDim.x) {
-            const int row = first_block * DENSE_ROWS + e / 32, piece = e % 32;
-            const int64_t at = vec0 + int64_t(row) * a.heads;
-            if (QUERY_MAJOR) {
-                if (piece < R / 4) reinterpret_cast<float4*>(a.dsq + at * R)[piece] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (piece == 31) a.dtau_rows[int64_t(bh) * n + row] = 0.f;
-            } else {
-                if (piece < R / 8) reinterpret_cast<uint4*>(a.dsk + at * R)[piece] = make_uint4(0u, 0u, 0u, 0u);
-                if (piece >= 16 && piece - 16 < DV / 8) reinterpret_cast<uint4*>(a.dv + at * DV)[piece - 16] = make_uint4(0u, 0u, 0u, 0u);
-            }
-        }
-        return;
-    }
-
     auto stage_partners = [&](DenseBackwardStage<R, DV>& stage, int c0) {  // partners c0 .. c0 + 31 (all below n)
         constexpr int A_ROWS = 32 / (R / 8), B_ROWS = 32 / (DV / 8);
 #pragma unroll
@@ -110,9 +96,31 @@ __device__ __forceinline__ void hard_backward_dense_chunk(const DenseBackwardArg
         const int o0 = block * DENSE_ROWS;  // first owner of the block
         const int* previous_line = block == first_block ? lines : lines + (1 + (block & 1)) * int64_t(n);
         int* next_line = lines + (1 + ((block + 1) & 1)) * int64_t(n);
-        // 32-partner steps on the causal side: keys up to the block's last query, or queries from the block's first key
-        const int low_step = QUERY_MAJOR ? 0 : o0 / DENSE_COLUMNS;
-        const int high_step = QUERY_MAJOR ? (o0 + DENSE_ROWS + DENSE_COLUMNS - 1) / DENSE_COLUMNS : n / DENSE_COLUMNS;
+        // A block lies inside one document (documents begin at multiples of 256) and one training row.
+        int begin = 0, end = n;
+        if (a.documents) {
+            const int2 document = __ldg(a.documents + o0 / 256);
+            begin = document.x;
+            end = document.y;
+        }
+        if (!a.hard[(a.documents ? o0 / (n / a.hard_rows) : b) * a.heads + h]) {  // rows that are not hard have zero gradients
+            for (int e = threadIdx.x; e < DENSE_ROWS * 32; e += blockDim.x) {
+                const int row = o0 + e / 32, piece = e % 32;
+                const int64_t at = vec0 + int64_t(row) * a.heads;
+                if (QUERY_MAJOR) {
+                    if (piece < R / 4) reinterpret_cast<float4*>(a.dsq + at * R)[piece] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (piece == 31) a.dtau_rows[int64_t(bh) * n + row] = 0.f;
+                } else {
+                    if (piece < R / 8) reinterpret_cast<uint4*>(a.dsk + at * R)[piece] = make_uint4(0u, 0u, 0u, 0u);
+                    if (piece >= 16 && piece - 16 < DV / 8) reinterpret_cast<uint4*>(a.dv + at * DV)[piece - 16] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            continue;
+        }
+        // 32-partner steps on the causal side inside the document: keys from its start up to the block's last query, or
+        // queries from the block's first key to its end
+        const int low_step = QUERY_MAJOR ? begin / DENSE_COLUMNS : o0 / DENSE_COLUMNS;
+        const int high_step = QUERY_MAJOR ? (o0 + DENSE_ROWS + DENSE_COLUMNS - 1) / DENSE_COLUMNS : end / DENSE_COLUMNS;
         const int first_step = low_step + warp * (high_step - low_step) / DENSE_WARPS;
         const int last_step = low_step + (warp + 1) * (high_step - low_step) / DENSE_WARPS;
 
@@ -139,7 +147,7 @@ __device__ __forceinline__ void hard_backward_dense_chunk(const DenseBackwardArg
         for (int r = 0; r < DENSE_ROWS; ++r) {
             owner_label[r] = __ldg(owner_labels + o0 + r);
             owner_norm[r] = QUERY_MAJOR ? __ldg(lse2 + o0 + r) : 0.f;
-            owner_center[r] = QUERY_MAJOR ? __ldg(dlut + o0 + r + 1) : 0.f;
+            owner_center[r] = QUERY_MAJOR ? __ldg(dlut + o0 + r - begin + 1) : 0.f;
         }
 
         float grad_a[RTILES][4], grad_b[QUERY_MAJOR ? 1 : VTILES][4];
@@ -157,7 +165,8 @@ __device__ __forceinline__ void hard_backward_dense_chunk(const DenseBackwardArg
             const int partner = c0 + lane;
             const int partner_label = __ldg(partner_labels + partner);
             const float partner_norm = QUERY_MAJOR ? 0.f : __ldg(lse2 + partner);
-            const bool has_above = QUERY_MAJOR ? partner >= 1 && partner <= o0 : o0 >= 1 && partner >= o0;
+            // the cell up and to the left exists inside the document and on the causal side
+            const bool has_above = QUERY_MAJOR ? partner >= begin + 1 && partner <= o0 : o0 >= begin + 1 && partner >= o0;
             int above = has_above ? previous_line[partner - 1] : 0;
             int run = 0, passed_on = 0;
 #pragma unroll
@@ -181,7 +190,7 @@ __device__ __forceinline__ void hard_backward_dense_chunk(const DenseBackwardArg
         };
 #pragma unroll
         for (int r = 0; r < DENSE_ROWS; ++r) edge[r] = 0;
-        if (first_step > 0 && first_step < last_step) run_lengths((first_step - 1) * DENSE_COLUMNS, false);
+        if (first_step > low_step && first_step < last_step) run_lengths((first_step - 1) * DENSE_COLUMNS, false);
 
         int buffer = 0;
         for (int step = first_step; step < last_step; ++step, buffer ^= 1) {
@@ -310,7 +319,7 @@ __device__ __forceinline__ void hard_backward_dense_chunk(const DenseBackwardArg
 #pragma unroll
                     for (int m = 0; m < 4; ++m) total[m] += shared[wp].partial.moments[m][row];
                 // centred four-moment form: the fallback has unit weight and zero derivative
-                const float norm = __ldg(lse2 + o0 + row), center = __ldg(dlut + o0 + row + 1);
+                const float norm = __ldg(lse2 + o0 + row), center = __ldg(dlut + o0 + row - begin + 1);
                 const float fallback = ex2(-norm), inverse = __fdividef(1.f, total[1] + fallback);
                 const float mean = fmaf(-fallback, center, total[2]) * inverse;
                 a.dtau_rows[int64_t(bh) * n + o0 + row] = fmaf(-total[0], mean, total[3]) * inverse;
@@ -337,7 +346,7 @@ template <int R, int DV>
 __global__ __launch_bounds__(DENSE_WARPS * 32, 1) void hard_backward_dense_kernel(const DenseBackwardArgs a) {
     const int batch_heads = a.batch * a.heads;
     if (!dense_any(a.route, batch_heads)) return;
-    dense_walk_all(a.iq, a.ik, a.route, a.lines, 2, batch_heads, a.chunks, a.n);
+    dense_walk_all(a.iq, a.ik, a.documents, a.route, a.lines, 2, batch_heads, a.chunks, a.n);
     __threadfence();
     cooperative_groups::this_grid().sync();
     for (int item = blockIdx.x; item < 2 * batch_heads * a.chunks; item += gridDim.x) {

@@ -113,10 +113,10 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
     args.next_tile = tile_starts + size_t(batch_heads) * (BUCKETS + 1);
     args.out = out; args.lse2 = lse2;
     args.batch = shape.batch; args.heads = shape.heads; args.n = shape.n; args.lut_stride = lut_stride;
-    // The dense route takes whole-sequence layouts whose length its 32-column steps divide; a (batch, head) goes
+    // The dense route takes sequences whose length its 32-column steps divide (packed or not); a (batch, head) goes
     // there when at least a tenth of all N^2 pairs have equal labels.
     int* route = args.next_tile + batch_heads;
-    const bool dense_allowed = !documents && shape.n % DENSE_COLUMNS == 0 && lut_stride > shape.n;
+    const bool dense_allowed = shape.n % DENSE_COLUMNS == 0 && (documents || lut_stride > shape.n);  // (a pack's table length is checked by the caller)
     {
         KernelTimer timer("plan_query_tiles", stream);
         plan_query_tiles_kernel<<<batch_heads, 1024, 0, stream>>>(args.queries.starts, args.keys.starts, tile_starts, tiles,
@@ -124,7 +124,7 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
                                                                   dense_allowed ? (unsigned long long)(shape.n) * shape.n / DENSE_SHARE : ~0ull);
     }
     DenseArgs dense{};
-    dense.sq = sq; dense.sk = sk; dense.v = v; dense.iq = iq; dense.ik = ik; dense.hard = hard; dense.lut = lut;
+    dense.sq = sq; dense.sk = sk; dense.v = v; dense.iq = iq; dense.ik = ik; dense.hard = hard; dense.documents = documents; dense.hard_rows = hard_rows; dense.lut = lut;
     dense.route = route;
     dense.rows = reinterpret_cast<int*>(reinterpret_cast<char*>(tile_starts) + plan_words_bytes(batch_heads));
     dense.out = out; dense.lse2 = lse2;

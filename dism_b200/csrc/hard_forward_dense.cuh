@@ -31,6 +31,8 @@ struct DenseArgs {
     const __nv_bfloat16 *sq, *sk, *v;
     const int *iq, *ik;
     const uint8_t* hard;
+    const int2* documents;  // packed layouts: (first position, end) of the document of every 256-position block; else null
+    int hard_rows;          // packed layouts: training rows the hard flags are given for
     const float* lut;
     const int* route;  // [BH]
     int* rows;         // [BH, chunks, 3, N]: the row above the chunk, then the two rows the sweep alternates between
@@ -72,19 +74,9 @@ __device__ __forceinline__ void hard_forward_dense_chunk(const DenseArgs& a, int
     const float* __restrict__ lut = a.lut + int64_t(h) * a.lut_stride;
     int* rows = a.rows + (int64_t(bh) * a.chunks + chunk) * 3 * n;
     const int first_block = dense_chunk_start(chunk, a.chunks, n), last_block = dense_chunk_start(chunk + 1, a.chunks, n);
-    const bool active = a.hard[b * a.heads + h] != 0;
     const unsigned sk_stride = unsigned(a.heads) * R * 2, v_stride = unsigned(a.heads) * DV * 2;
     const char* sk_lane = reinterpret_cast<const char*>(a.sk + vec0 * R) + (lane % (R / 8)) * 16;
     const char* v_lane = reinterpret_cast<const char*>(a.v + vec0 * DV) + (lane % (DV / 8)) * 16;
-
-    if (!active) {  // rows that are not hard read as zero, like everywhere else on this path
-        for (int e = threadIdx.x; e < (last_block - first_block) * DENSE_ROWS * (DV / 8); e += blockDim.x) {
-            const int row = first_block * DENSE_ROWS + e / (DV / 8);
-            reinterpret_cast<uint4*>(a.out + (vec0 + int64_t(row) * a.heads) * DV)[e % (DV / 8)] = make_uint4(0u, 0u, 0u, 0u);
-            if (e % (DV / 8) == 0) a.lse2[int64_t(bh) * n + row] = 0.f;
-        }
-        return;
-    }
 
     auto stage_columns = [&](DenseStage<R, DV>& stage, int c0) {  // rows c0 .. c0 + 31 of sk and v (all below n)
         constexpr int SK_ROWS = 32 / (R / 8), V_ROWS = 32 / (DV / 8);
@@ -101,7 +93,20 @@ __device__ __forceinline__ void hard_forward_dense_chunk(const DenseArgs& a, int
         const int i0 = block * DENSE_ROWS;
         const int* previous_row = block == first_block ? rows : rows + (1 + (block & 1)) * int64_t(n);  // L(i0 - 1, .)
         int* next_row = rows + (1 + ((block + 1) & 1)) * int64_t(n);                                    // L(i0 + 15, .)
-        const int steps = (i0 + DENSE_ROWS + DENSE_COLUMNS - 1) / DENSE_COLUMNS;  // 32-column steps that hold causal pairs
+        // A block lies inside one document (documents begin at multiples of 256) and one training row: its keys start
+        // at the document's first position, and its rows are hard or not together.
+        const int begin = a.documents ? __ldg(a.documents + i0 / 256).x : 0;
+        const bool active = a.hard[(a.documents ? i0 / (n / a.hard_rows) : b) * a.heads + h] != 0;
+        if (!active) {  // rows that are not hard read as zero, like everywhere else on this path; nothing follows from them
+            for (int e = threadIdx.x; e < DENSE_ROWS * (DV / 8); e += blockDim.x) {
+                const int row = i0 + e / (DV / 8);
+                reinterpret_cast<uint4*>(a.out + (vec0 + int64_t(row) * a.heads) * DV)[e % (DV / 8)] = make_uint4(0u, 0u, 0u, 0u);
+                if (e % (DV / 8) == 0) a.lse2[int64_t(bh) * n + row] = 0.f;
+            }
+            continue;
+        }
+        const int low_step = begin / DENSE_COLUMNS;
+        const int steps = (i0 + DENSE_ROWS + DENSE_COLUMNS - 1) / DENSE_COLUMNS;  // 32-column steps up to the causal edge
 
         unsigned query[KSTEPS][4];
 #pragma unroll
@@ -122,7 +127,8 @@ __device__ __forceinline__ void hard_forward_dense_chunk(const DenseArgs& a, int
         for (int c = 0; c < VTILES; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
 
         // this warp's share of the block's columns: a contiguous run of 32-column steps
-        const int first_step = warp * steps / DENSE_WARPS, last_step = (warp + 1) * steps / DENSE_WARPS;
+        const int first_step = low_step + warp * (steps - low_step) / DENSE_WARPS;
+        const int last_step = low_step + (warp + 1) * (steps - low_step) / DENSE_WARPS;
         if (first_step < last_step) stage_columns(mine.stage[0], first_step * DENSE_COLUMNS);
 
         // Run lengths, one key column per lane: L(i0 + r, c) = pair ? L(i0 + r - 1, c - 1) + 1 : 0.  The cell up and to the
@@ -131,7 +137,8 @@ __device__ __forceinline__ void hard_forward_dense_chunk(const DenseArgs& a, int
         auto run_lengths = [&](int c0, bool keep) {
             const int column = c0 + lane;
             const int key_label = __ldg(ik + column);
-            int above = column >= 1 && column <= i0 ? previous_row[column - 1] : 0;  // L(i0 - 1, column - 1); none on the non-causal side
+            // L(i0 - 1, column - 1): none before the document's first key, none on the non-causal side
+            int above = column >= begin + 1 && column <= i0 ? previous_row[column - 1] : 0;
             int run = 0, passed_on = 0;  // passed_on: the previous row's run of the last column, the next step's edge
 #pragma unroll
             for (int r = 0; r < DENSE_ROWS; ++r) {
@@ -151,7 +158,7 @@ __device__ __forceinline__ void hard_forward_dense_chunk(const DenseArgs& a, int
         for (int r = 0; r < DENSE_ROWS; ++r) edge[r] = 0;
         // The first step's edge comes from the 32 columns before it, worked through without an edge of their own: a wrong
         // cell in their first column moves one column per row and cannot reach their last column within sixteen rows.
-        if (first_step > 0 && first_step < last_step) run_lengths((first_step - 1) * DENSE_COLUMNS, false);
+        if (first_step > low_step && first_step < last_step) run_lengths((first_step - 1) * DENSE_COLUMNS, false);
 
         int buffer = 0;
         for (int step = first_step; step < last_step; ++step, buffer ^= 1) {
@@ -274,7 +281,7 @@ template <int R, int DV>
 __global__ __launch_bounds__(DENSE_WARPS * 32, 1) void hard_forward_dense_kernel(const DenseArgs a) {
     const int batch_heads = a.batch * a.heads;
     if (!dense_any(a.route, batch_heads)) return;
-    dense_walk_all(a.iq, a.ik, a.route, a.rows, 1, batch_heads, a.chunks, a.n);
+    dense_walk_all(a.iq, a.ik, a.documents, a.route, a.rows, 1, batch_heads, a.chunks, a.n);
     __threadfence();
     cooperative_groups::this_grid().sync();
     for (int item = blockIdx.x; item < batch_heads * a.chunks; item += gridDim.x) {
