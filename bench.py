@@ -533,7 +533,7 @@ def run_other_workload(args):
         v, dout = [torch.randn(b, n, h, dv, generator=g, device='cuda').bfloat16() for _ in range(2)]
         hard, tau = torch.ones(b, h, dtype=torch.bool, device='cuda'), torch.full((h,), .5, device='cuda')
         record = {'workload': 'hard forward and backward, B16 N2048 H6 R32 DV64, labels over 512 symbols or all equal', 'ms': {}}
-        for pattern in ('random', 'equal'):
+        for pattern in ('equal', 'random'):
             iq, ik = [torch.randint(0, 512, (b, h, n), generator=g, device='cuda', dtype=torch.int32) for _ in range(2)]
             if pattern == 'equal':
                 iq.zero_(), ik.zero_()
