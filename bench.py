@@ -123,7 +123,7 @@ def run_ours(args):
     import dism_b200
     dism_b200.install_dropin()
     import cu_flash_dism as cu
-    from flash_dism.hard_forward import forward_hard, hard_log_weights
+    from flash_dism.hard_forward import forward_hard, hard_readout, hard_log_weights
     from flash_dism.hard_backward import backward_hard
 
     rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
@@ -148,16 +148,16 @@ def run_ours(args):
         mark()
         iq, ik = cu.labels_pair(x['q'], params['eq'], x['k'], params['ek'])
         mark()
-        out, norm = forward_hard(x['sq'], x['sk'], x['v'], iq, ik, params['hard'], params['tau'])
+        lut = hard_log_weights(params['tau'], s['n'])  # built once per step, as forward_hard(save_state=True) keeps it for the backward
+        out, norm = hard_readout(x['sq'], x['sk'], x['v'], iq, ik, params['hard'], None, lut)
         mark()
-        lut = hard_log_weights(params['tau'], s['n'])
         grads = backward_hard(x['sq'], x['sk'], x['v'], x['dout'], iq, ik, params['hard'], norm,
                               dict(boundary=None, log_weights=lut))
         mark()
-        # labels of q and k (one launch); readout: log weights, index, tiles, label-block kernel, dense-route kernel (its
-        # CTAs return at once on these labels); log weights; backward: tiles of both passes with the dlog table (one
-        # launch), query-major, key-major, dense-route kernel, tau reduction (the index is the readout's)
-        launches[0] += 1 + 5 + 1 + 5
+        # labels of q and k (one launch); log weights; readout: index, tiles, label-block kernel, dense-route kernel (its
+        # CTAs return at once on these labels); backward: tiles of both passes with the dlog table (one launch),
+        # query-major, key-major, dense-route kernel, tau reduction (the index is the readout's)
+        launches[0] += 1 + 1 + 4 + 5
         return out, norm, grads
 
     def _event():

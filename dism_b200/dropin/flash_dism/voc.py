@@ -8,12 +8,12 @@ their gradient in the reference, is not part of this library; a soft flag raises
 import torch
 import cu_flash_dism as cu
 
-from .hard_forward import forward_hard, hard_log_weights
+from .hard_forward import hard_readout, hard_log_weights
 from .hard_backward import backward_hard
 
 
 class _HardVocabulary(torch.autograd.Function):
-    """labels -> forward_hard in the forward; backward_hard in the backward.  On hard sequences the
+    """labels -> log-weight table -> hard_readout in the forward; backward_hard in the backward.  On hard sequences the
     reference gives sq, sk, v and tau their gradient and q, k and both codebooks exactly zero
     (dism_v3/python/flash_dism/hard_backward.py:9-15, dism_v3/tests/test_hard_training.py:69-71)."""
 
@@ -23,18 +23,19 @@ class _HardVocabulary(torch.autograd.Function):
         if codes_q.dim() == 2:  # one codebook shared by the heads
             codes_q, codes_k = (c.expand(q.size(2), *c.shape).contiguous() for c in (codes_q, codes_k))
         idx_q, idx_k = cu.labels_pair(q.detach().contiguous(), codes_q, k.detach().contiguous(), codes_k)
-        tau32 = tau.detach().float().contiguous()
-        out, norm = forward_hard(sq.detach().contiguous(), sk.detach().contiguous(), v.detach().contiguous(), idx_q, idx_k, hard,
-                                 tau32, layout=layout, ctas=ctas)
-        ctx.save_for_backward(q, k, sq, sk, v, q_vocab, k_vocab, tau, idx_q, idx_k, hard, norm)
+        # the log-weight table is built once and kept for the backward, as forward_hard(save_state=True) keeps it
+        longest = sq.size(1) if layout is None else (layout.max_length or max(layout.lengths))
+        table = hard_log_weights(tau.detach().float().contiguous(), longest)
+        out, norm = hard_readout(sq.detach().contiguous(), sk.detach().contiguous(), v.detach().contiguous(), idx_q, idx_k, hard,
+                                 None, table, layout=layout, ctas=ctas)
+        ctx.save_for_backward(q, k, sq, sk, v, q_vocab, k_vocab, tau, idx_q, idx_k, hard, norm, table)
         ctx.layout, ctx.ctas = layout, ctas
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, sq, sk, v, q_vocab, k_vocab, tau, idx_q, idx_k, hard, norm = ctx.saved_tensors
-        n = sq.size(1) if ctx.layout is None else (ctx.layout.max_length or max(ctx.layout.lengths))
-        state = dict(boundary=None, log_weights=hard_log_weights(tau.detach().float().contiguous(), n))
+        q, k, sq, sk, v, q_vocab, k_vocab, tau, idx_q, idx_k, hard, norm, table = ctx.saved_tensors
+        state = dict(boundary=None, log_weights=table)
         dsq, dsk, dv, dtau = backward_hard(sq.detach().contiguous(), sk.detach().contiguous(), v.detach().contiguous(),
                                            dout.contiguous(), idx_q, idx_k, hard, norm, state, layout=ctx.layout, ctas=ctx.ctas)
         zero = lambda t, needed: torch.zeros_like(t) if needed else None
