@@ -125,7 +125,7 @@ static cudaError_t launch_backward_variant(const BackwardBlockArgs& args, int ct
     if (per_head < 1) per_head = 1;
     if (ctas) per_head = ctas / batch_heads > 0 ? ctas / batch_heads : 1;
     KernelTimer timer(QUERY_MAJOR ? "hard_backward_query" : "hard_backward_key", stream);
-    kernel<<<dim3(per_head, batch_heads), BLOCK_WARPS * 32, shared, stream>>>(args);
+    kernel<<<dim3(batch_heads, per_head), BLOCK_WARPS * 32, shared, stream>>>(args);
     return cudaGetLastError();
 }
 

@@ -81,7 +81,7 @@ static cudaError_t launch_blocks_layout(const BlockArgs& args, int ctas, cudaStr
     if (per_head < 1) per_head = 1;
     if (ctas) per_head = ctas / batch_heads > 0 ? ctas / batch_heads : 1;
     KernelTimer timer("hard_forward", stream);
-    kernel<<<dim3(per_head, batch_heads), BLOCK_WARPS * 32, shared, stream>>>(args);
+    kernel<<<dim3(batch_heads, per_head), BLOCK_WARPS * 32, shared, stream>>>(args);
     return cudaGetLastError();
 }
 

@@ -169,7 +169,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
     extern __shared__ __align__(16) unsigned char storage[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     auto& mine = reinterpret_cast<BlockWarpShared<R, DV>*>(storage)[warp];
-    const int bh = blockIdx.y, b = bh / a.heads, h = bh % a.heads;
+    const int bh = blockIdx.x, b = bh / a.heads, h = bh % a.heads;  // x: CTAs are handed out slice after slice, so every slice always has CTAs at work
     const int64_t vec0 = int64_t(b) * a.n * a.heads + h;
     const int* iq = a.iq + int64_t(bh) * a.n;
     const int* ik = a.ik + int64_t(bh) * a.n;
