@@ -78,7 +78,7 @@ struct BlockArgs {
 // Number of 16-query tiles a (batch, head) can have at most: every bucket may end with a partial tile.
 __host__ __device__ inline int tile_capacity_for(int n) { return n / QT + BUCKETS; }
 
-// tile_starts[b] = number of 16-query tiles in the buckets before b, and one descriptor per tile.
+// One descriptor per 16-query tile; tile_starts[b] = the first tile of bucket b, tile_starts[BUCKETS] = the number of tiles.
 // With `route` set, a (batch, head) whose buckets hold at least dense_pairs label-matching pairs (causal or not) is
 // marked for the dense kernel instead (route word 1) and gets no tiles here.
 __device__ __forceinline__ void plan_query_tiles(const int* __restrict__ query_starts, const int* __restrict__ key_starts,
@@ -86,32 +86,36 @@ __device__ __forceinline__ void plan_query_tiles(const int* __restrict__ query_s
                                                  int* __restrict__ next_tile, int tile_capacity, int* __restrict__ route = nullptr,
                                                  unsigned long long dense_pairs = 0) {
     constexpr int PER = BUCKETS / 1024;
-    __shared__ int warp_total[32];
+    constexpr int LONG_TILE = 4 * KT;  // a tile with more partners than this counts as long
+    __shared__ unsigned long long warp_total[32];  // tiles before a warp: long ones in the high word, the others in the low word
     __shared__ unsigned long long warp_pairs[32];
-    __shared__ int dense;
+    __shared__ int dense, long_tiles;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     query_starts += int64_t(blockIdx.x) * (BUCKETS + 1);
     key_starts += int64_t(blockIdx.x) * (BUCKETS + 1);
     tile_starts += int64_t(blockIdx.x) * (BUCKETS + 1);
     tiles += int64_t(blockIdx.x) * tile_capacity;
-    int local[PER], sum = 0;
+    // Tiles are handed out in the order of their descriptors.  The tiles of buckets with many partners take many times
+    // longer than the others, so they come first: a long tile taken last would keep its slice, and the kernel, waiting.
+    unsigned long long local[PER], sum = 0;
     unsigned long long pairs = 0;
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
         local[e] = sum;
         const int queries = query_starts[tid * PER + e + 1] - query_starts[tid * PER + e];
-        sum += (queries + QT - 1) / QT;
-        pairs += (unsigned long long)(queries) * (unsigned long long)(key_starts[tid * PER + e + 1] - key_starts[tid * PER + e]);
+        const int partners = key_starts[tid * PER + e + 1] - key_starts[tid * PER + e];
+        sum += (unsigned long long)((queries + QT - 1) / QT) << (partners > LONG_TILE ? 32 : 0);
+        pairs += (unsigned long long)(queries) * (unsigned long long)(partners);
     }
     if (route) {
 #pragma unroll
         for (int s = 16; s; s >>= 1) pairs += __shfl_xor_sync(FULL, pairs, s);
         if (lane == 0) warp_pairs[warp] = pairs;
     }
-    int prefix = sum;
+    unsigned long long prefix = sum;
 #pragma unroll
     for (int s = 1; s < 32; s <<= 1) {
-        const int other = __shfl_up_sync(FULL, prefix, s);
+        const unsigned long long other = __shfl_up_sync(FULL, prefix, s);
         if (lane >= s) prefix += other;
     }
     if (lane == 31) warp_total[warp] = prefix;
@@ -123,27 +127,31 @@ __device__ __forceinline__ void plan_query_tiles(const int* __restrict__ query_s
         route[blockIdx.x] = dense;
     }
     if (warp == 0) {
-        const int mine = warp_total[lane];
-        int scan = mine;
+        const unsigned long long mine = warp_total[lane];
+        unsigned long long scan = mine;
 #pragma unroll
         for (int s = 1; s < 32; s <<= 1) {
-            const int other = __shfl_up_sync(FULL, scan, s);
+            const unsigned long long other = __shfl_up_sync(FULL, scan, s);
             if (lane >= s) scan += other;
         }
         warp_total[lane] = scan - mine;
+        if (lane == 31) long_tiles = int(scan >> 32);
     }
     __syncthreads();
-    const int before = warp_total[warp] + prefix - sum;
+    const unsigned long long before = warp_total[warp] + prefix - sum;
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
-        const int bucket = tid * PER + e, first = before + local[e];
-        tile_starts[bucket] = first;
+        const int bucket = tid * PER + e;
         const int q0 = query_starts[bucket], q1 = query_starts[bucket + 1];
         const int k0 = key_starts[bucket], k1 = key_starts[bucket + 1];
+        const unsigned long long at = before + local[e];
+        const int first = k1 - k0 > LONG_TILE ? int(at >> 32) : long_tiles + int(at & 0xffffffffu);
+        tile_starts[bucket] = first;
         for (int q = q0, tile = first; q < q1; q += QT, ++tile) tiles[tile] = make_int4(q, min(QT, q1 - q), k0, k1);
     }
     if (tid == 1023) {
-        tile_starts[BUCKETS] = route && dense ? 0 : before + sum;  // `dense` was written before the last barrier
+        const unsigned long long all = before + sum;
+        tile_starts[BUCKETS] = route && dense ? 0 : int(all >> 32) + int(all & 0xffffffffu);  // `dense` was written before the last barrier
         next_tile[blockIdx.x] = 0;
     }
 }
