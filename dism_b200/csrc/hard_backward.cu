@@ -7,8 +7,10 @@
 // and adds dSQ and four per-query moments across CTAs with FP32 atomics, this design walks the
 // matched pairs twice, once owned by queries and once owned by keys: every gradient row is then
 // accumulated by exactly one warp, tile by tile in ascending partner order, with no atomics, no
-// zero-filled accumulators and bit-identical results for any grid size.  Pair coefficients stay
-// in FP32 (the reference rounds them to BF16 to feed its tensor-core tiles).
+// zero-filled accumulators and bit-identical results for any grid size.  Pair coefficients enter
+// the second tensor-core product as a bf16 value plus its rounding remainder, i.e. with FP32-like
+// accuracy (the reference rounds them to BF16 once).  Slices with dense labels take the
+// consecutive-position sweeps of hard_backward_dense.cuh instead.
 #include "hard_backward_dense.cuh"
 
 namespace dism {
@@ -54,28 +56,35 @@ cudaError_t launch_dlog_weights(const float* lut, int heads, int lut_stride, flo
 }
 
 // dtau[h] = sum over batch and rows of the per-row terms, in a fixed order (thread-strided partial
-// sums, then a tree), so the result is the same for every launch.
+// sums with all of a thread's loads in flight together, then a shuffle tree per warp and one over the
+// warps), so the result is the same for every launch.
 __global__ __launch_bounds__(1024) void tau_reduce_kernel(const float* __restrict__ rows, float* __restrict__ dtau,
                                                           int batch, int heads, int n) {
-    const int head = blockIdx.x;
-    float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int b = 0; b < batch; ++b) {
-        const float4* source = reinterpret_cast<const float4*>(rows + (int64_t(b) * heads + head) * n);
-#pragma unroll 2
-        for (int e = threadIdx.x; e < n / 4; e += blockDim.x) {
-            const float4 x = __ldg(source + e);
-            sum[0] += x.x; sum[1] += x.y; sum[2] += x.z; sum[3] += x.w;
+    const int head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per_row = n / 4, total = batch * per_row;  // float4 pieces of this head: [batch][n / 4]
+    float sum = 0.f;
+    for (int first = threadIdx.x; first < total; first += 8 * blockDim.x) {
+        float4 piece[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int e = first + u * blockDim.x;
+            piece[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (e < total) piece[u] = __ldg(reinterpret_cast<const float4*>(rows + (int64_t(e / per_row) * heads + head) * n) + e % per_row);
         }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) sum += (piece[u].x + piece[u].y) + (piece[u].z + piece[u].w);
     }
-    __shared__ float partial[1024];
-    partial[threadIdx.x] = (sum[0] + sum[1]) + (sum[2] + sum[3]);
+#pragma unroll
+    for (int s = 16; s; s >>= 1) sum += __shfl_xor_sync(FULL, sum, s);
+    __shared__ float partial[32];
+    if (lane == 0) partial[warp] = sum;
     __syncthreads();
-    for (int s = 512; s; s >>= 1) {
-        if (threadIdx.x < s) partial[threadIdx.x] += partial[threadIdx.x + s];
-        __syncthreads();
+    if (warp == 0) {
+        float all = lane < blockDim.x / 32 ? partial[lane] : 0.f;
+#pragma unroll
+        for (int s = 16; s; s >>= 1) all += __shfl_xor_sync(FULL, all, s);
+        if (lane == 0) dtau[head] = all;
     }
-    if (threadIdx.x == 0) dtau[head] = partial[0];
 }
 
 // Workspace: both position indices, a tile plan (descriptors, first-tile table, counter) for each of

@@ -8,7 +8,8 @@
 // accumulates them in ascending key order with the online max / unit-fallback normalisation of
 // the reference (maximum starts at 0, denominator at 1).  A row is reduced by one warp in a fixed
 // order, so outputs do not depend on the grid size.  This file holds the table kernel, the
-// workspace layout and the launch; the tile kernel is in hard_forward_blocks.cuh.
+// workspace layout and the launches; the tile kernel is in hard_forward_blocks.cuh, the kernel
+// that takes the slices with dense labels in hard_forward_dense.cuh.
 #include "hard_forward_dense.cuh"
 
 namespace dism {
