@@ -11,6 +11,8 @@
 // the only serial part: sixteen slots per thread and one exchange of part totals per round.  Items
 // are first put in order in shared memory and leave from there, so that consecutive threads write
 // consecutive entries: a scattered 8-byte store costs the SM a cycle per lane.
+#include <cooperative_groups.h>
+
 #include "dism_common.cuh"
 
 namespace dism {
@@ -41,13 +43,14 @@ struct IndexShared {
     int warp_sum[32];
 };
 
-// One stable counting pass over n items of this (batch, head).  FIRST reads labels in position
+// One stable counting pass over the items low .. high-1 of this (batch, head), which go to the places shared.base
+// holds for their bins.  FIRST reads labels in position
 // order and sorts by the low six bucket bits; the second pass reads the first pass's entries and
 // sorts by the high six bits.
 template <bool FIRST, int THREADS>
 __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, const int2* __restrict__ source,
                                               const int* __restrict__ source_previous, int2* __restrict__ target,
-                                              int* __restrict__ target_previous, int n, IndexShared<THREADS>& shared) {
+                                              int* __restrict__ target_previous, int low, int high, IndexShared<THREADS>& shared) {
     using Shared = IndexShared<THREADS>;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int* base = shared.base[FIRST ? 0 : 1];
@@ -56,7 +59,7 @@ __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, co
         const int bucket = bucket_of(label);
         return FIRST ? bucket & (PASS_BINS - 1) : bucket >> 6;
     };
-    for (int round = 0; round < n; round += Shared::ITEMS) {
+    for (int round = low; round < high; round += Shared::ITEMS) {
         int2 item[PER_THREAD];
         int before_item[PER_THREAD];
 #pragma unroll
@@ -64,18 +67,19 @@ __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, co
             const int at = round + c * THREADS + tid;
             item[c] = make_int2(0, 0);
             before_item[c] = 0;
-            if (at < n) {
-                item[c] = FIRST ? make_int2(at, __ldg(labels + at)) : source[at];
-                before_item[c] = FIRST ? (at > 0 ? __ldg(labels + at - 1) : 0) : source_previous[at];
+            if (at < high) {  // the first pass's output was written in this launch, maybe by another CTA: read it past L1
+                item[c] = FIRST ? make_int2(at, __ldg(labels + at)) : __ldcg(source + at);
+                before_item[c] = FIRST ? (at > 0 ? __ldg(labels + at - 1) : 0) : __ldcg(source_previous + at);
             }
         }
         unsigned places[PER_THREAD / 2] = {};  // per item sixteen bits: its bin, and above it its rank among the slot's items of that bin
 #pragma unroll
         for (int c = 0; c < PER_THREAD; ++c) {
             const int at = round + c * THREADS + tid, slot = c * (THREADS / 32) + warp;
-            const bool valid = at < n;
+            const bool valid = at < high;
             const int bin = valid ? bin_of(item[c].y) : PASS_BINS;  // invalid lanes pair up only with each other
             reinterpret_cast<unsigned*>(shared.counts[slot])[lane] = 0u;  // the slot's 64 counters, two per lane
+            if (round + c * THREADS >= high) continue;  // a slot past the end of the items (the same test in every thread)
             __syncwarp();
             unsigned peers = FULL;  // the lanes with this lane's bin: one vote per bit (cheaper than a warp match)
 #pragma unroll
@@ -127,7 +131,7 @@ __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, co
 #pragma unroll
         for (int c = 0; c < PER_THREAD; ++c) {
             const int at = round + c * THREADS + tid, slot = c * (THREADS / 32) + warp;
-            if (at >= n) continue;
+            if (at >= high) continue;
             const unsigned place = places[c >> 1] >> (16 * (c & 1));
             const int bin = place & 255;
             const int to = shared.local_base[bin] + shared.counts[slot][bin] + ((place >> 8) & 255);
@@ -138,7 +142,7 @@ __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, co
 #pragma unroll
         for (int c = 0; c < PER_THREAD; ++c) {
             const int i = c * THREADS + tid;
-            if (round + i >= n) continue;
+            if (round + i >= high) continue;
             const int2 entry = shared.staged[i];
             const int bin = bin_of(entry.y);
             const int to = base[bin] + i - shared.local_base[bin];
@@ -224,8 +228,125 @@ __global__ __launch_bounds__(THREADS, THREADS == 512 ? 2 : 1) void build_index_k
     __syncthreads();
     if (warp < 4 && (warp & 1)) shared.base[warp >> 1][32 + lane] += shared.part_total[0][warp - 1];
     __syncthreads();
-    counting_pass<true, THREADS>(labels, nullptr, nullptr, scratch, scratch_previous, n, shared);
-    counting_pass<false, THREADS>(labels, scratch, scratch_previous, entries, previous, n, shared);
+    counting_pass<true, THREADS>(labels, nullptr, nullptr, scratch, scratch_previous, 0, n, shared);
+    counting_pass<false, THREADS>(labels, scratch, scratch_previous, entries, previous, 0, n, shared);
+}
+
+// The same sort by a cluster of CTAs, for launches with few (batch, head, side) slices: CTA r of the cluster takes the
+// r-th part of the items in each pass.  What a CTA must know of the others goes through distributed shared memory:
+// the sizes of its peers' bins (its items follow those of the CTAs before it, bin by bin) and, for the bucket starts,
+// the peers' bucket histograms.  The second pass reads what the whole cluster wrote in the first, so the parts' bin
+// sizes of the second pass are counted in between.  All waiting is the hardware's cluster barrier.
+constexpr int CLUSTER_THREADS = 1024;
+struct IndexClusterShared {
+    IndexShared<CLUSTER_THREADS> sort;
+    int histogram[BUCKETS];      // this CTA's part of the bucket histogram (kept while the peers read it)
+    int bins[3][PASS_BINS];      // this CTA's bin sizes: first pass, second pass by original part, second pass by its part of the first pass's output
+};
+
+__global__ __launch_bounds__(CLUSTER_THREADS, 1) void build_index_cluster_kernel(const IndexSide side0, const IndexSide side1, int n) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int parts = cluster.num_blocks(), part = cluster.block_rank(), slice = blockIdx.x / parts;
+    const IndexSide& side = blockIdx.y ? side1 : side0;
+    const int* __restrict__ labels = side.labels + int64_t(slice) * n;
+    int2* entries = side.entries + int64_t(slice) * n;
+    int2* scratch = side.scratch + int64_t(slice) * n;
+    int* previous = side.previous + int64_t(slice) * n;
+    int* scratch_previous = side.scratch_previous + int64_t(slice) * n;
+    int* starts = side.starts + int64_t(slice) * (BUCKETS + 1);
+    extern __shared__ __align__(16) unsigned char index_storage[];
+    IndexClusterShared& shared = *reinterpret_cast<IndexClusterShared*>(index_storage);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int share = ((n + parts - 1) / parts + 31) & ~31, low = min(n, part * share), high = min(n, low + share);
+
+    // this part's bucket histogram and its bin sizes for both passes
+    for (int e = tid; e < BUCKETS; e += CLUSTER_THREADS) shared.histogram[e] = 0;
+    __syncthreads();
+    for (int at = low + tid; at < high; at += CLUSTER_THREADS) atomicAdd(&shared.histogram[bucket_of(__ldg(labels + at))], 1);
+    __syncthreads();
+    if (warp < 4) {
+        const int pass = warp >> 1, bin = (warp & 1) * 32 + lane;
+        int size = 0;
+        for (int e = 0; e < PASS_BINS; ++e) {
+            const int turned = (e + lane) & (PASS_BINS - 1);  // lanes start at different columns: no two in one bank
+            size += shared.histogram[pass ? bin * PASS_BINS + turned : turned * PASS_BINS + bin];
+        }
+        shared.bins[pass][bin] = size;
+    }
+    cluster.sync();
+
+    // bucket starts, by the first CTA: an exclusive scan of the whole cluster's histogram, four buckets per thread
+    if (part == 0) {
+        constexpr int PER = BUCKETS / CLUSTER_THREADS;
+        int local[PER], sum = 0;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            int size = 0;
+            for (int r = 0; r < parts; ++r) size += cluster.map_shared_rank(shared.histogram, r)[tid * PER + e];
+            local[e] = sum;
+            sum += size;
+        }
+        int prefix = sum;
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+            const int other = __shfl_up_sync(FULL, prefix, s);
+            if (lane >= s) prefix += other;
+        }
+        if (lane == 31) shared.sort.warp_sum[warp] = prefix;
+        __syncthreads();
+        if (warp == 0) {
+            const int mine = shared.sort.warp_sum[lane];
+            int scan = mine;
+#pragma unroll
+            for (int s = 1; s < 32; s <<= 1) {
+                const int other = __shfl_up_sync(FULL, scan, s);
+                if (lane >= s) scan += other;
+            }
+            shared.sort.warp_sum[lane] = scan - mine;
+        }
+        __syncthreads();
+        const int before = shared.sort.warp_sum[warp] + prefix - sum;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) starts[tid * PER + e] = before + local[e];
+        if (tid == CLUSTER_THREADS - 1) starts[BUCKETS] = n;
+    }
+    // Where this part's items of a bin go: after the bins before it (sizes over the whole cluster) and after the same
+    // bin's items of the parts before it.  `mine` picks the per-part sizes: 0 for the first pass, 2 for the second.
+    auto place_bins = [&](int pass, int mine) {
+        if (warp < 2) {
+            const int bin = warp * 32 + lane;
+            int all = 0, before = 0;
+            for (int r = 0; r < parts; ++r) {
+                all += cluster.map_shared_rank(&shared.bins[pass][0], r)[bin];
+                if (r < part) before += cluster.map_shared_rank(&shared.bins[mine][0], r)[bin];
+            }
+            int prefix = all;
+#pragma unroll
+            for (int s = 1; s < 32; s <<= 1) {
+                const int other = __shfl_up_sync(FULL, prefix, s);
+                if (lane >= s) prefix += other;
+            }
+            shared.sort.base[pass][bin] = prefix - all + before;
+            if (lane == 31) shared.sort.part_total[0][warp] = prefix;  // the first half's size, for the second half
+        }
+        __syncthreads();
+        if (warp == 1) shared.sort.base[pass][32 + lane] += shared.sort.part_total[0][0];
+        __syncthreads();
+    };
+    place_bins(0, 0);
+    counting_pass<true, CLUSTER_THREADS>(labels, nullptr, nullptr, scratch, scratch_previous, low, high, shared.sort);
+    __threadfence();
+    cluster.sync();  // the first pass's output is complete
+
+    // bin sizes of this part of the first pass's output
+    if (tid < PASS_BINS) shared.bins[2][tid] = 0;
+    __syncthreads();
+    for (int at = low + tid; at < high; at += CLUSTER_THREADS) atomicAdd(&shared.bins[2][bucket_of(__ldcg(scratch + at).y) >> 6], 1);
+    cluster.sync();
+    place_bins(1, 2);
+    counting_pass<false, CLUSTER_THREADS>(labels, scratch, scratch_previous, entries, previous, low, high, shared.sort);
+    cluster.sync();  // no CTA leaves while a peer may still read its shared memory
 }
 
 // Per side: entries int2 [BH, N], sort scratch int2 [BH, N], previous int [BH, N], its sort scratch int [BH, N],
@@ -252,17 +373,39 @@ static IndexSide index_side(const int* labels, void* workspace, int batch_heads,
     return IndexSide{labels, entries, entries + size_t(batch_heads) * n, previous, previous + size_t(batch_heads) * n, const_cast<int*>(index.starts)};
 }
 
-// Few CTAs: the widest CTA, which finishes a slice soonest.  Many: narrower CTAs, several to an SM.
+// Very few slices: a cluster of CTAs per slice.  Few: the widest CTA, which finishes a slice soonest.  Many: narrower
+// CTAs, several to an SM.
 static void run_build_index(const IndexSide& side0, const IndexSide& side1, int batch_heads, int sides, int n, cudaStream_t stream) {
     static const bool ready = [] {  // shared memory beyond 48 KiB has to be asked for once per kernel
         return cudaFuncSetAttribute(build_index_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(IndexShared<1024>))) == cudaSuccess &&
                cudaFuncSetAttribute(build_index_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(IndexShared<512>))) == cudaSuccess;
     }();
     (void)ready;
-    if (batch_heads * sides <= device_sm_count())
+    const int sms = device_sm_count(), slices = batch_heads * sides;
+    int parts = 1;  // CTAs per slice: as many as keep the launch within one CTA per SM, a power of two up to eight
+    while (parts < 8 && slices * parts * 2 <= sms && n / (parts * 2) >= 8192) parts *= 2;  // (at 8192 positions a slice the cluster is no faster than one CTA)
+    if (parts > 1) {
+        static const bool cluster_ready = cudaFuncSetAttribute(build_index_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                               int(sizeof(IndexClusterShared))) == cudaSuccess;
+        (void)cluster_ready;
+        cudaLaunchConfig_t config{};
+        config.gridDim = dim3(batch_heads * parts, sides);
+        config.blockDim = dim3(CLUSTER_THREADS);
+        config.dynamicSmemBytes = sizeof(IndexClusterShared);
+        config.stream = stream;
+        cudaLaunchAttribute attribute{};
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = parts;
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        cudaLaunchKernelEx(&config, build_index_cluster_kernel, side0, side1, n);
+    } else if (slices <= sms) {
         build_index_kernel<1024><<<dim3(batch_heads, sides), 1024, sizeof(IndexShared<1024>), stream>>>(side0, side1, n);
-    else
+    } else {
         build_index_kernel<512><<<dim3(batch_heads, sides), 512, sizeof(IndexShared<512>), stream>>>(side0, side1, n);
+    }
 }
 
 cudaError_t launch_build_index(const int* labels, int batch_heads, int n, void* workspace, int side, int sides,
