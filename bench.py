@@ -35,6 +35,7 @@ KERNEL_BYTES = {
     'hard_forward': 396,         # labels 8, sq+sk 128, v 128 read; out 128, lse2 4 written
     'hard_backward_query': 524,  # sq,sk 128, v,dO 256, labels 8, lse2 4 read; dsq (f32) 128 written
     'hard_backward_key': 588,    # the same reads; dsk 64, dv 128 written
+    'hard_backward': 524 + 588,  # both passes in one launch, which the library does when a GPU holds little work
 }
 STEP_BYTES = 2 * 132 + 396 + 716  # whole path: two label launches, forward, backward (inputs counted once)
 
@@ -175,8 +176,9 @@ def run_ours(args):
         mark()
         # labels of q and k (one launch); log weights; readout: index, tiles, label-block kernel, dense-route kernel (its
         # CTAs return at once on these labels); backward: tiles of both passes with the dlog table (one launch),
-        # query-major, key-major, dense-route kernel, tau reduction (the index is the readout's)
-        launches[0] += 1 + 1 + 4 + 5
+        # query-major and key-major pass (one launch when the GPU holds at most 262144 positions), dense-route kernel, tau
+        # reduction (the index is the readout's)
+        launches[0] += 1 + 1 + 4 + (4 if positions <= 262144 else 5)
         return out, norm, grads
 
     def _event():

@@ -117,31 +117,40 @@ static cudaError_t launch_dense_backward(const DenseBackwardArgs& args, cudaStre
                                        shared, stream);
 }
 
-template <bool QUERY_MAJOR, bool PACKED, int R, int DV>
-static cudaError_t launch_backward_variant(const BackwardBlockArgs& args, int ctas, cudaStream_t stream) {
-    auto kernel = hard_backward_blocks_kernel<QUERY_MAJOR, PACKED, R, DV>;
+template <bool PACKED, int R, int DV>
+static cudaError_t launch_backward_variant(const BackwardBlockArgs& by_query, const BackwardBlockArgs& by_key, int ctas, cudaStream_t stream) {
+    auto kernel = hard_backward_blocks_kernel<PACKED, R, DV>;
     const int shared = sizeof(BackwardWarpShared<R, DV>) * BLOCK_WARPS;
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
     if (status != cudaSuccess) return status;
-    const int batch_heads = args.batch * args.heads;
+    const int batch_heads = by_query.batch * by_query.heads, n = by_query.n;
     // about eight full tiles per warp (partial tiles of small buckets come on top), and with few (batch, head) slices at
-    // least four CTAs per SM over the whole grid: warps take tiles from a counter, so any grid covers the work;
-    // `ctas` caps the whole grid
-    int per_head = args.n / (QT * BLOCK_WARPS * 8);
+    // least four CTAs per SM over each pass: warps take tiles from a counter, so any grid covers the work;
+    // `ctas` caps the grid of a pass
+    int per_head = n / (QT * BLOCK_WARPS * 8);
     const int fill = (4 * device_sm_count() + batch_heads - 1) / batch_heads;
     if (per_head < fill) per_head = fill;
-    if (per_head > (args.n + QT * BLOCK_WARPS - 1) / (QT * BLOCK_WARPS)) per_head = (args.n + QT * BLOCK_WARPS - 1) / (QT * BLOCK_WARPS);
+    if (per_head > (n + QT * BLOCK_WARPS - 1) / (QT * BLOCK_WARPS)) per_head = (n + QT * BLOCK_WARPS - 1) / (QT * BLOCK_WARPS);
     if (per_head < 1) per_head = 1;
     if (ctas) per_head = ctas / batch_heads > 0 ? ctas / batch_heads : 1;
-    KernelTimer timer(QUERY_MAJOR ? "hard_backward_query" : "hard_backward_key", stream);
-    kernel<<<dim3(batch_heads, per_head), BLOCK_WARPS * 32, shared, stream>>>(args);
+    if (int64_t(batch_heads) * n <= 262144) {  // little work on this GPU: both passes in one launch
+        KernelTimer timer("hard_backward", stream);
+        kernel<<<dim3(batch_heads, per_head, 2), BLOCK_WARPS * 32, shared, stream>>>(by_query, by_key, 0);
+        return cudaGetLastError();
+    }
+    {
+        KernelTimer timer("hard_backward_query", stream);
+        kernel<<<dim3(batch_heads, per_head), BLOCK_WARPS * 32, shared, stream>>>(by_query, by_key, 0);
+    }
+    KernelTimer timer("hard_backward_key", stream);
+    kernel<<<dim3(batch_heads, per_head), BLOCK_WARPS * 32, shared, stream>>>(by_query, by_key, 1);
     return cudaGetLastError();
 }
 
-template <bool QUERY_MAJOR, int R, int DV>
-static cudaError_t launch_backward_blocks(const BackwardBlockArgs& args, int ctas, cudaStream_t stream) {
-    return args.documents ? launch_backward_variant<QUERY_MAJOR, true, R, DV>(args, ctas, stream)
-                          : launch_backward_variant<QUERY_MAJOR, false, R, DV>(args, ctas, stream);
+template <int R, int DV>
+static cudaError_t launch_backward_blocks(const BackwardBlockArgs& by_query, const BackwardBlockArgs& by_key, int ctas, cudaStream_t stream) {
+    return by_query.documents ? launch_backward_variant<true, R, DV>(by_query, by_key, ctas, stream)
+                              : launch_backward_variant<false, R, DV>(by_query, by_key, ctas, stream);
 }
 
 cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const __nv_bfloat16* sk,
@@ -207,8 +216,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     status = cudaErrorInvalidValue;
 #define DISM_CASE(RR, VV)                                                                         \
     if (shape.r == RR && shape.dv == VV) {                                                        \
-        status = launch_backward_blocks<true, RR, VV>(by_query, ctas, stream);                    \
-        if (status == cudaSuccess) status = launch_backward_blocks<false, RR, VV>(by_key, ctas, stream); \
+        status = launch_backward_blocks<RR, VV>(by_query, by_key, ctas, stream);                  \
         if (status == cudaSuccess && dense_allowed) status = launch_dense_backward<RR, VV>(dense, stream); \
     }
     DISM_CASE(16, 32) DISM_CASE(16, 64) DISM_CASE(16, 128)

@@ -62,7 +62,7 @@ __device__ __forceinline__ void split_bf16(float x, float y, unsigned& high, uns
 // PACKED: rows carry document limits (a.documents is set); otherwise every row's document is the whole sequence
 // and the limits are constants the compiler folds away.
 template <bool QUERY_MAJOR, bool PACKED, int R, int DV>
-__global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kernel(const BackwardBlockArgs a) {
+__device__ __forceinline__ void hard_backward_blocks_pass(const BackwardBlockArgs& a) {
     constexpr int KSTEPS = R / 16, VSTEPS = DV / 16, RTILES = R / 8, VTILES = DV / 8;
     extern __shared__ __align__(16) unsigned char storage[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -485,6 +485,17 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kern
             }
         }
     }
+}
+
+// blockIdx.z + first_pass picks the pass (0 query-major, 1 key-major), so one launch can run either pass or both.  The
+// passes do not depend on each other, and CTAs are handed out z last: in a launch of both, the key-major CTAs move into
+// the SMs that the query-major pass frees as it runs out of tiles, and the launch has one ramp and one tail instead of
+// two of each.  That pays when a GPU holds little work; with much work the passes are faster one after the other.
+template <bool PACKED, int R, int DV>
+__global__ __launch_bounds__(BLOCK_WARPS * 32, 2) void hard_backward_blocks_kernel(const BackwardBlockArgs by_query,
+                                                                                  const BackwardBlockArgs by_key, int first_pass) {
+    if (blockIdx.z + first_pass == 0) hard_backward_blocks_pass<true, PACKED, R, DV>(by_query);
+    else hard_backward_blocks_pass<false, PACKED, R, DV>(by_key);
 }
 
 }  // namespace dism
