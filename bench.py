@@ -77,6 +77,29 @@ def kernel_roofline(name, ms, positions, traffic):
             'peak_kind': kind, 'traffic': traffic, 'algorithmic_bytes_per_launch': KERNEL_BYTES[name] * positions}
 
 
+def bind_to_gpu_cpus(index):
+    """Runs this process on the CPUs next to GPU `index` (NVML's CPU affinity of the device), so that the pinned host
+    buffers of the end-to-end leg, which are placed where the allocating thread runs, sit on the GPU's own NUMA node.
+    Returns (the previous CPU set, a note for the JSON line); nothing changes when NVML cannot say."""
+    before = os.sched_getaffinity(0)
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        properties = torch.cuda.get_device_properties(index)
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByUUID('GPU-' + str(properties.uuid))
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        near = {cpu for cpu in before if (words[cpu // 64] >> (cpu % 64)) & 1}
+        if near and near != before:
+            os.sched_setaffinity(0, near)
+            return before, f'{len(near)} of {len(before)} CPUs: those next to the GPU'
+        return before, f'all {len(before)} CPUs (already next to the GPU)'
+    except Exception as error:
+        return before, f'all {len(before)} CPUs (NVML affinity unavailable: {type(error).__name__})'
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -159,6 +182,7 @@ def run_ours(args):
     heads_here = s['heads'] // split
     total_positions = s['batch'] * s['heads'] * s['n']  # the whole job, over all ranks
     positions = s['batch'] * heads_here * s['n']        # this rank's share
+    all_cpus, cpu_note = bind_to_gpu_cpus(local)
     host, params = make_inputs(0, device, rank, split)
     resident = {k: v.to(device) for k, v in host.items()}
     launches = [0]
@@ -291,6 +315,7 @@ def run_ours(args):
         e2e_ms = e2e_start.elapsed_time(e2e_stop)
         d2h = d2h[0]
 
+    os.sched_setaffinity(0, all_cpus)  # the CPU baseline below runs on every host core
     flip_rate = label_flip_rate(cu, resident, params)
     long_context = long_context_record(cu, forward_hard, device, rank, world, args)
     times = torch.tensor([elapsed_ms, e2e_ms, long_context['ms_labels'] + long_context['ms_forward']], device=device, dtype=torch.float64)
@@ -318,7 +343,8 @@ def run_ours(args):
             'config': {'workload': WORKLOAD.format(batch=s['batch']),
                        'parallelism': f'16 heads / {world} = {heads_here} heads per GPU, one problem, no collective',
                        'l2': f'inputs per step and GPU ({sum(v.numel() * v.element_size() for v in host.values()) / 1e6:.0f} MB) '
-                             + ('exceed L2' if heads_here >= 4 else 'are flushed from L2 by a 256 MB write between steps')},
+                             + ('exceed L2' if heads_here >= 4 else 'are flushed from L2 by a 256 MB write between steps'),
+                       'host_cpus': cpu_note},
             'stage_ms': {'labels': float(stage_ms[0]), 'forward': float(stage_ms[1]), 'backward': float(stage_ms[2])},
             'kernel_ms': kernel_ms,
             'per_gpu_value': positions / (ms_per_step * 1e-3),
