@@ -147,6 +147,51 @@ def test_dense_labels_take_the_consecutive_tile_kernels(api, oracle, n, r, dv):
         assert not gradient[1, :, 1].count_nonzero()
 
 
+@pytest.mark.parametrize('seed', range(16))
+def test_mixed_label_kinds_against_oracle(api, oracle, seed):
+    """Every (batch, head) slice of a call draws its own kind of labels: all equal, two symbols, a period of 2 to 8 with
+    a shift between the sides, 12 symbols (around the dense-route threshold), 400 symbols, 5000 symbols with the keys a
+    rolled copy of the queries (buckets shared by several labels, long runs).  Slices of one call so take different
+    routes; forward and backward against the oracle."""
+    rng = np.random.default_rng(5000 + seed)
+    b, h = int(rng.integers(1, 3)), int(rng.integers(1, 4))
+    n = int(rng.choice([256, 512, 768, 1024, 2048]))
+    r, dv = int(rng.choice([16, 32])), int(rng.choice([32, 64, 128]))
+    q, k = np.empty((b, h, n), np.int32), np.empty((b, h, n), np.int32)
+    for slice_q, slice_k in zip(q.reshape(-1, n), k.reshape(-1, n)):
+        kind = rng.choice(['equal', 'two', 'period', 'sparse', 'threshold', 'rolled'])
+        if kind == 'equal':
+            slice_q[:] = slice_k[:] = 7
+        elif kind == 'two':
+            slice_q[:], slice_k[:] = rng.integers(0, 2, n), rng.integers(0, 2, n)
+        elif kind == 'period':
+            period = int(rng.integers(2, 9))
+            slice_q[:], slice_k[:] = np.arange(n) % period, (np.arange(n) + int(rng.integers(0, period))) % period
+        elif kind == 'sparse':
+            slice_q[:], slice_k[:] = rng.integers(0, 400, n), rng.integers(0, 400, n)
+        elif kind == 'threshold':
+            slice_q[:], slice_k[:] = rng.integers(0, 12, n), rng.integers(0, 12, n)
+        else:
+            slice_q[:] = rng.integers(0, 5000, n)
+            slice_k[:] = np.roll(slice_q, int(rng.integers(0, 5)))
+    hard = rng.random((b, h)) < .85
+    hard[0, 0] = True
+    sq, sk, v, dout = vectors(3000 + seed, b, n, h, r, dv)
+    tau = torch.from_numpy(rng.uniform(-.6, .6, h).astype(np.float32))
+    x = [sq.cuda(), sk.cuda(), v.cuda(), dev(q), dev(k), dev(hard)]
+    out, norm = api['fwd'].forward_hard(*x, tau.cuda())
+    state = dict(boundary=None, log_weights=api['fwd'].hard_log_weights(tau.cuda(), n))
+    got = api['bwd'].backward_hard(*x[:3], dout.cuda(), *x[3:], norm, state)
+    f = lambda t: t.float().numpy()
+    expected, lse2 = oracle.forward(f(sq), f(sk), f(v), q, k, hard, tau.numpy(), threads=8)
+    want = oracle.backward(f(sq), f(sk), f(v), f(dout), q, k, hard, tau.numpy(), threads=8)
+    assert_vectors(out, expected)
+    torch.testing.assert_close(norm.double().cpu(), torch.from_numpy(lse2), atol=2e-5, rtol=2e-6)
+    for a, e in zip(got[:3], want[:3]):
+        assert_vectors(a, e)
+    torch.testing.assert_close(got[3].double().cpu(), torch.from_numpy(want[3]), atol=.003, rtol=.01)
+
+
 def test_forward_long_chain_tau_sweep(api):
     g = golden('chain_equal.npz')
     x = [dev(g['sq'], torch.bfloat16), dev(g['sk'], torch.bfloat16), dev(g['v'], torch.bfloat16),
