@@ -630,6 +630,46 @@ def test_packed_documents_match_fixed_length(api, oracle, pattern):
     assert torch.equal(changed[:, 256:], out[:, 256:]) and torch.equal(changed_norm, norm)
 
 
+@pytest.mark.parametrize('seed', range(8))
+def test_packed_random_documents_match_stand_alone_runs(api, seed):
+    """Random 256-aligned document splits of a pack, each head with its own kind of labels (equal, two symbols, a period,
+    many symbols): forward and backward of the pack against every document run by itself."""
+    from flash_dism.varlen import VarlenLayout
+    rng = np.random.default_rng(7000 + seed)
+    n, h, r, dv = 2048, 3, 32, 64
+    q, k = np.empty((1, h, n), np.int32), np.empty((1, h, n), np.int32)
+    for head in range(h):
+        kind = rng.choice(['equal', 'two', 'period', 'sparse'])
+        if kind == 'equal':
+            q[0, head] = k[0, head] = 3
+        elif kind == 'two':
+            q[0, head], k[0, head] = rng.integers(0, 2, n), rng.integers(0, 2, n)
+        elif kind == 'period':
+            q[0, head], k[0, head] = np.arange(n) % 5, (np.arange(n) + 2) % 5
+        else:
+            q[0, head], k[0, head] = rng.integers(0, 300, n), rng.integers(0, 300, n)
+    # documents end at the training rows' borders (1024) and at random multiples of 256 inside them
+    cuts = sorted({0, 1024, 2048} | {int(c) * 256 for c in rng.integers(1, 8, 3)})
+    layout = VarlenLayout.from_cu_seqlens(torch.tensor(cuts, dtype=torch.int32), n)
+    sq, sk, v, dout = vectors(90 + seed, 1, n, h, r, dv)
+    hard = torch.from_numpy(rng.random((2, h)) < .8).cuda()
+    tau = torch.from_numpy(rng.uniform(-.5, .5, h).astype(np.float32)).cuda()
+    x = [sq.cuda(), sk.cuda(), v.cuda(), dev(q), dev(k), hard, tau]
+    out, norm = api['fwd'].forward_hard(*x, layout=layout)
+    grads = api['bwd'].backward_hard_recompute(*x[:3], dout.cuda(), *x[3:], layout=layout)
+    dtau = torch.zeros(h, device='cuda')
+    for start, end in zip(cuts, cuts[1:]):
+        local, local_dout = document(x, dout.cuda(), start, end)
+        want, want_norm = api['fwd'].forward_hard(*local)
+        torch.testing.assert_close(out[:, start:end].float(), want.float(), atol=.008, rtol=.025)
+        torch.testing.assert_close(norm[:, :, start:end], want_norm, atol=2e-5, rtol=2e-6)
+        local_grads = api['bwd'].backward_hard_recompute(*local[:3], local_dout, *local[3:])
+        for name in ('sq_vec', 'sk_vec', 'v'):
+            torch.testing.assert_close(grads[name][:, start:end].float(), local_grads[name].float(), atol=.008, rtol=.025)
+        dtau += local_grads['rtau']
+    torch.testing.assert_close(grads['rtau'], dtau, atol=3e-3, rtol=1e-3)
+
+
 def test_packed_saved_state_gives_the_same_bits(api):
     """forward_hard(save_state=True) with a layout returns the packed rectangle (what the reference's forward always
     builds); readout and backward accept it and give the bits of the label-only route."""
