@@ -45,3 +45,16 @@ def test_gradient_sum_two_ranks():
     results = manager.dict()
     mp.spawn(_rank, args=(2, port, results), nprocs=2, join=True)
     assert results[0] and results[1]
+
+
+def test_model_of_the_benchmark_has_the_stated_size():
+    """The model workload's architecture (depth 20, width 1280, 10 heads of 128, vocabulary 65536), built on the meta
+    device: parameter count as `bench.py --workload model` reports it, and the DISM layer's own parameters."""
+    import torch
+    from dism_b200.model import DismLM
+    with torch.device('meta'):
+        model = DismLM(depth=20, width=1280, heads=10, head_dim=128, vocab=65536)
+    assert sum(p.numel() for p in model.parameters()) == 603586760
+    mixer = model.blocks[0].mixer
+    assert mixer.q_vocab.shape == (10, 512, 128) and mixer.k_vocab.shape == (10, 512, 128)
+    assert mixer.sq_proj.weight.shape == (10 * 32, 1280) and mixer.log_sel_tau.shape == (10,)
