@@ -3,8 +3,8 @@
 The reference's Python wrappers (dism_v3/python/flash_dism/{summary,hard_forward,hard_backward,varlen}.py and its
 FP64 oracle reference/dism_v3_ref.py) are linked by path into a scratch package next to this library's
 `cu_flash_dism`, and pytest runs dism_v3/tests/test_hard_{summary,chunk,forward,backward}.py in a child process.
-Left out: the `codegen` cases (they disassemble the reference's object files), the sanitizer smoke test and the
-CUDA-graph replay cases (the graph route word is not built).  Every other case has to pass.  Needs a reference checkout
+Left out: the `codegen` cases (they disassemble the reference's object files) and the sanitizer smoke test.  Every
+other case has to pass, the CUDA-graph capture and replay cases included.  Needs a reference checkout
 (REFERENCE_ROOT, default /root/reference); without one the test is skipped.
 """
 import os
@@ -20,7 +20,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REFERENCE_ROOT = os.environ.get('REFERENCE_ROOT', '/root/reference')
 MODULES = ('summary.py', 'hard_forward.py', 'hard_backward.py', 'varlen.py', os.path.join('reference', 'dism_v3_ref.py'))
 TESTS = ('test_hard_summary.py', 'test_hard_chunk.py', 'test_hard_forward.py', 'test_hard_backward.py')
-LEFT_OUT = 'not codegen and not sanitizer and not graph'
+LEFT_OUT = 'not codegen and not sanitizer'
 
 
 def test_reference_hard_tests_pass_against_the_dropin(tmp_path):
