@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the reference's own Python.
 
-Run once in a container that has the reference checkout (REFERENCE_ROOT, default
-/root/reference); the resulting .npz files are committed and are what the test-suite reads, so
+Run once in a container that has the reference checkout (the REFERENCE_ROOT environment variable, or
+the default below); the resulting .npz files are committed and are what the test-suite reads, so
 nothing at test time needs the checkout.  What is executed here is reference code only:
   * flash_dism/reference/dism_v3_ref.py  dism_ref / dism_ref_backward in float64 (forward output,
     dSQ/dSK/dV/dtau);

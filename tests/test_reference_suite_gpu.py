@@ -5,7 +5,7 @@ FP64 oracle reference/dism_v3_ref.py) are linked by path into a scratch package 
 `cu_flash_dism`, and pytest runs dism_v3/tests/test_hard_{summary,chunk,forward,backward}.py in a child process.
 Left out: the `codegen` cases (they disassemble the reference's object files) and the sanitizer smoke test.  Every
 other case has to pass, the CUDA-graph capture and replay cases included.  Needs a reference checkout
-(REFERENCE_ROOT, default /root/reference); without one the test is skipped.
+(the REFERENCE_ROOT environment variable, or the default below); without one the test is skipped.
 """
 import os
 import re
