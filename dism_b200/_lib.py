@@ -11,6 +11,7 @@ _P, _I, _Z = _c.c_void_p, _c.c_int, _c.c_size_t
 SIGNATURES = {
     'dism_last_error': (_c.c_char_p, []),
     'dism_abi_version': (_I, []),
+    'dism_route_word': (_I, [_P]),
     'dism_hard_dlog_weights': (_I, [_P, _I, _I, _P, _P]),
     'dism_labels': (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _P]),
     'dism_labels_pair': (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),

@@ -50,7 +50,13 @@ int record_count = 0, events_made = 0;
 Record records[MAX_RECORDS];
 }  // namespace
 
+namespace {
+thread_local const unsigned* current_route = nullptr;
+}  // namespace
+
 namespace dism {
+const unsigned* route_word() { return current_route; }
+
 KernelTimer::KernelTimer(const char* name, cudaStream_t s) : slot(-1), stream(s) {
     if (!timing_on || record_count >= MAX_RECORDS) return;
     slot = record_count++;
@@ -87,7 +93,13 @@ int dism_profile_read(int index, char* name, int capacity, float* milliseconds) 
 }
 
 const char* dism_last_error(void) { return last_error; }
-int dism_abi_version(void) { return 7; }
+int dism_abi_version(void) { return 8; }
+
+int dism_route_word(const uint32_t* choice) {
+    if (choice && !aligned(choice, 4)) return fail(DISM_EINVAL, "graph choice must be one aligned device int32");
+    current_route = choice;
+    return DISM_OK;
+}
 
 int dism_labels(const void* x, const void* codebook, int batch, int n, int heads, int d, int vocab,
                 int32_t* labels, void* stream) {

@@ -114,6 +114,19 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
+// ---- route word of a captured graph (dism_v3/include/common/graph_route.cuh:8-13) --------------
+// A graph that holds both the quadratic hard path and another route reads one device word per
+// replay: 0 runs this path, anything else makes every kernel of it return before it reads or
+// writes anything.  A null pointer (eager calls) always runs.
+__device__ __forceinline__ bool route_open(const unsigned* choice) {
+    if (!choice) return true;
+    unsigned value;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(choice) : "memory");
+    return value == 0;
+}
+// The word the calling thread's launches pass to their kernels (set through dism_route_word).
+const unsigned* route_word();
+
 struct KernelTimer {
     KernelTimer(const char* name, cudaStream_t stream);
     ~KernelTimer();

@@ -28,7 +28,8 @@ __device__ __forceinline__ float dlog_weight(float table_one, int l) {
     }
     return g;
 }
-__global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __restrict__ out, int stride) {
+__global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __restrict__ out, int stride, const unsigned* choice) {
+    if (!route_open(choice)) return;
     int l = blockIdx.x * blockDim.x + threadIdx.x, head = blockIdx.y;
     if (l >= stride) return;
     out[int64_t(head) * stride + l] = dlog_weight(lut[int64_t(head) * stride + 1], l);
@@ -39,7 +40,18 @@ __global__ void dlog_weights_kernel(const float* __restrict__ lut, float* __rest
 static __global__ __launch_bounds__(1024) void prepare_backward_kernel(const TilePlan first, const TilePlan second, int tile_capacity,
                                                                        int* route, unsigned long long dense_pairs,
                                                                        const float* __restrict__ lut, float* __restrict__ dlut,
-                                                                       int heads, int lut_stride) {
+                                                                       int heads, int lut_stride, const unsigned* choice) {
+    if (!route_open(choice)) {
+        // The backward tile kernels take no route word (they sit at their register limit): a closed route leaves them no tiles
+        // and marks no slice dense, so they read their tile count and return.
+        if (blockIdx.y < 2 && threadIdx.x == 0) {
+            const TilePlan& plan = blockIdx.y ? second : first;
+            plan.tile_starts[int64_t(blockIdx.x) * (BUCKETS + 1) + BUCKETS] = 0;
+            plan.next_tile[blockIdx.x] = 0;
+            route[blockIdx.x] = 0;
+        }
+        return;
+    }
     if (blockIdx.y == 2) {
         for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < heads * lut_stride; e += gridDim.x * blockDim.x)
             dlut[e] = dlog_weight(lut[int64_t(e / lut_stride) * lut_stride + 1], e % lut_stride);
@@ -51,7 +63,7 @@ static __global__ __launch_bounds__(1024) void prepare_backward_kernel(const Til
 
 cudaError_t launch_dlog_weights(const float* lut, int heads, int lut_stride, float* out, cudaStream_t stream) {
     KernelTimer timer("dlog_weights", stream);
-    dlog_weights_kernel<<<dim3((lut_stride + 255) / 256, heads), 256, 0, stream>>>(lut, out, lut_stride);
+    dlog_weights_kernel<<<dim3((lut_stride + 255) / 256, heads), 256, 0, stream>>>(lut, out, lut_stride, route_word());
     return cudaGetLastError();
 }
 
@@ -59,7 +71,8 @@ cudaError_t launch_dlog_weights(const float* lut, int heads, int lut_stride, flo
 // sums with all of a thread's loads in flight together, then a shuffle tree per warp and one over the
 // warps), so the result is the same for every launch.
 __global__ __launch_bounds__(1024) void tau_reduce_kernel(const float* __restrict__ rows, float* __restrict__ dtau,
-                                                          int batch, int heads, int n) {
+                                                          int batch, int heads, int n, const unsigned* choice) {
+    if (!route_open(choice)) return;
     const int head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int per_row = n / 4, total = batch * per_row;  // float4 pieces of this head: [batch][n / 4]
     float sum = 0.f;
@@ -190,7 +203,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
         const TilePlan by_key{keys.starts, queries.starts, tile_starts[1], tiles[1], tile_starts[1] + size_t(batch_heads) * (BUCKETS + 1)};
         prepare_backward_kernel<<<dim3(batch_heads, 3), 1024, 0, stream>>>(by_query, by_key, capacity, route,
                                                                            dense_allowed ? (unsigned long long)(shape.n) * shape.n / DENSE_SHARE : ~0ull,
-                                                                           lut, dlut, shape.heads, lut_stride);
+                                                                           lut, dlut, shape.heads, lut_stride, route_word());
     }
     BackwardBlockArgs args{};
     args.sq = sq; args.sk = sk; args.v = v; args.dout = dout;
@@ -213,6 +226,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
     dense.dsq = dsq; dense.dtau_rows = rows; dense.dsk = dsk; dense.dv = dv;
     dense.batch = shape.batch; dense.heads = shape.heads; dense.n = shape.n; dense.lut_stride = lut_stride;
     dense.chunks = dense_chunks(batch_heads, shape.n);
+    dense.choice = route_word();
     status = cudaErrorInvalidValue;
 #define DISM_CASE(RR, VV)                                                                         \
     if (shape.r == RR && shape.dv == VV) {                                                        \
@@ -224,7 +238,7 @@ cudaError_t launch_hard_backward(HardShape shape, const __nv_bfloat16* sq, const
 #undef DISM_CASE
     if (status != cudaSuccess) return status;
     KernelTimer timer("tau_reduce", stream);
-    tau_reduce_kernel<<<shape.heads, 1024, 0, stream>>>(rows, dtau, shape.batch, shape.heads, shape.n);
+    tau_reduce_kernel<<<shape.heads, 1024, 0, stream>>>(rows, dtau, shape.batch, shape.heads, shape.n, route_word());
     return cudaGetLastError();
 }
 

@@ -33,6 +33,7 @@ struct DenseBackwardArgs {
     float *dsq, *dtau_rows;
     __nv_bfloat16 *dsk, *dv;
     int batch, heads, n, lut_stride, chunks;
+    const unsigned* choice;  // route word of a captured graph, or null
 };
 
 // Scratch of the dense backward: for each pass what the forward keeps for its one sweep.
@@ -345,6 +346,7 @@ __device__ __forceinline__ void hard_backward_dense_chunk(const DenseBackwardArg
 template <int R, int DV>
 __global__ __launch_bounds__(DENSE_WARPS * 32, 1) void hard_backward_dense_kernel(const DenseBackwardArgs a) {
     const int batch_heads = a.batch * a.heads;
+    if (!route_open(a.choice)) return;
     if (!dense_any(a.route, batch_heads)) return;
     dense_walk_all(a.iq, a.ik, a.documents, a.route, a.lines, 2, batch_heads, a.chunks, a.n);
     __threadfence();

@@ -14,7 +14,8 @@
 
 namespace dism {
 
-__global__ void log_weights_kernel(const float* __restrict__ tau, float* __restrict__ out, int stride) {
+__global__ void log_weights_kernel(const float* __restrict__ tau, float* __restrict__ out, int stride, const unsigned* choice) {
+    if (!route_open(choice)) return;
     int length = blockIdx.x * blockDim.x + threadIdx.x;
     if (length >= stride) return;
     float t = tau[blockIdx.y], result = LOG_ZERO;
@@ -31,7 +32,7 @@ __global__ void log_weights_kernel(const float* __restrict__ tau, float* __restr
 
 cudaError_t launch_log_weights(const float* tau, int heads, int n, float* lut, cudaStream_t stream) {
     KernelTimer timer("log_weights", stream);
-    log_weights_kernel<<<dim3((n + 256) / 256, heads), 256, 0, stream>>>(tau, lut, n + 1);
+    log_weights_kernel<<<dim3((n + 256) / 256, heads), 256, 0, stream>>>(tau, lut, n + 1, route_word());
     return cudaGetLastError();
 }
 
@@ -114,6 +115,7 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
     args.next_tile = tile_starts + size_t(batch_heads) * (BUCKETS + 1);
     args.out = out; args.lse2 = lse2;
     args.batch = shape.batch; args.heads = shape.heads; args.n = shape.n; args.lut_stride = lut_stride;
+    args.choice = route_word();
     // The dense route takes sequences whose length its 32-column steps divide (packed or not); a (batch, head) goes
     // there when at least a tenth of all N^2 pairs have equal labels.
     int* route = args.next_tile + batch_heads;
@@ -122,7 +124,8 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
         KernelTimer timer("plan_query_tiles", stream);
         plan_query_tiles_kernel<<<batch_heads, 1024, 0, stream>>>(args.queries.starts, args.keys.starts, tile_starts, tiles,
                                                                   args.next_tile, args.tile_capacity, route,
-                                                                  dense_allowed ? (unsigned long long)(shape.n) * shape.n / DENSE_SHARE : ~0ull);
+                                                                  dense_allowed ? (unsigned long long)(shape.n) * shape.n / DENSE_SHARE : ~0ull,
+                                                                  route_word());
     }
     DenseArgs dense{};
     dense.sq = sq; dense.sk = sk; dense.v = v; dense.iq = iq; dense.ik = ik; dense.hard = hard; dense.documents = documents; dense.hard_rows = hard_rows; dense.lut = lut;
@@ -131,6 +134,7 @@ cudaError_t launch_hard_forward(HardShape shape, const __nv_bfloat16* sq, const 
     dense.out = out; dense.lse2 = lse2;
     dense.batch = shape.batch; dense.heads = shape.heads; dense.n = shape.n; dense.lut_stride = lut_stride;
     dense.chunks = dense_chunks(batch_heads, shape.n);
+    dense.choice = route_word();
     cudaError_t status_blocks = cudaErrorInvalidValue;
 #define DISM_CASE(RR, VV)                                                                   \
     if (shape.r == RR && shape.dv == VV) {                                                  \

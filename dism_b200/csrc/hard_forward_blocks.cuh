@@ -73,6 +73,7 @@ struct BlockArgs {
     __nv_bfloat16* out;
     float* lse2;
     int batch, heads, n, lut_stride, hard_rows;
+    const unsigned* choice;  // route word of a captured graph, or null
 };
 
 // Number of 16-query tiles a (batch, head) can have at most: every bucket may end with a partial tile.
@@ -158,7 +159,9 @@ __device__ __forceinline__ void plan_query_tiles(const int* __restrict__ query_s
 
 static __global__ __launch_bounds__(1024) void plan_query_tiles_kernel(const int* query_starts, const int* key_starts,
                                                                        int* tile_starts, int4* tiles, int* next_tile,
-                                                                       int tile_capacity, int* route, unsigned long long dense_pairs) {
+                                                                       int tile_capacity, int* route, unsigned long long dense_pairs,
+                                                                       const unsigned* choice) {
+    if (!route_open(choice)) return;
     plan_query_tiles(query_starts, key_starts, tile_starts, tiles, next_tile, tile_capacity, route, dense_pairs);
 }
 
@@ -174,6 +177,7 @@ struct TilePlan {
 template <bool PACKED, int R, int DV>
 __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(const BlockArgs a) {
     constexpr int KSTEPS = R / 16, VTILES = DV / 8;
+    if (!route_open(a.choice)) return;
     extern __shared__ __align__(16) unsigned char storage[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     auto& mine = reinterpret_cast<BlockWarpShared<R, DV>*>(storage)[warp];

@@ -39,6 +39,7 @@ struct DenseArgs {
     __nv_bfloat16* out;
     float* lse2;
     int batch, heads, n, lut_stride, chunks;
+    const unsigned* choice;  // route word of a captured graph, or null
 };
 
 template <int R, int DV>
@@ -280,6 +281,7 @@ __device__ __forceinline__ void hard_forward_dense_chunk(const DenseArgs& a, int
 template <int R, int DV>
 __global__ __launch_bounds__(DENSE_WARPS * 32, 1) void hard_forward_dense_kernel(const DenseArgs a) {
     const int batch_heads = a.batch * a.heads;
+    if (!route_open(a.choice)) return;  // (the word holds still during a replay, so the whole grid agrees)
     if (!dense_any(a.route, batch_heads)) return;
     dense_walk_all(a.iq, a.ik, a.documents, a.route, a.rows, 1, batch_heads, a.chunks, a.n);
     __threadfence();

@@ -157,7 +157,8 @@ __device__ __forceinline__ void counting_pass(const int* __restrict__ labels, co
 
 // blockIdx.y picks the side: both sides of a readout are built by one launch.
 template <int THREADS>
-__global__ __launch_bounds__(THREADS, THREADS == 512 ? 2 : 1) void build_index_kernel(const IndexSide side0, const IndexSide side1, int n) {
+__global__ __launch_bounds__(THREADS, THREADS == 512 ? 2 : 1) void build_index_kernel(const IndexSide side0, const IndexSide side1, int n, const unsigned* choice) {
+    if (!route_open(choice)) return;
     const IndexSide& side = blockIdx.y ? side1 : side0;
     const int* __restrict__ labels = side.labels;
     int2* __restrict__ entries = side.entries;
@@ -244,7 +245,8 @@ struct IndexClusterShared {
     int bins[3][PASS_BINS];      // this CTA's bin sizes: first pass, second pass by original part, second pass by its part of the first pass's output
 };
 
-__global__ __launch_bounds__(CLUSTER_THREADS, 1) void build_index_cluster_kernel(const IndexSide side0, const IndexSide side1, int n) {
+__global__ __launch_bounds__(CLUSTER_THREADS, 1) void build_index_cluster_kernel(const IndexSide side0, const IndexSide side1, int n, const unsigned* choice) {
+    if (!route_open(choice)) return;  // (every CTA of a cluster reads the same word, so none waits for another)
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const int parts = cluster.num_blocks(), part = cluster.block_rank(), slice = blockIdx.x / parts;
@@ -375,7 +377,8 @@ static IndexSide index_side(const int* labels, void* workspace, int batch_heads,
 
 // Very few slices: a cluster of CTAs per slice.  Few: the widest CTA, which finishes a slice soonest.  Many: narrower
 // CTAs, several to an SM.
-static void run_build_index(const IndexSide& side0, const IndexSide& side1, int batch_heads, int sides, int n, cudaStream_t stream) {
+static void run_build_index(const IndexSide& side0, const IndexSide& side1, int batch_heads, int sides, int n, const unsigned* choice,
+                            cudaStream_t stream) {
     static const bool ready = [] {  // shared memory beyond 48 KiB has to be asked for once per kernel
         return cudaFuncSetAttribute(build_index_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(IndexShared<1024>))) == cudaSuccess &&
                cudaFuncSetAttribute(build_index_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(IndexShared<512>))) == cudaSuccess;
@@ -400,11 +403,11 @@ static void run_build_index(const IndexSide& side0, const IndexSide& side1, int 
         attribute.val.clusterDim.z = 1;
         config.attrs = &attribute;
         config.numAttrs = 1;
-        cudaLaunchKernelEx(&config, build_index_cluster_kernel, side0, side1, n);
+        cudaLaunchKernelEx(&config, build_index_cluster_kernel, side0, side1, n, choice);
     } else if (slices <= sms) {
-        build_index_kernel<1024><<<dim3(batch_heads, sides), 1024, sizeof(IndexShared<1024>), stream>>>(side0, side1, n);
+        build_index_kernel<1024><<<dim3(batch_heads, sides), 1024, sizeof(IndexShared<1024>), stream>>>(side0, side1, n, choice);
     } else {
-        build_index_kernel<512><<<dim3(batch_heads, sides), 512, sizeof(IndexShared<512>), stream>>>(side0, side1, n);
+        build_index_kernel<512><<<dim3(batch_heads, sides), 512, sizeof(IndexShared<512>), stream>>>(side0, side1, n, choice);
     }
 }
 
@@ -412,7 +415,7 @@ cudaError_t launch_build_index(const int* labels, int batch_heads, int n, void* 
                                cudaStream_t stream) {
     const IndexSide target = index_side(labels, workspace, batch_heads, n, side, sides);
     KernelTimer timer("build_index", stream);
-    run_build_index(target, target, batch_heads, 1, n, stream);
+    run_build_index(target, target, batch_heads, 1, n, nullptr, stream);  // (the longest-match entry is not routed)
     return cudaGetLastError();
 }
 
@@ -420,7 +423,7 @@ cudaError_t launch_build_index_pair(const int* labels0, const int* labels1, int 
                                     cudaStream_t stream) {
     KernelTimer timer("build_index", stream);
     run_build_index(index_side(labels0, workspace, batch_heads, n, 0, 2), index_side(labels1, workspace, batch_heads, n, 1, 2),
-                    batch_heads, 2, n, stream);
+                    batch_heads, 2, n, route_word(), stream);
     return cudaGetLastError();
 }
 

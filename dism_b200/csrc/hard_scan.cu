@@ -13,7 +13,8 @@ namespace dism {
 // first mismatch, which is the largest coordinate because columns fall as the walk rises.
 __global__ void hard_summary_kernel(const int* __restrict__ iq, const int* __restrict__ ik,
                                     const uint8_t* __restrict__ hard, int batch_heads, int n,
-                                    int* __restrict__ out) {
+                                    int* __restrict__ out, const unsigned* choice) {
+    if (!route_open(choice)) return;
     const int checkpoints = (n - 1) / 32;
     const int64_t total = int64_t(batch_heads) * checkpoints * n;
     for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += int64_t(gridDim.x) * blockDim.x) {
@@ -40,14 +41,16 @@ cudaError_t launch_hard_summary(const int* iq, const int* ik, const uint8_t* har
     const int64_t cap = ctas ? ctas : int64_t(device_sm_count()) * 32;
     if (blocks > cap) blocks = cap;
     KernelTimer timer("hard_summary", stream);
-    hard_summary_kernel<<<int(blocks), 256, 0, stream>>>(iq, ik, hard, batch * heads, n, summary);
+    hard_summary_kernel<<<int(blocks), 256, 0, stream>>>(iq, ik, hard, batch * heads, n, summary, route_word());
     return cudaGetLastError();
 }
 
 // boundary[c][j] = max(summary[c][j], boundary[c-1][j-32]).  A thread owns one chain
 // (c, e+32c), c ascending, so in-place operation is safe; entries right of a strip's last row are
 // written -1 and never read.
-__global__ void hard_chunk_kernel(const int* __restrict__ summary, int* __restrict__ out, int batch_heads, int n) {
+__global__ void hard_chunk_kernel(const int* __restrict__ summary, int* __restrict__ out, int batch_heads, int n,
+                                  const unsigned* choice) {
+    if (!route_open(choice)) return;
     const int checkpoints = (n - 1) / 32, chains = 32 * checkpoints;
     const int64_t plane = int64_t(checkpoints) * n;
     const int64_t threads = int64_t(gridDim.x) * blockDim.x, self = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -74,7 +77,7 @@ cudaError_t launch_hard_chunk(const int* summary, int* boundary, int batch_heads
     const int64_t cap = int64_t(device_sm_count()) * 64;
     if (blocks > cap) blocks = cap;
     KernelTimer timer("hard_chunk", stream);
-    hard_chunk_kernel<<<int(blocks), 128, 0, stream>>>(summary, boundary, batch_heads, n);
+    hard_chunk_kernel<<<int(blocks), 128, 0, stream>>>(summary, boundary, batch_heads, n, route_word());
     return cudaGetLastError();
 }
 

@@ -10,9 +10,12 @@ Differences a caller can see: `hard_readout` and `hard_backward` accept `boundar
 lengths are then derived from the labels inside the kernel, nothing quadratic is stored); with a
 packed `table` a boundary is checked for shape and otherwise left unread (same bits either way);
 the packed `hard_summary` / `hard_chunk` run document by document through the fixed-length kernels; the soft path (`core_forward`, `core_backward`) is not
-built and raises NotImplementedError; the `choice` device word of the reference's CUDA-graph
-router is accepted only as None.
+built and raises NotImplementedError.  The `choice` device word of the reference's CUDA-graph
+router (one CUDA int32; 0 runs the hard path, anything else makes its kernels return at once) is
+handed to the library for the calls of the operator it was given to.
 """
+import contextlib
+
 import torch
 
 from dism_b200 import _lib
@@ -41,11 +44,20 @@ def _stream(tensor):
     return torch.cuda.current_stream(tensor.device).cuda_stream
 
 
-def _no_table(table, choice):
-    if table is not None:
-        raise NotImplementedError('this entry takes fixed-length input only')
-    if choice is not None:
-        raise NotImplementedError('the CUDA-graph route word is not supported')
+@contextlib.contextmanager
+def _routed(choice, device):
+    """Checks the route word as dism_v3/include/host/graph_route.h:4-10 does and sets it for the library calls inside."""
+    if choice is None:
+        yield
+        return
+    if not (torch.is_tensor(choice) and choice.device == device and choice.dtype == torch.int32
+            and choice.numel() == 1 and choice.is_contiguous()):
+        _fail('graph choice must be one contiguous CUDA int32 on the operand device')
+    _lib.check(_abi.dism_route_word(choice.data_ptr()))
+    try:
+        yield
+    finally:
+        _abi.dism_route_word(None)
 
 
 # ---- packed (varlen) layouts -------------------------------------------------------------------
@@ -145,7 +157,6 @@ def hard_summary(query, key, hard, table=None, ctas=0, choice=None):
     """int32 labels [B,H,N] -> strip summaries int32 [B,H,(N-1)//32,N]; packed: the documents'
     [H,(length-1)//32,length] regions one after the other, flattened."""
     if table is not None:
-        _no_table(None, choice)
         if not (torch.is_tensor(query) and query.dim() == 3 and query.size(0) == 1):
             _fail('packed labels/layout length mismatch')
         h, n = query.size(1), query.size(2)
@@ -153,10 +164,9 @@ def hard_summary(query, key, hard, table=None, ctas=0, choice=None):
         spans = _documents(table, n, hard.size(0))
         row_tokens = n // hard.size(0)
         pieces = [hard_summary(query[:, :, a:a + m].contiguous(), key[:, :, a:a + m].contiguous(),
-                               hard[a // row_tokens:a // row_tokens + 1].contiguous(), None, ctas).flatten()
+                               hard[a // row_tokens:a // row_tokens + 1].contiguous(), None, ctas, choice).flatten()
                   for a, m in spans]
         return torch.cat(pieces) if pieces else torch.empty(0, dtype=torch.int32, device=query.device)
-    _no_table(table, choice)
     if not (torch.is_tensor(query) and query.is_cuda and query.dtype == torch.int32 and query.dim() == 3
             and query.is_contiguous()):
         _fail('query labels must be contiguous CUDA int32 [B,H,N]')
@@ -169,7 +179,7 @@ def hard_summary(query, key, hard, table=None, ctas=0, choice=None):
     _check_hard(hard, query.device, b, h)
     if ctas < 0:
         _fail('invalid CTA count')
-    with torch.cuda.device(query.device):
+    with torch.cuda.device(query.device), _routed(choice, query.device):
         out = torch.empty((b, h, (n - 1) // 32, n), dtype=torch.int32, device=query.device)
         _lib.check(_abi.dism_hard_summary(query.data_ptr(), key.data_ptr(), hard.data_ptr(), b, h, n, int(ctas),
                                           out.data_ptr(), _stream(query)))
@@ -181,7 +191,6 @@ def hard_chunk(summary, table=None, heads=0, choice=None, inplace=False):
     if not (torch.is_tensor(summary) and summary.is_cuda and summary.dtype == torch.int32 and summary.is_contiguous()):
         _fail('hard summary must be contiguous CUDA int32')
     if table is not None:
-        _no_table(None, choice)
         lengths = [m for _, m, *_ in table.tolist() if m]
         expected = sum(heads * ((m - 1) // 32) * m for m in lengths)
         if heads <= 0 or summary.dim() != 1 or summary.numel() != expected:
@@ -192,10 +201,9 @@ def hard_chunk(summary, table=None, heads=0, choice=None, inplace=False):
             size = heads * ((m - 1) // 32) * m
             if size:
                 region = summary[at:at + size].view(1, heads, (m - 1) // 32, m)
-                out[at:at + size] = hard_chunk(region, None, heads, None, inplace).flatten()
+                out[at:at + size] = hard_chunk(region, None, heads, choice, inplace).flatten()
             at += size
         return out
-    _no_table(table, choice)
     if summary.dim() != 4:
         _fail('fixed hard summary must be [B,H,C,N]')
     b, h, c, n = summary.shape
@@ -203,7 +211,7 @@ def hard_chunk(summary, table=None, heads=0, choice=None, inplace=False):
         _fail('invalid fixed batch/head count')
     if n <= 0 or n % 256 or c != (n - 1) // 32:
         _fail('invalid hard checkpoint shape/alignment')
-    with torch.cuda.device(summary.device):
+    with torch.cuda.device(summary.device), _routed(choice, summary.device):
         out = summary if inplace else torch.empty_like(summary)
         _lib.check(_abi.dism_hard_chunk(summary.data_ptr(), out.data_ptr(), b * h, n, _stream(summary)))
     return out
@@ -211,13 +219,12 @@ def hard_chunk(summary, table=None, heads=0, choice=None, inplace=False):
 
 def hard_log_weights(tau, n, choice=None):
     """FP32 log2 geometric-sum table [H,n+1] for per-head tau."""
-    _no_table(None, choice)
     if not (torch.is_tensor(tau) and tau.is_cuda and tau.dtype == torch.float32 and tau.dim() == 1
             and tau.is_contiguous() and 0 < tau.numel() <= 65535):
         _fail('tau must be contiguous CUDA FP32 [H]')
     if n <= 0 or n % 256:
         _fail('LUT maximum length must be positive and 256-aligned')
-    with torch.cuda.device(tau.device):
+    with torch.cuda.device(tau.device), _routed(choice, tau.device):
         out = torch.empty((tau.numel(), n + 1), dtype=torch.float32, device=tau.device)
         _lib.check(_abi.dism_hard_log_weights(tau.data_ptr(), tau.numel(), int(n), out.data_ptr(), _stream(tau)))
     return out
@@ -306,7 +313,6 @@ def _recall_index(norm, iq, ik):
 
 def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
     """x = (sq, sk, v, query labels, key labels, hard) -> (bf16 [B,N,H,DV], FP32 log2 normaliser [B,H,N])."""
-    _no_table(None, choice)
     b, n, h, r = _vectors(x, 6, ('SQ', 'SK', 'V', 'query labels', 'key labels', 'hard flags'))
     sq, sk, v, iq, ik, hard = x
     _check(sq, torch.bfloat16, (b, n, h, r), 'SQ')
@@ -321,9 +327,12 @@ def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
     if ctas < 0:
         _fail('invalid CTA count')
     boundary_ptr = _check_boundary(boundary, b, h, n, sq.device) if table is None else 0
-    with torch.cuda.device(sq.device):
-        out = torch.empty((b, n, h, dv), dtype=torch.bfloat16, device=sq.device)
-        norm = torch.empty((b, h, n), dtype=torch.float32, device=sq.device)
+    # The kernels write every row, so outputs start uninitialised; with a route word they start as zeros, which is
+    # what a closed route returns (the reference zero-fills them always: dism_v3/src/host/hard_forward.cpp:92-93).
+    fresh = torch.empty if choice is None else torch.zeros
+    with torch.cuda.device(sq.device), _routed(choice, sq.device):
+        out = fresh((b, n, h, dv), dtype=torch.bfloat16, device=sq.device)
+        norm = fresh((b, h, n), dtype=torch.float32, device=sq.device)
         size = _abi.dism_hard_readout_workspace(b, h, n)
         workspace = torch.empty((size,), dtype=torch.uint8, device=sq.device)
         _lib.check(_abi.dism_hard_readout(sq.data_ptr(), sk.data_ptr(), v.data_ptr(), iq.data_ptr(), ik.data_ptr(),
@@ -336,7 +345,6 @@ def hard_readout(x, boundary, lut, table=None, ctas=0, choice=None):
 
 def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None):
     """x = (sq, sk, v, dO, query labels, key labels, hard) -> [dSQ f32, dSK bf16, dV bf16, dtau f32[H]]."""
-    _no_table(None, choice)
     b, n, h, r = _vectors(x, 7, ('SQ', 'SK', 'V', 'dO', 'query labels', 'key labels', 'hard'))
     sq, sk, v, dout, iq, ik, hard = x
     _check(sq, torch.bfloat16, (b, n, h, r), 'SQ')
@@ -356,10 +364,12 @@ def hard_backward(x, boundary, lut, normalizer, ctas=0, table=None, choice=None)
     if ctas < 0:
         _fail('invalid CTA count')
     boundary_ptr = _check_boundary(boundary, b, h, n, sq.device) if table is None else 0
-    with torch.cuda.device(sq.device):
-        dsq = torch.empty((b, n, h, r), dtype=torch.float32, device=sq.device)
-        dsk, dv_out = torch.empty_like(sk), torch.empty_like(v)
-        dtau = torch.empty((h,), dtype=torch.float32, device=sq.device)
+    # zeros under a route word: a closed route returns zero gradients (dism_v3/src/host/hard_backward.cpp:106-108)
+    fresh = torch.empty if choice is None else torch.zeros
+    with torch.cuda.device(sq.device), _routed(choice, sq.device):
+        dsq = fresh((b, n, h, r), dtype=torch.float32, device=sq.device)
+        dsk, dv_out = fresh(sk.shape, dtype=sk.dtype, device=sk.device), fresh(v.shape, dtype=v.dtype, device=v.device)
+        dtau = fresh((h,), dtype=torch.float32, device=sq.device)
         size = _abi.dism_hard_backward_workspace(b, h, n, lut.size(1))
         workspace = torch.empty((size,), dtype=torch.uint8, device=sq.device)
         index = _recall_index(normalizer, iq, ik)

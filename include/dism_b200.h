@@ -26,6 +26,19 @@ const char *dism_last_error(void);
 /* ABI revision; bumped on any signature change. */
 int dism_abi_version(void);
 
+/* Route word of a captured CUDA graph: the `choice` argument of the reference's hard operators
+ * (dism_v3/include/host/graph_route.h:4-10 validates it, include/common/graph_route.cuh:8-13 reads it;
+ * passed to the kernels in src/host/hard_summary.cpp, hard_forward.cpp, hard_backward.cpp).
+ * `choice` is one int32 in device memory, or NULL.  While it is set, every kernel that this THREAD
+ * launches through dism_hard_summary, dism_hard_chunk, dism_hard_log_weights, dism_hard_dlog_weights,
+ * dism_hard_readout(_static) and dism_hard_backward reads the word with acquire semantics when it
+ * starts and returns at once, unless the word is 0 (the backward's tile kernels instead find an
+ * empty tile plan that its plan kernel wrote into the workspace).  No operand is read, no output written.  The word
+ * is read at execution time, so a captured graph follows the value written before each replay.
+ * Set it before the calls of one operator and clear it (NULL) afterwards; the discretiser and
+ * dism_longest_match are not routed.  Outputs of a closed route are left as they were. */
+int dism_route_word(const uint32_t *choice);
+
 /* Discretiser: labels[b,h,n] = argmax_v <x[b,n,h,:], codebook[h,v,:]>, lowest index on ties,
  * FP32 accumulation in ascending d.  x bf16 [B,N,H,D], codebook bf16 [H,V,D], D in {32,64,128}.
  * Stands in for the label output of emb_fwd (dism_v3/python/flash_dism/emb_kernel.py:88-108,

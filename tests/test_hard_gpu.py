@@ -376,6 +376,60 @@ def test_backward_reuses_the_forward_index(api):
     assert all(torch.equal(a, e) for a, e in zip(fresh, again))
 
 
+# ---- the route word of a captured graph ----------------------------------------------------------------
+@pytest.mark.parametrize('kind', ['random', 'equal'])
+def test_route_word_opens_and_closes_a_captured_graph(api, kind):
+    """`_graph_choice` (dism_v3/include/common/graph_route.cuh:8-13): word 0 runs the path and gives the bits of a
+    call without it; any other value makes every kernel return, which leaves the zero-filled outputs.  The word is
+    read when the kernels run, so one captured graph follows what was written before each replay (the use in
+    dism_v3/tests/test_planner_graph.py:403-433).  `equal` labels take the dense kernels, `random` the tile kernels."""
+    b, n, h, r, dv = 2, 512, 2, 16, 64
+    sq, sk, v, dout = (t.cuda() for t in vectors(21, b, n, h, r, dv))
+    g = torch.Generator().manual_seed(22)
+    if kind == 'random':
+        iq, ik = (torch.randint(0, 9, (b, h, n), generator=g, dtype=torch.int32).cuda() for _ in range(2))
+    else:
+        iq, ik = (torch.full((b, h, n), 3, dtype=torch.int32, device='cuda') for _ in range(2))
+    hard = torch.ones(b, h, dtype=torch.bool, device='cuda')
+    tau = torch.tensor([.3, -.2], device='cuda')
+
+    def call(choice):
+        out, norm, state = api['fwd'].forward_hard(sq, sk, v, iq, ik, hard, tau, save_state=True, _graph_choice=choice)
+        grads = api['bwd'].backward_hard(sq, sk, v, dout, iq, ik, hard, norm, state, _graph_choice=choice)
+        return [out, norm, *grads], state['boundary']
+
+    expected, boundary = call(None)
+    choice = torch.zeros(1, dtype=torch.int32, device='cuda')
+    opened, opened_boundary = call(choice)
+    assert all(torch.equal(a, e) for a, e in zip(opened, expected)) and torch.equal(opened_boundary, boundary)
+    choice.fill_(7)
+    closed, _ = call(choice)
+    assert all(not t.any() for t in closed)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call(choice)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        replayed, replayed_boundary = call(choice)
+    for selected in (0, 5, 0, 1):
+        choice.fill_(selected)
+        graph.replay()
+        torch.cuda.synchronize()
+        if selected == 0:
+            assert all(torch.equal(a, e) for a, e in zip(replayed, expected)) and torch.equal(replayed_boundary, boundary)
+        else:
+            assert all(not t.any() for t in replayed)
+
+    for wrong in (torch.zeros(1, dtype=torch.int64, device='cuda'), torch.zeros(2, dtype=torch.int32, device='cuda'),
+                  torch.zeros(1, dtype=torch.int32)):
+        with pytest.raises(RuntimeError, match='graph choice'):
+            api['fwd'].hard_log_weights(tau, n, _graph_choice=wrong)
+
+
 # ---- the CPU-runnable reference configuration --------------------------------------------------------
 def test_config1_reference_case(api, oracle):
     g = golden('config1.npz')
