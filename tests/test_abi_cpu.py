@@ -29,7 +29,7 @@ def test_every_declared_symbol_is_exported_and_typed(lib):
     for name in names:
         assert hasattr(lib, name), f'{name} is declared in include/dism_b200.h but not exported'
         assert name in _lib.SIGNATURES, f'{name} has no ctypes signature'
-    assert lib.dism_abi_version() >= 6
+    assert lib.dism_abi_version() >= 8
 
 
 def test_library_has_no_torch_dependency(lib):
@@ -74,6 +74,9 @@ def test_argument_checks_run_without_a_device(lib):
     assert lib.dism_labels(p, p, 1, 16, 2, 48, 512, p, None) == 2 and 'unsupported' in message(lib)
     assert lib.dism_labels(p, ctypes.c_void_p(4104), 1, 16, 2, 64, 512, p, None) == 1 and '16-byte aligned' in message(lib)
     assert lib.dism_longest_match(p, 1, 13, p, p, p, p, 1 << 20, None) == 1
+    # the route word: one aligned device int32, or NULL to clear it (the pointer is only stored here)
+    assert lib.dism_route_word(ctypes.c_void_p(4098)) == 1 and 'graph choice' in message(lib)
+    assert lib.dism_route_word(p) == 0 and lib.dism_route_word(None) == 0
     assert lib.dism_hard_readout_workspace(8, 16, 8192) > 8 * 16 * 8192 * 8
     assert lib.dism_hard_backward_workspace(8, 16, 8192, 8193) > 2 * 8 * 16 * 8192 * 8
 
