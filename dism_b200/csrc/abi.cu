@@ -142,6 +142,7 @@ int dism_hard_summary(const int32_t* iq, const int32_t* ik, const uint8_t* hard,
     if (int status = check_shape(batch, heads, n)) return status;
     if (!iq || !ik || !hard || (!summary && n > 32)) return fail(DISM_EINVAL, "null pointer");
     if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
+    if (!aligned(summary, 16)) return fail(DISM_EINVAL, "hard summary must be 16-byte aligned");
     return cuda_status(dism::launch_hard_summary(iq, ik, hard, batch, heads, n, ctas, summary,
                                                  static_cast<cudaStream_t>(stream)), "hard_summary");
 }
@@ -149,6 +150,7 @@ int dism_hard_summary(const int32_t* iq, const int32_t* ik, const uint8_t* hard,
 int dism_hard_chunk(const int32_t* summary, int32_t* boundary, int batch_heads, int n, void* stream) {
     if (int status = check_shape(1, batch_heads, n)) return status;
     if (!summary || !boundary) return fail(DISM_EINVAL, "null pointer");
+    if (!aligned(boundary, 16)) return fail(DISM_EINVAL, "hard boundary must be 16-byte aligned");
     if (int64_t(n) + int64_t((n - 1) / 32) * 32 > INT_MAX) return fail(DISM_EINVAL, "invalid hard checkpoint shape");
     return cuda_status(dism::launch_hard_chunk(summary, boundary, batch_heads, n, static_cast<cudaStream_t>(stream)),
                        "hard_chunk");

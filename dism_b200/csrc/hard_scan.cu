@@ -9,36 +9,46 @@
 namespace dism {
 
 // summary[bh][c][j] = largest mismatching key coordinate on the diagonal segment that ends at
-// (32c+31, j) inside strip c, or -1.  One thread per entry walks up the diagonal and stops at the
-// first mismatch, which is the largest coordinate because columns fall as the walk rises.
-__global__ void hard_summary_kernel(const int* __restrict__ iq, const int* __restrict__ ik,
-                                    const uint8_t* __restrict__ hard, int batch_heads, int n,
-                                    int* __restrict__ out, const unsigned* choice) {
+// (32c+31, j) inside strip c, or -1.  An entry walks up its diagonal and stops at the first
+// mismatch, which is the largest coordinate because columns fall as the walk rises.  The stage is
+// bound by the 4 bytes it writes per entry: a CTA takes whole (slice, strip) rows of the rectangle
+// (row and column come from the loop counters, not from a division per entry), a thread fills four
+// adjacent entries and writes them with one 16-byte streaming store; entries right of the strip's
+// last row are -1 without a look at the labels.
+__global__ __launch_bounds__(256) void hard_summary_kernel(const int* __restrict__ iq, const int* __restrict__ ik,
+                                                           const uint8_t* __restrict__ hard, int batch_heads, int n,
+                                                           int* __restrict__ out, const unsigned* choice) {
     if (!route_open(choice)) return;
     const int checkpoints = (n - 1) / 32;
-    const int64_t total = int64_t(batch_heads) * checkpoints * n;
-    for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += int64_t(gridDim.x) * blockDim.x) {
-        const int j = int(e % n);
-        const int64_t t = e / n;
-        const int c = int(t % checkpoints), bh = int(t / checkpoints);
-        int result = -1;
-        if (hard[bh] && j <= 32 * c + 31) {
-            const int* q = iq + int64_t(bh) * n + 32 * c + 31;
-            const int* k = ik + int64_t(bh) * n + j;
-            const int steps = min(32, j + 1);
-            for (int s = 0; s < steps; ++s)
-                if (__ldg(q - s) != __ldg(k - s)) { result = j - s; break; }
+    const int64_t rows = int64_t(batch_heads) * checkpoints;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int bh = int(row / checkpoints), c = int(row - int64_t(bh) * checkpoints);
+        const int last = 32 * c + 31;  // the strip's last query row
+        const bool walk = hard[bh] != 0;
+        const int* q = iq + int64_t(bh) * n + last;
+        const int* k = ik + int64_t(bh) * n;
+        int4* target = reinterpret_cast<int4*>(out + row * n);
+        for (int j4 = threadIdx.x * 4; j4 < n; j4 += blockDim.x * 4) {
+            int result[4] = {-1, -1, -1, -1};
+            if (walk && j4 <= last) {  // (then j4 + 3 <= last too: last + 1 is a multiple of 32)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int j = j4 + u, steps = min(32, j + 1);
+                    for (int s = 0; s < steps; ++s)
+                        if (__ldg(q - s) != __ldg(k + j - s)) { result[u] = j - s; break; }
+                }
+            }
+            __stcs(target + j4 / 4, make_int4(result[0], result[1], result[2], result[3]));
         }
-        out[e] = result;
     }
 }
 
 cudaError_t launch_hard_summary(const int* iq, const int* ik, const uint8_t* hard, int batch, int heads, int n,
                                 int ctas, int* summary, cudaStream_t stream) {
-    const int64_t total = int64_t(batch) * heads * ((n - 1) / 32) * n;
-    if (!total) return cudaSuccess;
-    int64_t blocks = (total + 255) / 256;
-    const int64_t cap = ctas ? ctas : int64_t(device_sm_count()) * 32;
+    const int64_t rows = int64_t(batch) * heads * ((n - 1) / 32);
+    if (!rows) return cudaSuccess;
+    int64_t blocks = rows;
+    const int64_t cap = ctas ? ctas : int64_t(device_sm_count()) * 16;
     if (blocks > cap) blocks = cap;
     KernelTimer timer("hard_summary", stream);
     hard_summary_kernel<<<int(blocks), 256, 0, stream>>>(iq, ik, hard, batch * heads, n, summary, route_word());
@@ -46,27 +56,42 @@ cudaError_t launch_hard_summary(const int* iq, const int* ik, const uint8_t* har
 }
 
 // boundary[c][j] = max(summary[c][j], boundary[c-1][j-32]).  A thread owns one chain
-// (c, e+32c), c ascending, so in-place operation is safe; entries right of a strip's last row are
-// written -1 and never read.
-__global__ void hard_chunk_kernel(const int* __restrict__ summary, int* __restrict__ out, int batch_heads, int n,
-                                  const unsigned* choice) {
+// (c, e+32c), c ascending, so in-place operation is safe (no __restrict__: the two may be one
+// buffer); the 32 chains of a warp read and write one aligned 128-byte line per strip.  Entries
+// right of a strip's last row are written -1, row by row with 16-byte stores, and never read.
+__global__ __launch_bounds__(128) void hard_chunk_kernel(const int* summary, int* out, int batch_heads, int n,
+                                                         const unsigned* choice) {
     if (!route_open(choice)) return;
     const int checkpoints = (n - 1) / 32, chains = 32 * checkpoints;
     const int64_t plane = int64_t(checkpoints) * n;
     const int64_t threads = int64_t(gridDim.x) * blockDim.x, self = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     for (int64_t id = self; id < int64_t(batch_heads) * chains; id += threads) {
-        const int bh = int(id / chains), e = 31 - int(id % chains);
-        const int64_t base = bh * plane;
+        const int bh = int(id / chains), e = 31 - int(id - int64_t(bh) * chains);
+        const int first = e >= 0 ? 0 : (31 - e) / 32;
+        const int* source = summary + bh * plane + e;
+        int* target = out + bh * plane + e;
         int state = -1;
-        for (int c = e >= 0 ? 0 : (31 - e) / 32; c < checkpoints; ++c) {
-            const int64_t at = base + int64_t(c) * n + e + 32 * c;
-            state = max(state, summary[at]);
-            out[at] = state;
+        int c = first;
+        for (; c + 4 <= checkpoints; c += 4) {  // four independent loads in flight, then the dependent maxima
+            int value[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) value[u] = __ldcs(source + int64_t(c + u) * (n + 32));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                state = max(state, value[u]);
+                __stcs(target + int64_t(c + u) * (n + 32), state);
+            }
+        }
+        for (; c < checkpoints; ++c) {
+            state = max(state, __ldcs(source + int64_t(c) * (n + 32)));
+            __stcs(target + int64_t(c) * (n + 32), state);
         }
     }
-    for (int64_t id = self; id < int64_t(batch_heads) * plane; id += threads) {
-        const int j = int(id % n), c = int(id / n % checkpoints);
-        if (j > 32 * c + 31) out[id] = -1;
+    const int64_t rows = int64_t(batch_heads) * checkpoints;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int c = int(row % checkpoints);
+        int4* target = reinterpret_cast<int4*>(out + row * n);
+        for (int j4 = 32 * c + 32 + threadIdx.x * 4; j4 < n; j4 += blockDim.x * 4) __stcs(target + j4 / 4, make_int4(-1, -1, -1, -1));
     }
 }
 
