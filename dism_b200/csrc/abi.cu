@@ -142,7 +142,7 @@ int dism_hard_summary(const int32_t* iq, const int32_t* ik, const uint8_t* hard,
     if (int status = check_shape(batch, heads, n)) return status;
     if (!iq || !ik || !hard || (!summary && n > 32)) return fail(DISM_EINVAL, "null pointer");
     if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
-    if (!aligned(summary, 16)) return fail(DISM_EINVAL, "hard summary must be 16-byte aligned");
+    if (!aligned(summary, 16) || !aligned(ik, 16)) return fail(DISM_EINVAL, "key labels and hard summary must be 16-byte aligned");
     return cuda_status(dism::launch_hard_summary(iq, ik, hard, batch, heads, n, ctas, summary,
                                                  static_cast<cudaStream_t>(stream)), "hard_summary");
 }

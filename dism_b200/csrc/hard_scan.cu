@@ -31,11 +31,23 @@ __global__ __launch_bounds__(256) void hard_summary_kernel(const int* __restrict
         for (int j4 = threadIdx.x * 4; j4 < n; j4 += blockDim.x * 4) {
             int result[4] = {-1, -1, -1, -1};
             if (walk && j4 <= last) {  // (then j4 + 3 <= last too: last + 1 is a multiple of 32)
+                // the four walks go up together: step s compares query label last - s with keys j4 - s .. j4 - s + 3,
+                // three of which the step before already held
+                const int4 head = __ldg(reinterpret_cast<const int4*>(k + j4));
+                int window[4] = {head.x, head.y, head.z, head.w};
+                unsigned pending = 0xf;
+                for (int s = 0; s < 32 && pending; ++s) {
+                    const int mine = __ldg(q - s);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int j = j4 + u, steps = min(32, j + 1);
-                    for (int s = 0; s < steps; ++s)
-                        if (__ldg(q - s) != __ldg(k + j - s)) { result[u] = j - s; break; }
+                    for (int u = 0; u < 4; ++u) {
+                        if (j4 + u - s < 0) pending &= ~(1u << u);  // the diagonal left the rectangle
+                        else if ((pending >> u & 1) && window[u] != mine) {
+                            result[u] = j4 + u - s;
+                            pending &= ~(1u << u);
+                        }
+                    }
+                    window[3] = window[2]; window[2] = window[1]; window[1] = window[0];
+                    window[0] = j4 - s - 1 >= 0 ? __ldg(k + j4 - s - 1) : 0;
                 }
             }
             __stcs(target + j4 / 4, make_int4(result[0], result[1], result[2], result[3]));
@@ -72,12 +84,12 @@ __global__ __launch_bounds__(128) void hard_chunk_kernel(const int* summary, int
         int* target = out + bh * plane + e;
         int state = -1;
         int c = first;
-        for (; c + 4 <= checkpoints; c += 4) {  // four independent loads in flight, then the dependent maxima
-            int value[4];
+        for (; c + 8 <= checkpoints; c += 8) {  // eight independent loads in flight, then the dependent maxima
+            int value[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) value[u] = __ldcs(source + int64_t(c + u) * (n + 32));
+            for (int u = 0; u < 8; ++u) value[u] = __ldcs(source + int64_t(c + u) * (n + 32));
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 state = max(state, value[u]);
                 __stcs(target + int64_t(c + u) * (n + 32), state);
             }
