@@ -523,8 +523,9 @@ def run_reference(args):
 
 
 def run_other_workload(args):
-    """The two side workloads: forward only on the long-context shape (one GPU's share: 4 heads of
-    N = 131072 with planted 1024-long runs), and the single-longest-match reduction on symbol streams."""
+    """The side workloads: forward only on the long-context shape (one GPU's share: 4 heads of
+    N = 131072 with planted 1024-long runs), forward and backward on dense labels, the integer stages of the saved-state
+    route, and the single-longest-match reduction on symbol streams."""
     import dism_b200
     dism_b200.install_dropin()
     import cu_flash_dism as cu
@@ -591,6 +592,38 @@ def run_other_workload(args):
             record['ms'][pattern] = {
                 'forward': timed(lambda: forward_hard(sq, sk, v, iq, ik, hard, tau)),
                 'backward': timed(lambda: backward_hard(sq, sk, v, dout, iq, ik, hard, norm, dict(boundary=None, log_weights=lut)))}
+        record.update(steps=args.steps, warmup=args.warmup)
+        print(json.dumps(record))
+    elif args.workload == 'saved_state':
+        # The integer stages that forward_hard(save_state=True) adds: strip summaries, then boundary composition, on the
+        # benchmark shape and on the shape of the reference's own hard-forward benchmark.  Both move bytes: the summary
+        # writes the int32 rectangle [B,H,(N-1)//32,N]; the composition reads its causal part (32c+32 entries of strip c)
+        # and writes all of it.  Times are the library's per-kernel CUDA events, fractions are of the HBM copy peak.
+        from dism_b200 import _lib
+        peak, source = measured_peak('hbm_gbs', 6650.0)
+        record = {'workload': 'strip summaries and boundary composition, labels uniform over 512 symbols', 'peak_gbs': peak,
+                  'peak_source': source, 'shapes': {}}
+        for b, h, n in ((8, 16, 8192), (16, 6, 2048)):
+            iq, ik = [torch.randint(0, 512, (b, h, n), generator=g, device='cuda', dtype=torch.int32) for _ in range(2)]
+            hard = torch.ones(b, h, dtype=torch.bool, device='cuda')
+            for _ in range(args.warmup):
+                cu.hard_chunk(cu.hard_summary(iq, ik, hard))
+            torch.cuda.synchronize()
+            _lib.load().dism_profile_enable(1)
+            for _ in range(args.steps):
+                cu.hard_chunk(cu.hard_summary(iq, ik, hard))
+            torch.cuda.synchronize()
+            times = {}
+            for name, ms in _lib.kernel_timings():
+                times.setdefault(name, []).append(ms)
+            _lib.load().dism_profile_enable(0)
+            strips = (n - 1) // 32
+            rectangle = b * h * strips * n * 4
+            causal = b * h * 32 * strips * (strips + 1) // 2 * 4
+            moved = {'hard_summary': rectangle + 2 * b * h * n * 4, 'hard_chunk': causal + rectangle}
+            record['shapes'][f'B{b} H{h} N{n}'] = {
+                name: {'ms': sum(v) / len(v), 'bytes': moved[name], 'gbs': moved[name] / (sum(v) / len(v) * 1e-3) / 1e9,
+                       'frac': moved[name] / (sum(v) / len(v) * 1e-3) / 1e9 / peak} for name, v in times.items()}
         record.update(steps=args.steps, warmup=args.warmup)
         print(json.dumps(record))
     else:
@@ -698,7 +731,7 @@ def main():
     parser.add_argument('--kernels-only', action='store_true', help='skip the end-to-end and CPU-baseline legs')
     parser.add_argument('--share', type=int, default=0, help='with --kernels-only: time the head slice one of this many GPUs would get')
     parser.add_argument('--model-batch', type=int, default=16, help='sequences per GPU of the model workload')
-    parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams', 'dense_labels', 'model'],
+    parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams', 'dense_labels', 'saved_state', 'model'],
                         help='side workloads print their own line; the benchmark contract is the training shape')
     args = parser.parse_args()
     SHAPE['batch'] = args.batch
