@@ -525,7 +525,7 @@ def run_reference(args):
 def run_other_workload(args):
     """The side workloads: forward only on the long-context shape (one GPU's share: 4 heads of
     N = 131072 with planted 1024-long runs), forward and backward on dense labels, the integer stages of the saved-state
-    route, and the single-longest-match reduction on symbol streams."""
+    route, a pack of documents, and the single-longest-match reduction on symbol streams."""
     import dism_b200
     dism_b200.install_dropin()
     import cu_flash_dism as cu
@@ -592,6 +592,42 @@ def run_other_workload(args):
             record['ms'][pattern] = {
                 'forward': timed(lambda: forward_hard(sq, sk, v, iq, ik, hard, tau)),
                 'backward': timed(lambda: backward_hard(sq, sk, v, dout, iq, ik, hard, norm, dict(boundary=None, log_weights=lut)))}
+        record.update(steps=args.steps, warmup=args.warmup)
+        print(json.dumps(record))
+    elif args.workload == 'packed':
+        # The benchmark's tokens as one pack: 8 training rows of 8192 tokens, each cut into 256-aligned documents of random
+        # lengths, 16 heads, R32 DV64, labels uniform over 512 symbols.  Forward and backward with the layout, beside the
+        # same tensors run as 8 whole sequences (fixed layout).  A document sees only itself, so the pack has fewer pairs.
+        from flash_dism.hard_forward import hard_log_weights
+        from flash_dism.hard_backward import backward_hard
+        from flash_dism.varlen import VarlenLayout
+        rows, row_tokens, h, r, dv = 8, 8192, 16, 32, 64
+        n = rows * row_tokens
+        rng = np.random.default_rng(0)
+        offsets = [0]
+        for row in range(rows):
+            at = 0
+            while at < row_tokens:
+                at = min(row_tokens, at + 256 * int(rng.integers(1, 17)))
+                offsets.append(row * row_tokens + at)
+        layout = VarlenLayout.from_cu_seqlens(torch.tensor(offsets, dtype=torch.int32), n)
+        sq, sk = [(torch.randn(1, n, h, r, generator=g, device='cuda') * .3).bfloat16() for _ in range(2)]
+        v, dout = [torch.randn(1, n, h, dv, generator=g, device='cuda').bfloat16() for _ in range(2)]
+        iq, ik = [torch.randint(0, 512, (1, h, n), generator=g, device='cuda', dtype=torch.int32) for _ in range(2)]
+        hard, tau = torch.ones(rows, h, dtype=torch.bool, device='cuda'), torch.full((h,), .5, device='cuda')
+        lut = hard_log_weights(tau, row_tokens)
+        _, norm = forward_hard(sq, sk, v, iq, ik, hard, tau, layout=layout)
+        record = {'workload': f'one pack of {len(offsets) - 1} documents in 8 rows of 8192 tokens, H16 R32 DV64, beside the same tokens as 8 whole sequences',
+                  'ms': {'packed': {
+                      'forward': timed(lambda: forward_hard(sq, sk, v, iq, ik, hard, tau, layout=layout)),
+                      'backward': timed(lambda: backward_hard(sq, sk, v, dout, iq, ik, hard, norm, dict(boundary=None, log_weights=lut),
+                                                              layout=layout))}}}
+        fixed = [t.view(rows, row_tokens, h, -1) for t in (sq, sk, v, dout)]
+        fq, fk = [t.view(h, rows, row_tokens).transpose(0, 1).contiguous() for t in (iq, ik)]
+        _, fixed_norm = forward_hard(*fixed[:3], fq, fk, hard, tau)
+        record['ms']['whole sequences'] = {
+            'forward': timed(lambda: forward_hard(*fixed[:3], fq, fk, hard, tau)),
+            'backward': timed(lambda: backward_hard(*fixed[:3], fixed[3], fq, fk, hard, fixed_norm, dict(boundary=None, log_weights=lut)))}
         record.update(steps=args.steps, warmup=args.warmup)
         print(json.dumps(record))
     elif args.workload == 'saved_state':
@@ -731,7 +767,7 @@ def main():
     parser.add_argument('--kernels-only', action='store_true', help='skip the end-to-end and CPU-baseline legs')
     parser.add_argument('--share', type=int, default=0, help='with --kernels-only: time the head slice one of this many GPUs would get')
     parser.add_argument('--model-batch', type=int, default=16, help='sequences per GPU of the model workload')
-    parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams', 'dense_labels', 'saved_state', 'model'],
+    parser.add_argument('--workload', default='training', choices=['training', 'long_context', 'symbol_streams', 'dense_labels', 'saved_state', 'packed', 'model'],
                         help='side workloads print their own line; the benchmark contract is the training shape')
     args = parser.parse_args()
     SHAPE['batch'] = args.batch

@@ -82,6 +82,22 @@ __device__ __forceinline__ int lower_bound_position(const int2* __restrict__ ent
     return lo;
 }
 
+// The same by a whole warp (every lane calls it with the same arguments): 32 evenly spaced probes per round, so one
+// dependent load per factor of 32 of the range instead of one per factor of 2.
+__device__ __forceinline__ int warp_lower_bound_position(const int2* __restrict__ entries, int lo, int hi, int bound, int lane) {
+    while (lo < hi) {
+        const int stride = (hi - lo + 31) >> 5;
+        const int at = lo + lane * stride;
+        const unsigned mask = __ballot_sync(FULL, at < hi && __ldg(&entries[at].x) < bound);
+        const int count = __popc(mask);  // positions ascend, so the probes below the bound are the first `count`
+        if (stride == 1) return lo + count;
+        if (count == 0) return lo;
+        hi = min(hi, lo + count * stride);  // the first probe at or above the bound, if there is one
+        lo += (count - 1) * stride + 1;     // one past the last probe below it
+    }
+    return lo;
+}
+
 // Range of the bucket of `label` that can hold causal partners of owner position `row`.
 template <bool QUERY_MAJOR>
 __device__ __forceinline__ void partner_range(const SideIndex& index, int label, int row, int& cursor, int& end,

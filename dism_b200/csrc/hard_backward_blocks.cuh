@@ -157,7 +157,7 @@ __device__ __forceinline__ void hard_backward_blocks_pass(const BackwardBlockArg
             if (PACKED) {
                 int first = mine.begin[0];
                 for (int r = 1; r < owners; ++r) first = min(first, mine.begin[r]);
-                partner_begin = lower_bound_position(partner_entries, partner_begin, partner_end, first);
+                partner_begin = warp_lower_bound_position(partner_entries, partner_begin, partner_end, first, lane);
             }
         } else {
             // First query at or after the tile's first key.  The bucket's queries are probed 32 at a time by the
@@ -172,12 +172,12 @@ __device__ __forceinline__ void hard_backward_blocks_pass(const BackwardBlockArg
                     partner_begin += __popc(mask);
                     if (mask != FULL) break;
                 }
-                if (probed >= 64) partner_begin = lower_bound_position(partner_entries, partner_begin, partner_end, bound);
+                if (probed >= 64) partner_begin = warp_lower_bound_position(partner_entries, partner_begin, partner_end, bound, lane);
             }
             if (PACKED) {
                 int last = mine.end[0];
                 for (int r = 1; r < owners; ++r) last = max(last, mine.end[r]);
-                partner_end = lower_bound_position(partner_entries, partner_begin, partner_end, last);
+                partner_end = warp_lower_bound_position(partner_entries, partner_begin, partner_end, last, lane);
             }
         }
         const int last_owner = mine.position[owners - 1];

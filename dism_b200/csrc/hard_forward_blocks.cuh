@@ -274,7 +274,7 @@ __global__ __launch_bounds__(BLOCK_WARPS * 32) void hard_forward_blocks_kernel(c
         if (PACKED) {  // the bucket also holds keys of earlier documents
             int first_begin = mine.begin[0];
             for (int r = 1; r < queries; ++r) first_begin = min(first_begin, mine.begin[r]);
-            key_begin = lower_bound_position(key_entries, key_begin, key_end, first_begin);
+            key_begin = warp_lower_bound_position(key_entries, key_begin, key_end, first_begin, lane);
         }
 
         unsigned query[KSTEPS][4];
