@@ -724,6 +724,38 @@ def test_packed_random_documents_match_stand_alone_runs(api, seed):
     torch.testing.assert_close(grads['rtau'], dtau, atol=3e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize('n,symbols', [(8192, 12), (16384, 11)])
+def test_packed_long_buckets_match_stand_alone_runs(api, n, symbols):
+    """A long pack over few symbols (just under the share of matching pairs that would send it to the dense kernels):
+    buckets hold hundreds to more than a thousand keys of many documents, so the warp-wide search for a tile's
+    document range takes two and three rounds.  The pack against every document run by itself."""
+    from flash_dism.varlen import VarlenLayout
+    rng = np.random.default_rng(n + symbols)
+    h, r, dv = 2, 16, 32
+    q, k = (rng.integers(0, symbols, (1, h, n)).astype(np.int32) for _ in range(2))
+    rows = n // 4096
+    cuts = sorted({4096 * row for row in range(rows + 1)} | {int(c) * 256 for c in rng.integers(1, n // 256, 9)})
+    layout = VarlenLayout.from_cu_seqlens(torch.tensor(cuts, dtype=torch.int32), n)
+    sq, sk, v, dout = (t.cuda() for t in vectors(n, 1, n, h, r, dv))
+    hard = torch.ones(rows, h, dtype=torch.bool, device='cuda')
+    tau = torch.tensor([.2, -.3], device='cuda')
+    x = [sq, sk, v, dev(q), dev(k), hard, tau]
+    out, norm = api['fwd'].forward_hard(*x, layout=layout)
+    grads = api['bwd'].backward_hard_recompute(*x[:3], dout, *x[3:], layout=layout)
+    dtau = torch.zeros(h, device='cuda')
+    for start, end in zip(cuts, cuts[1:]):
+        local = ([t[:, start:end].contiguous() for t in x[:3]] + [t[:, :, start:end].contiguous() for t in x[3:5]] +
+                 [hard[:1].contiguous(), tau])
+        want, want_norm = api['fwd'].forward_hard(*local)
+        torch.testing.assert_close(out[:, start:end].float(), want.float(), atol=.008, rtol=.025)
+        torch.testing.assert_close(norm[:, :, start:end], want_norm, atol=2e-5, rtol=2e-6)
+        local_grads = api['bwd'].backward_hard_recompute(*local[:3], dout[:, start:end].contiguous(), *local[3:])
+        for name in ('sq_vec', 'sk_vec', 'v'):
+            torch.testing.assert_close(grads[name][:, start:end].float(), local_grads[name].float(), atol=.008, rtol=.025)
+        dtau += local_grads['rtau']
+    torch.testing.assert_close(grads['rtau'], dtau, atol=3e-2, rtol=2e-3)
+
+
 def test_packed_saved_state_gives_the_same_bits(api):
     """forward_hard(save_state=True) with a layout returns the packed rectangle (what the reference's forward always
     builds); readout and backward accept it and give the bits of the label-only route."""
