@@ -65,12 +65,12 @@ int dism_labels_wait_selftest(int code, int *outcome, void *stream);
 
 /* Strip summaries: summary int32 [B,H,(N-1)/32,N]; non-causal and soft entries are -1.
  * Stands in for cu_flash_dism.hard_summary (dism_v3/src/frontend.cpp:309-312,
- * dism_v3/src/host/hard_summary.cpp:11-73), fixed-length layout. */
+ * dism_v3/src/host/hard_summary.cpp:11-73), fixed-length layout.  ik and summary 16-byte aligned. */
 int dism_hard_summary(const int32_t *iq, const int32_t *ik, const uint8_t *hard, int batch, int heads,
                       int n, int ctas, int32_t *summary, void *stream);
 
 /* Boundary composition over [BH,(N-1)/32,N]; `boundary` may alias `summary` (in place).
- * Stands in for cu_flash_dism.hard_chunk (dism_v3/src/host/hard_chunk.cpp:10-68). */
+ * Stands in for cu_flash_dism.hard_chunk (dism_v3/src/host/hard_chunk.cpp:10-68).  boundary 16-byte aligned. */
 int dism_hard_chunk(const int32_t *summary, int32_t *boundary, int batch_heads, int n, void *stream);
 
 /* lut float [H, n+1]: log2 of sum_{s=1..l} exp(s*tau[h]); entry 0 is -1e6.
