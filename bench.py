@@ -620,6 +620,7 @@ def run_other_workload(args):
         record = {'workload': f'one pack of {len(offsets) - 1} documents in 8 rows of 8192 tokens, H16 R32 DV64, beside the same tokens as 8 whole sequences',
                   'ms': {'packed': {
                       'forward': timed(lambda: forward_hard(sq, sk, v, iq, ik, hard, tau, layout=layout)),
+                      'forward keeping the rectangle': timed(lambda: forward_hard(sq, sk, v, iq, ik, hard, tau, layout=layout, save_state=True)),
                       'backward': timed(lambda: backward_hard(sq, sk, v, dout, iq, ik, hard, norm, dict(boundary=None, log_weights=lut),
                                                               layout=layout))}}}
         fixed = [t.view(rows, row_tokens, h, -1) for t in (sq, sk, v, dout)]
@@ -627,6 +628,7 @@ def run_other_workload(args):
         _, fixed_norm = forward_hard(*fixed[:3], fq, fk, hard, tau)
         record['ms']['whole sequences'] = {
             'forward': timed(lambda: forward_hard(*fixed[:3], fq, fk, hard, tau)),
+            'forward keeping the rectangle': timed(lambda: forward_hard(*fixed[:3], fq, fk, hard, tau, save_state=True)),
             'backward': timed(lambda: backward_hard(*fixed[:3], fixed[3], fq, fk, hard, fixed_norm, dict(boundary=None, log_weights=lut)))}
         record.update(steps=args.steps, warmup=args.warmup)
         print(json.dumps(record))

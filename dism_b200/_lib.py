@@ -19,6 +19,8 @@ SIGNATURES = {
     'dism_labels_wait_selftest': (_I, [_I, _P, _P]),
     'dism_hard_summary': (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P]),
     'dism_hard_chunk': (_I, [_P, _P, _I, _I, _P]),
+    'dism_hard_summary_packed': (_I, [_P, _P, _P, _P, _I, _c.c_int64, _I, _I, _I, _I, _P, _P]),
+    'dism_hard_chunk_packed': (_I, [_P, _P, _P, _I, _c.c_int64, _I, _I, _P]),
     'dism_hard_log_weights': (_I, [_P, _I, _I, _P, _P]),
     'dism_hard_readout_workspace': (_Z, [_I, _I, _I]),
     'dism_hard_readout': (_I, [_P] * 8 + [_I, _I, _P] + [_I] * 7 + [_P, _P, _P, _Z, _P]),

@@ -93,7 +93,7 @@ int dism_profile_read(int index, char* name, int capacity, float* milliseconds) 
 }
 
 const char* dism_last_error(void) { return last_error; }
-int dism_abi_version(void) { return 8; }
+int dism_abi_version(void) { return 9; }
 
 int dism_route_word(const uint32_t* choice) {
     if (choice && !aligned(choice, 4)) return fail(DISM_EINVAL, "graph choice must be one aligned device int32");
@@ -154,6 +154,36 @@ int dism_hard_chunk(const int32_t* summary, int32_t* boundary, int batch_heads, 
     if (int64_t(n) + int64_t((n - 1) / 32) * 32 > INT_MAX) return fail(DISM_EINVAL, "invalid hard checkpoint shape");
     return cuda_status(dism::launch_hard_chunk(summary, boundary, batch_heads, n, static_cast<cudaStream_t>(stream)),
                        "hard_chunk");
+}
+
+static int check_pack(const int64_t* table, int documents, int64_t rows, int heads, int n) {
+    if (int status = check_shape(1, heads, n)) return status;
+    if (documents < 0 || rows < 0 || (documents > 0 && !table)) return fail(DISM_EINVAL, "invalid packed document table");
+    if (documents > n / 256) return fail(DISM_EINVAL, "more documents than 256-token blocks: packed labels/layout length mismatch");
+    if (rows > int64_t(heads) * ((n - 1) / 32 + 1)) return fail(DISM_EINVAL, "packed rows exceed the layout");
+    return DISM_OK;
+}
+
+int dism_hard_summary_packed(const int32_t* iq, const int32_t* ik, const uint8_t* hard, const int64_t* table, int documents,
+                             int64_t rows, int heads, int n, int hard_rows, int ctas, int32_t* summary, void* stream) {
+    if (int status = check_pack(table, documents, rows, heads, n)) return status;
+    if (!iq || !ik || !hard || (!summary && rows)) return fail(DISM_EINVAL, "null pointer");
+    if (hard_rows <= 0 || n % hard_rows || (n / hard_rows) % 256)
+        return fail(DISM_EINVAL, "packed hard rows must evenly divide tokens into 256-aligned training rows");
+    if (ctas < 0) return fail(DISM_EINVAL, "invalid CTA count");
+    if (!aligned(summary, 16) || !aligned(ik, 16)) return fail(DISM_EINVAL, "key labels and hard summary must be 16-byte aligned");
+    return cuda_status(dism::launch_hard_summary_packed(iq, ik, hard, reinterpret_cast<const long long*>(table), documents, rows,
+                                                        heads, n, hard_rows, ctas, summary, static_cast<cudaStream_t>(stream)),
+                       "hard_summary");
+}
+
+int dism_hard_chunk_packed(const int32_t* summary, int32_t* boundary, const int64_t* table, int documents, int64_t rows,
+                           int heads, int n, void* stream) {
+    if (int status = check_pack(table, documents, rows, heads, n)) return status;
+    if ((!summary || !boundary) && rows) return fail(DISM_EINVAL, "null pointer");
+    if (!aligned(boundary, 16)) return fail(DISM_EINVAL, "hard boundary must be 16-byte aligned");
+    return cuda_status(dism::launch_hard_chunk_packed(summary, boundary, reinterpret_cast<const long long*>(table), documents, rows,
+                                                      static_cast<cudaStream_t>(stream)), "hard_chunk");
 }
 
 int dism_hard_log_weights(const float* tau, int heads, int n, float* lut, void* stream) {

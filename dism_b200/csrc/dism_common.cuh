@@ -171,6 +171,11 @@ cudaError_t run_wait_selftest(int code, int* outcome, cudaStream_t stream);
 cudaError_t launch_hard_summary(const int* iq, const int* ik, const uint8_t* hard, int batch, int heads, int n,
                                 int ctas, int* summary, cudaStream_t stream);
 cudaError_t launch_hard_chunk(const int* summary, int* boundary, int batch_heads, int n, cudaStream_t stream);
+cudaError_t launch_hard_summary_packed(const int* iq, const int* ik, const uint8_t* hard, const long long* table,
+                                       int documents, int64_t rows, int heads, int n, int hard_rows, int ctas, int* summary,
+                                       cudaStream_t stream);
+cudaError_t launch_hard_chunk_packed(const int* summary, int* boundary, const long long* table, int documents, int64_t rows,
+                                     cudaStream_t stream);
 
 // Index workspace: per (batch, head) N entries of int2 plus BUCKETS+1 starts, for `sides` sides.
 size_t index_bytes(int batch_heads, int n, int sides);

@@ -9,7 +9,7 @@ compute of its own and has no fallback: without the library, importing it fails.
 Differences a caller can see: `hard_readout` and `hard_backward` accept `boundary=None` (run
 lengths are then derived from the labels inside the kernel, nothing quadratic is stored); with a
 packed `table` a boundary is checked for shape and otherwise left unread (same bits either way);
-the packed `hard_summary` / `hard_chunk` run document by document through the fixed-length kernels; the soft path (`core_forward`, `core_backward`) is not
+the soft path (`core_forward`, `core_backward`) is not
 built and raises NotImplementedError.  The `choice` device word of the reference's CUDA-graph
 router (one CUDA int32; 0 runs the hard path, anything else makes its kernels return at once) is
 handed to the library for the calls of the operator it was given to.
@@ -131,6 +131,28 @@ def _document_table(spans, n, device):
     return cached
 
 
+_row_tables = {}
+
+
+def _row_table(spans, heads, device):
+    """Device int64 [documents, 4] for the packed summary and composition kernels: per non-empty document its first
+    position, its length, the (head, strip) rows before it and the rectangle elements before it; with the totals of
+    the last two.  Uploaded once per distinct pack, head count and device."""
+    key = (tuple(spans), heads, str(device))
+    cached = _row_tables.get(key)
+    if cached is None:
+        if len(_row_tables) >= 32:
+            _row_tables.pop(next(iter(_row_tables)))
+        records, rows, elements = [], 0, 0
+        for begin, length in spans:
+            records.append([begin, length, rows, elements])
+            rows += heads * ((length - 1) // 32)
+            elements += heads * ((length - 1) // 32) * length
+        table = torch.tensor(records, dtype=torch.int64).reshape(len(records), 4).to(device)
+        cached = _row_tables[key] = (table, rows, elements)
+    return cached
+
+
 def _packed_hard(hard, device, heads):
     if not (torch.is_tensor(hard) and hard.device == device and hard.dtype == torch.bool and hard.dim() == 2
             and hard.size(0) > 0 and hard.size(1) == heads and hard.is_contiguous()):
@@ -157,16 +179,27 @@ def hard_summary(query, key, hard, table=None, ctas=0, choice=None):
     """int32 labels [B,H,N] -> strip summaries int32 [B,H,(N-1)//32,N]; packed: the documents'
     [H,(length-1)//32,length] regions one after the other, flattened."""
     if table is not None:
-        if not (torch.is_tensor(query) and query.dim() == 3 and query.size(0) == 1):
+        if not (torch.is_tensor(query) and query.is_cuda and query.dtype == torch.int32 and query.dim() == 3
+                and query.is_contiguous()):
+            _fail('query labels must be contiguous CUDA int32 [B,H,N]')
+        if query.size(0) != 1:
             _fail('packed labels/layout length mismatch')
         h, n = query.size(1), query.size(2)
+        if not (torch.is_tensor(key) and key.device == query.device and key.dtype == torch.int32
+                and key.shape == query.shape and key.is_contiguous()):
+            _fail('invalid key labels')
         _packed_hard(hard, query.device, h)
         spans = _documents(table, n, hard.size(0))
-        row_tokens = n // hard.size(0)
-        pieces = [hard_summary(query[:, :, a:a + m].contiguous(), key[:, :, a:a + m].contiguous(),
-                               hard[a // row_tokens:a // row_tokens + 1].contiguous(), None, ctas, choice).flatten()
-                  for a, m in spans]
-        return torch.cat(pieces) if pieces else torch.empty(0, dtype=torch.int32, device=query.device)
+        if ctas < 0:
+            _fail('invalid CTA count')
+        records, rows, elements = _row_table(spans, h, query.device)
+        with torch.cuda.device(query.device), _routed(choice, query.device):
+            out = torch.empty((elements,), dtype=torch.int32, device=query.device)
+            if rows:
+                _lib.check(_abi.dism_hard_summary_packed(query.data_ptr(), key.data_ptr(), hard.data_ptr(), records.data_ptr(),
+                                                         len(spans), rows, h, n, hard.size(0), int(ctas), out.data_ptr(),
+                                                         _stream(query)))
+        return out
     if not (torch.is_tensor(query) and query.is_cuda and query.dtype == torch.int32 and query.dim() == 3
             and query.is_contiguous()):
         _fail('query labels must be contiguous CUDA int32 [B,H,N]')
@@ -191,18 +224,20 @@ def hard_chunk(summary, table=None, heads=0, choice=None, inplace=False):
     if not (torch.is_tensor(summary) and summary.is_cuda and summary.dtype == torch.int32 and summary.is_contiguous()):
         _fail('hard summary must be contiguous CUDA int32')
     if table is not None:
-        lengths = [m for _, m, *_ in table.tolist() if m]
-        expected = sum(heads * ((m - 1) // 32) * m for m in lengths)
-        if heads <= 0 or summary.dim() != 1 or summary.numel() != expected:
+        if not (torch.is_tensor(table) and table.device.type == 'cpu' and table.dtype == torch.int64 and table.dim() == 2
+                and table.size(1) == 7):
+            _fail('layout must be CPU int64 [sequences,7]')
+        spans = [(begin, m) for begin, m, *_ in table.tolist() if m]
+        tokens = sum(m for _, m in spans)
+        expected = sum(heads * ((m - 1) // 32) * m for _, m in spans)
+        if heads <= 0 or summary.dim() != 1 or summary.numel() != expected or tokens % 256 or any(m % 256 for _, m in spans):
             _fail('invalid packed hard summary/heads')
-        out = summary if inplace else torch.empty_like(summary)
-        at = 0
-        for m in lengths:
-            size = heads * ((m - 1) // 32) * m
-            if size:
-                region = summary[at:at + size].view(1, heads, (m - 1) // 32, m)
-                out[at:at + size] = hard_chunk(region, None, heads, choice, inplace).flatten()
-            at += size
+        records, rows, _ = _row_table(spans, heads, summary.device)
+        with torch.cuda.device(summary.device), _routed(choice, summary.device):
+            out = summary if inplace else torch.empty_like(summary)
+            if rows:
+                _lib.check(_abi.dism_hard_chunk_packed(summary.data_ptr(), out.data_ptr(), records.data_ptr(), len(spans), rows,
+                                                       heads, tokens, _stream(summary)))
         return out
     if summary.dim() != 4:
         _fail('fixed hard summary must be [B,H,C,N]')

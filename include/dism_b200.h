@@ -73,6 +73,20 @@ int dism_hard_summary(const int32_t *iq, const int32_t *ik, const uint8_t *hard,
  * Stands in for cu_flash_dism.hard_chunk (dism_v3/src/host/hard_chunk.cpp:10-68).  boundary 16-byte aligned. */
 int dism_hard_chunk(const int32_t *summary, int32_t *boundary, int batch_heads, int n, void *stream);
 
+/* The same two stages over a pack of documents (one batch row of n tokens): the `table` branches of
+ * dism_v3/src/host/hard_summary.cpp:29-60 and dism_v3/src/host/hard_chunk.cpp:18-45.  The rectangle is the
+ * documents' [H,(length-1)/32,length] regions one after the other (the reference's ForwardOffset * H layout,
+ * dism_v3/include/varlen/layout.cuh:17-20).  `table` is DEVICE int64 [documents,4], one record per non-empty
+ * document in order: first position, length (both multiples of 256), rows before the document (a row is
+ * one (head, strip): H * (length-1)/32 per document), rectangle elements before it; `rows` is the total.
+ * The caller builds and vouches for the table (the library cannot read it on the host); `hard` is
+ * [hard_rows,H], a document lies inside one training row of n / hard_rows tokens. */
+int dism_hard_summary_packed(const int32_t *iq, const int32_t *ik, const uint8_t *hard, const int64_t *table,
+                             int documents, int64_t rows, int heads, int n, int hard_rows, int ctas,
+                             int32_t *summary, void *stream);
+int dism_hard_chunk_packed(const int32_t *summary, int32_t *boundary, const int64_t *table, int documents,
+                           int64_t rows, int heads, int n, void *stream);
+
 /* lut float [H, n+1]: log2 of sum_{s=1..l} exp(s*tau[h]); entry 0 is -1e6.
  * Stands in for cu_flash_dism.hard_log_weights (dism_v3/src/host/hard_forward.cpp:11-23). */
 int dism_hard_log_weights(const float *tau, int heads, int n, float *lut, void *stream);

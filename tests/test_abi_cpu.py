@@ -29,7 +29,7 @@ def test_every_declared_symbol_is_exported_and_typed(lib):
     for name in names:
         assert hasattr(lib, name), f'{name} is declared in include/dism_b200.h but not exported'
         assert name in _lib.SIGNATURES, f'{name} has no ctypes signature'
-    assert lib.dism_abi_version() >= 8
+    assert lib.dism_abi_version() >= 9
 
 
 def test_library_has_no_torch_dependency(lib):
@@ -74,6 +74,13 @@ def test_argument_checks_run_without_a_device(lib):
     assert lib.dism_labels(p, p, 1, 16, 2, 48, 512, p, None) == 2 and 'unsupported' in message(lib)
     assert lib.dism_labels(p, ctypes.c_void_p(4104), 1, 16, 2, 64, 512, p, None) == 1 and '16-byte aligned' in message(lib)
     assert lib.dism_longest_match(p, 1, 13, p, p, p, p, 1 << 20, None) == 1
+    # packed summary / composition: the checks that need no look at the device table
+    assert lib.dism_hard_summary_packed(p, p, p, p, 3, 40, 2, 1000, 1, 0, p, None) == 1 and '256-aligned' in message(lib)
+    assert lib.dism_hard_summary_packed(p, p, p, p, 3, 40, 2, 1024, 3, 0, p, None) == 1 and 'training rows' in message(lib)
+    assert lib.dism_hard_summary_packed(p, p, p, p, 5, 40, 2, 1024, 1, 0, p, None) == 1 and 'length mismatch' in message(lib)
+    assert lib.dism_hard_summary_packed(p, p, p, p, 3, 40, 2, 1024, 1, -1, p, None) == 1 and 'CTA' in message(lib)
+    assert lib.dism_hard_chunk_packed(p, p, p, 3, 1 << 40, 2, 1024, None) == 1 and 'exceed' in message(lib)
+    assert lib.dism_hard_chunk_packed(p, ctypes.c_void_p(4100), p, 3, 10, 2, 1024, None) == 1 and '16-byte aligned' in message(lib)
     # the route word: one aligned device int32, or NULL to clear it (the pointer is only stored here)
     assert lib.dism_route_word(ctypes.c_void_p(4098)) == 1 and 'graph choice' in message(lib)
     assert lib.dism_route_word(p) == 0 and lib.dism_route_word(None) == 0
