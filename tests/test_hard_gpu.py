@@ -771,6 +771,37 @@ def test_packed_saved_state_gives_the_same_bits(api):
         api['fwd'].hard_readout(*x[:6], state['boundary'][:-1].contiguous(), state['log_weights'], layout=layout)
 
 
+@pytest.mark.parametrize('seed', range(3))
+def test_packed_summary_and_chunk_equal_the_documents_own(api, seed):
+    """Many documents of random lengths in one pack, three heads with runs of different lengths, mixed hard flags: the
+    packed summary and composition (one launch each) against the fixed-length kernels run document by document, bit
+    for bit; in place and with a capped grid too."""
+    from flash_dism.varlen import VarlenLayout
+    rng = np.random.default_rng(400 + seed)
+    n, h, rows = 8192, 3, 4
+    q = np.stack([rng.integers(0, s, n) for s in (2, 3, 40)])[None].astype(np.int32)
+    k = np.stack([rng.integers(0, s, n) for s in (2, 3, 40)])[None].astype(np.int32)
+    cuts = sorted({2048 * row for row in range(rows + 1)} | {int(c) * 256 for c in rng.integers(1, n // 256, 14)})
+    cuts = cuts[:3] + [cuts[2]] + cuts[3:]  # an empty document among them
+    layout = VarlenLayout.from_cu_seqlens(torch.tensor(cuts, dtype=torch.int32), n)
+    hard = torch.from_numpy(rng.random((rows, h)) < .7).cuda()
+    iq, ik = dev(q), dev(k)
+    summary = api['summary'].summarize_hard(iq, ik, hard, layout=layout)
+    capped = api['summary'].summarize_hard(iq, ik, hard, layout=layout, ctas=3)
+    boundary = api['summary'].hard_chunk_scan(summary, layout=layout, heads=h)
+    want_summary, want_boundary = [], []
+    for start, end in zip(cuts, cuts[1:]):
+        if end > start:
+            flags = hard[start // 2048:start // 2048 + 1].contiguous()
+            local = api['summary'].summarize_hard(iq[:, :, start:end].contiguous(), ik[:, :, start:end].contiguous(), flags)
+            want_summary.append(local.flatten())
+            want_boundary.append(api['summary'].hard_chunk_scan(local).flatten())
+    assert torch.equal(summary, torch.cat(want_summary)) and torch.equal(capped, summary)
+    assert torch.equal(boundary, torch.cat(want_boundary))
+    inplace = api['summary'].hard_chunk_scan(summary, layout=layout, heads=h, inplace=True)
+    assert inplace.data_ptr() == summary.data_ptr() and torch.equal(inplace, boundary)
+
+
 def test_packed_summary_chunk_and_errors(api, oracle):
     x, dout, layout, spans = packed_case(api, 'boundary')
     summary = api['summary'].summarize_hard(x[3], x[4], x[5], layout=layout)
